@@ -1,0 +1,181 @@
+"""The step function: a batch of sequences, their new tokens in, the logits at the wanted places
+out, the cache advanced.
+
+ember.cpp's interpreter has `forward(tokens, start_pos, all_rows, tail_rows)` for one sequence:
+the tokens sit at absolute positions start_pos.., the state must hold the positions before them,
+and it returns the last row, every row or the last rows (graph_ir.h:115-124).  Its llama path runs a
+batch's prompts concatenated in one call and then one token per active sequence per call
+(api.cpp:1933-2063, 2212-2303).  All checks that a launch cannot make are made on the host first
+(graph_ir.cpp:3733-3743, 3756-3758, 3897-3899), and an error leaves the state as it was
+(tools/ir_adapter.cpp:244-245).  `Engine.step` is that for a batch of slots.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import numpy as np
+import torch
+
+from ..cache.sequence_cache import CacheError, SequenceCache
+from ..config.base import ModelConfig, get_architecture, load_config
+from ..parts.model import DecoderModel
+from ..parts.spec import ModelSpec
+from ..weights.loader import check_tensors, load_checked
+from .plan import StepPlan, build_step
+
+DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+
+
+class StepError(ValueError):
+    """A step that was refused on the host; nothing was launched and nothing changed."""
+
+
+class Runtime:
+    """Compute type, device and the kernels; prepares stored tensors for them."""
+
+    def __init__(self, dtype, device, ops):
+        self.dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
+        if self.dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute type {dtype!r} is not bfloat16 or float32")
+        self.device = torch.device(device)
+        self.ops = ops
+
+    def matrix(self, t: torch.Tensor, transpose: bool = False) -> torch.Tensor:
+        """[out, in] row-major in the compute type.  float32 compute widens bfloat16 exactly;
+        bfloat16 compute rounds a matrix that was stored in 32-bit, which is what asking for
+        bfloat16 means for a 32-bit checkpoint."""
+        t = t.to(self.device)
+        if transpose:
+            t = t.t()
+        return t.to(self.dtype).contiguous()
+
+    def table(self, t: torch.Tensor) -> torch.Tensor:
+        return t.to(self.device).to(self.dtype).contiguous()
+
+    def vector(self, t: torch.Tensor) -> torch.Tensor:
+        """Biases and norm parameters are read as float32 by every kernel."""
+        return t.to(self.device).to(torch.float32).contiguous()
+
+
+@dataclasses.dataclass
+class AppHandle:
+    """What a mixer gets for one entry of the schedule."""
+    index: int
+    layer: int
+    cache: object            # CacheView or None
+    writes_cache: bool
+    state: object            # tensor [slots, *shape] or None
+
+
+@dataclasses.dataclass
+class StepContext:
+    ops: object
+    dtype: torch.dtype
+    plan: StepPlan
+    apps: list
+    position: object
+
+
+class Engine:
+    """A model, its cache and the step function."""
+
+    def __init__(self, model: DecoderModel, runtime: Runtime, max_tokens: int, max_slots: int | None = None,
+                 config: ModelConfig | None = None):
+        self.model, self.runtime, self.config = model, runtime, config
+        self.ops = runtime.ops
+        spec = model.spec
+        self.vocab_size = spec.vocab_size
+        self.cache = SequenceCache(model.application_needs(), [a.cache_of for a in spec.schedule], max_tokens,
+                                   model.max_positions(), runtime.dtype, runtime.device, max_slots)
+        self.apps = [AppHandle(i, a.layer, self.cache.views[i], self.cache.writes[i], self.cache.states[i])
+                     for i, a in enumerate(spec.schedule)]
+        self._device_buffer = None
+        self.counters = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0}
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda", ops=None,
+                    max_slots: int | None = None) -> "Engine":
+        """Config, model class and weights from `<folder>/config.json` and `model.safetensors`."""
+        config = load_config(folder)
+        spec = get_architecture(config.architecture).build_spec(config)
+        model = DecoderModel(spec)
+        runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
+        tensors = load_checked(folder, model.weight_specs(), spec.ignored_tensors)
+        model.load(tensors, runtime)
+        return cls(model, runtime, max_tokens, max_slots, config)
+
+    @classmethod
+    def from_spec(cls, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096, device="cuda",
+                  ops=None, max_slots: int | None = None) -> "Engine":
+        """A model given as data, with its tensors by name (how tests build toy models)."""
+        model = DecoderModel(spec)
+        runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
+        model.load(check_tensors("tensors", tensors, model.weight_specs(), spec.ignored_tensors), runtime)
+        return cls(model, runtime, max_tokens, max_slots)
+
+    # ------------------------------------------------------------------ sequences
+    def open(self) -> int:
+        return self.cache.open()
+
+    def close(self, slot: int) -> None:
+        self.cache.close(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ------------------------------------------------------------------ the step
+    def check_step(self, entries) -> None:
+        if not entries:
+            raise StepError("a step without sequences")
+        for slot, tokens, want in entries:
+            if len(tokens) == 0:
+                raise StepError(f"slot {slot}: a step brings no tokens")
+            bad = [int(t) for t in tokens if not 0 <= int(t) < self.vocab_size]
+            if bad:
+                raise StepError(f"slot {slot}: token id {bad[0]} is outside the vocabulary [0, {self.vocab_size})")
+            for w in want:
+                if not 0 <= int(w) < len(tokens):
+                    raise StepError(f"slot {slot}: wanted place {w} is not among its {len(tokens)} new tokens")
+
+    def prepare(self, entries, pad_to: int = 0):
+        """Checks a step, takes its pages and builds its description; launches nothing."""
+        self.check_step(entries)
+        shape = [(slot, len(tokens)) for slot, tokens, _ in entries]
+        try:
+            self.cache.reserve(shape)
+        except CacheError as e:
+            raise StepError(str(e)) from None
+        tables = [g.table for g in self.cache.groups]
+        return build_step(entries, self.cache.lengths, tables, self.cache.max_blocks, pad_to), shape
+
+    def upload(self, host) -> StepPlan:
+        n = host.packed.shape[0]
+        if self._device_buffer is None or self._device_buffer.numel() < n:
+            self._device_buffer = torch.empty(max(n, 4096), dtype=torch.int32, device=self.runtime.device)
+        src = torch.from_numpy(host.packed)
+        if self.runtime.device.type == "cuda":
+            src = src.pin_memory()
+        self._device_buffer[:n].copy_(src, non_blocking=True)
+        return StepPlan(host, self._device_buffer)
+
+    def step(self, entries) -> torch.Tensor | None:
+        """entries: (slot, tokens, want) per sequence; `want` lists the places among this step's
+        tokens whose logits are returned.  Returns float32 [sum of wants, vocab] on the device,
+        in the order of the entries and of `want` (None if nothing is wanted)."""
+        host, shape = self.prepare(entries)
+        plan = self.upload(host)
+        logits = self.run(plan)
+        self.cache.commit(shape)
+        self.counters["steps"] += 1
+        self.counters["decode_tokens" if host.all_single else "prompt_tokens"] += sum(n for _, n in shape)
+        return logits
+
+    def run(self, plan: StepPlan):
+        ctx = StepContext(self.ops, self.runtime.dtype, plan, self.apps, self.model.position)
+        return self.model.forward(ctx)
+
+
+def _cuda_ops():
+    from ..csrc.ops import CudaOps
+    return CudaOps()

@@ -1,0 +1,139 @@
+"""The description of one step that the kernels read: which tokens, at which positions, of which
+sequences, in which pages.
+
+ember.cpp's batch path gathers, per step, the active sequences' (token, position, original index)
+(api.cpp:1819-1834) and gives prompt lengths beside the concatenated prompts
+(api.cpp:1961-2011); its graph replay keeps [token, pos, kv_row] in device memory
+(graph_ir.cpp:4361-4364).  Here a step is one packed int32 buffer, built on the host and copied
+once:
+
+  tokens[T] positions[T] token_seq[T]            one entry per token, sequences back to back
+  seq_slot[n] seq_start[n] seq_new[n] cu_new[n+1] one entry per sequence (slot -1: padding)
+  want_rows[R]                                   rows of the token list whose logits are wanted
+  pages[g][n, max_blocks]                        per cache group, each sequence's page numbers
+
+Padding sequences (slot -1, no tokens of their own in prefill; one dummy token in a padded decode
+batch) are skipped by every kernel that touches the cache and change no result.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+import numpy as np
+
+
+@dataclasses.dataclass
+class StepLayout:
+    """Offsets (in int32 elements) of the fields inside the packed buffer."""
+    T: int
+    n: int
+    R: int
+    max_blocks: int
+    n_groups: int
+
+    def __post_init__(self):
+        off = 0
+
+        def take(count):
+            nonlocal off
+            start = off
+            off += -(-count // 4) * 4  # fields start on 16-byte boundaries
+            return start
+
+        self.tokens = take(self.T)
+        self.positions = take(self.T)
+        self.token_seq = take(self.T)
+        self.seq_slot = take(self.n)
+        self.seq_start = take(self.n)
+        self.seq_new = take(self.n)
+        self.cu_new = take(self.n + 1)
+        self.want_rows = take(max(self.R, 1))
+        self.pages = [take(self.n * self.max_blocks) for _ in range(self.n_groups)]
+        self.size = off
+
+
+@dataclasses.dataclass
+class HostStep:
+    """A checked step on the host: the packed buffer and the facts kernels are launched with."""
+    layout: StepLayout
+    packed: np.ndarray            # int32 [layout.size]
+    T: int                        # tokens in the step (with padding tokens)
+    n: int                        # sequences (with padding sequences)
+    n_want: int
+    max_new: int                  # most new tokens of one sequence
+    max_end: int                  # longest sequence after the step
+    all_from_zero: bool           # every real sequence starts at position 0
+    all_single: bool              # every sequence brings one token
+
+
+def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0) -> HostStep:
+    """entries: (slot, tokens, want) per sequence, `want` being indices into that sequence's new
+    tokens.  lengths: slot -> positions held before the step.  page_tables: per group, a function
+    (slots, width) -> int32 [n, width].  pad_to: pad a one-token-each batch with dummy sequences
+    up to this many (0: no padding)."""
+    n_real = len(entries)
+    single = all(len(t) == 1 for _, t, _ in entries)
+    n = max(n_real, pad_to) if (single and pad_to) else n_real
+    T = sum(len(t) for _, t, _ in entries) + (n - n_real)
+    R = sum(len(w) for _, _, w in entries)
+    lay = StepLayout(T, n, R, max_blocks, len(page_tables))
+    buf = np.zeros(lay.size, dtype=np.int32)
+    slots = []
+    t0 = 0
+    r0 = 0
+    max_new = max_end = 0
+    from_zero = True
+    for i in range(n):
+        if i < n_real:
+            slot, toks, want = entries[i]
+            start = lengths[slot]
+        else:
+            slot, toks, want, start = -1, [0], (), 0
+        k = len(toks)
+        slots.append(slot)
+        buf[lay.tokens + t0: lay.tokens + t0 + k] = toks
+        buf[lay.positions + t0: lay.positions + t0 + k] = np.arange(start, start + k)
+        buf[lay.token_seq + t0: lay.token_seq + t0 + k] = i
+        buf[lay.seq_slot + i] = slot
+        buf[lay.seq_start + i] = start
+        buf[lay.seq_new + i] = k
+        buf[lay.cu_new + i] = t0
+        for w in want:
+            if not 0 <= w < k:
+                raise ValueError(f"sequence {i}: wanted place {w} is not among its {k} new tokens")
+            buf[lay.want_rows + r0] = t0 + w
+            r0 += 1
+        t0 += k
+        if slot >= 0:
+            max_new = max(max_new, k)
+            max_end = max(max_end, start + k)
+            from_zero = from_zero and start == 0
+    buf[lay.cu_new + n] = t0
+    for g, table in enumerate(page_tables):
+        buf[lay.pages[g]: lay.pages[g] + n * max_blocks] = table(slots, max_blocks).reshape(-1)
+    return HostStep(lay, buf, T, n, R, max_new, max_end, from_zero, single)
+
+
+class StepPlan:
+    """The same step as the kernels see it: views into one device buffer."""
+
+    def __init__(self, host: HostStep, device_buffer):
+        lay = host.layout
+        self.host = host
+        self.buffer = device_buffer
+        self.T, self.n, self.n_want = host.T, host.n, host.n_want
+        self.max_new, self.max_end, self.max_blocks = host.max_new, host.max_end, lay.max_blocks
+        self.all_from_zero, self.all_single = host.all_from_zero, host.all_single
+
+        def view(start, count):
+            return device_buffer[start:start + count]
+
+        self.tokens = view(lay.tokens, lay.T)
+        self.positions = view(lay.positions, lay.T)
+        self.token_seq = view(lay.token_seq, lay.T)
+        self.seq_slot = view(lay.seq_slot, lay.n)
+        self.seq_start = view(lay.seq_start, lay.n)
+        self.seq_new = view(lay.seq_new, lay.n)
+        self.cu_new = view(lay.cu_new, lay.n + 1)
+        self.want_rows = view(lay.want_rows, max(lay.R, 1))
+        self.pages = [view(p, lay.n * lay.max_blocks).view(lay.n, lay.max_blocks) for p in lay.pages]

@@ -1,0 +1,149 @@
+"""Interfaces of the parts and their registry.
+
+A part is built from a `PartSpec` alone: its sizes and constants are constructor parameters, its
+tensors are named by a prefix that the architecture gives it.  No part knows which model it is in.
+
+Roles and what each must provide:
+
+  norm      forward(ctx, x, out_dtype) -> tensor                     (x: fp32 residual stream)
+  mixer     forward(ctx, h, residual, app) -> new residual stream    (h: normed input)
+            cache_need() -> CacheNeed | None, state_need() -> StateNeed | None
+  ffn       forward(ctx, h, residual) -> new residual stream
+  position  embedding_table() -> tensor | None, max_positions() -> int | None,
+            apply_qk(ctx, qkv, n_heads, kv_heads, head_dim) (in place; default: nothing)
+  block     forward(ctx, x, app) -> x       (the arrangement of the four parts above)
+
+Every part lists its tensors with `weight_specs()` (name, stored shape, how random-weights mode
+fills it) and receives them in `load(get, runtime)`.
+"""
+from __future__ import annotations
+
+import dataclasses
+from typing import Any, Callable
+
+from .spec import PartSpec
+
+
+@dataclasses.dataclass(frozen=True)
+class WeightSpec:
+    """One tensor of a checkpoint: its full name, its shape as stored, and how the
+    random-weights mode draws it: N(mean, std)."""
+    name: str
+    shape: tuple[int, ...]
+    mean: float = 0.0
+    std: float = 0.02
+    integer: bool = False     # an integer table (kept as int32); none in GPT-2
+
+
+@dataclasses.dataclass(frozen=True)
+class CacheNeed:
+    """What a mixer wants from the cache: all keys (`full`) or the last `window` of them."""
+    kind: str                 # "full" | "window"
+    kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclasses.dataclass(frozen=True)
+class StateNeed:
+    """Per-sequence state of fixed size: `shape` float32 values per sequence, set to `init` when a
+    sequence starts."""
+    shape: tuple[int, ...]
+    init: float = 0.0
+
+
+class Part:
+    role = ""
+
+    def __init__(self, prefix: str = ""):
+        self.prefix = prefix
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return []
+
+    def load(self, get: Callable[[str], Any], runtime) -> None:
+        """Fetch the tensors named in weight_specs() with `get(name)` (as stored, on the
+        runtime's device) and keep them in the form the kernels want."""
+
+
+class Norm(Part):
+    role = "norm"
+
+    def forward(self, ctx, x, out_dtype):
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    role = "mixer"
+
+    def cache_need(self) -> CacheNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, ctx, h, residual, app):
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    role = "ffn"
+
+    def forward(self, ctx, h, residual):
+        raise NotImplementedError
+
+
+class Position(Part):
+    role = "position"
+
+    def embedding_table(self):
+        return None
+
+    def max_positions(self) -> int | None:
+        return None
+
+    def apply_qk(self, ctx, qkv, n_heads: int, kv_heads: int, head_dim: int) -> None:
+        return None
+
+
+class Block(Part):
+    role = "block"
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
+        super().__init__("")
+        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+
+    def parts(self):
+        return [self.norm1, self.mixer, self.norm2, self.ffn]
+
+    def forward(self, ctx, x, app):
+        raise NotImplementedError
+
+
+_REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {r: {} for r in ("norm", "mixer", "ffn", "position", "block")}
+
+
+def register_part(role: str, kind: str, factory: Callable[..., Part]) -> None:
+    """Makes `kind` available to specs for `role`.  `factory(prefix=..., **params)` builds the
+    part (for a block: `factory(norm1, mixer, norm2, ffn)`)."""
+    if role not in _REGISTRY:
+        raise ValueError(f"unknown role {role!r}; roles: {sorted(_REGISTRY)}")
+    _REGISTRY[role][kind] = factory
+
+
+def registered(role: str) -> list[str]:
+    return sorted(_REGISTRY[role])
+
+
+def build_part(role: str, spec: PartSpec) -> Part:
+    kinds = _REGISTRY[role]
+    if spec.kind not in kinds:
+        raise ValueError(f"no {role} of kind {spec.kind!r} is registered; registered: {registered(role)}")
+    return kinds[spec.kind](prefix=spec.prefix, **spec.params)
+
+
+def build_block(kind: str, norm1, mixer, norm2, ffn) -> Block:
+    kinds = _REGISTRY["block"]
+    if kind not in kinds:
+        raise ValueError(f"no block arrangement {kind!r} is registered; registered: {registered('block')}")
+    return kinds[kind](norm1, mixer, norm2, ffn)
