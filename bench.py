@@ -1,0 +1,285 @@
+"""Benchmark of the library on one B200: decode tokens per second of GPT-2 XL shape with random
+weights (batch 8 by default, 128-token prompts decoded towards the 1,024-token context), with the
+2,048-token prefill, the decode step's memory roofline and batch 1 / 64 beside it.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+
+Prints ONE JSON line on stdout (everything else goes to stderr).  A "step" is one decode step of
+the whole batch.  `value` times K steps of the engine's own loop (step function + device sampler,
+ids read back every step) with CUDA events; `e2e` is the same count of tokens through the Python
+entry point (`Session.generate_batch`, host ids in, host ids out) by wall clock between its first
+and last new token.  ember.cpp publishes no GPT-2 speed, so `vs_baseline` is null.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+XL = dict(vocab_size=50257, n_positions=1024, n_embd=1600, n_layer=48, n_head=25, n_inner=6400,
+          activation_function="gelu_new", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+PROMPT_LEN = 128
+PREFILL = (2, 1024)
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def xl_config() -> dict:
+    """The sizes of BASELINE.json's configs[2] (read from the file when it is there)."""
+    cfg = dict(XL)
+    try:
+        with open(os.path.join(ROOT, "BASELINE.json")) as f:
+            text = json.load(f)["configs"][2]
+        for key in ("n_layer", "n_embd", "n_head", "n_inner", "n_positions"):
+            m = re.search(key + r"=(\d+)", text)
+            if m:
+                cfg[key] = int(m.group(1))
+        m = re.search(r"vocab=(\d+)", text)
+        if m:
+            cfg["vocab_size"] = int(m.group(1))
+    except (OSError, KeyError, IndexError, ValueError):
+        pass
+    return cfg
+
+
+def peaks() -> dict:
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed regions run (read only)."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self, windows) -> dict:
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        sm, mx, reasons = [], [], set()
+        for t, cols in self.rows:
+            if len(cols) < 6 or not any(a <= t <= b for a, b in windows):
+                continue
+            try:
+                sm.append(float(cols[0]))
+                mx.append(float(cols[1]))
+            except ValueError:
+                continue
+            for name, v in zip(names, cols[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def reference_arm() -> int:
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    why = ("ember.cpp is a CMake/C++ project whose build fetches its JSON dependency from the network and has no "
+           "sm_100 target; it does not install offline" if not os.path.isdir(ref) or not os.listdir(ref)
+           else "baseline/_ref holds no importable GPT-2 path of ember.cpp")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures one GPU: this library runs a model on a single GPU (asked for {args.gpus})")
+        return 2
+
+    import numpy as np
+    import torch
+
+    import ember_cpp_b200 as E
+    from ember_cpp_b200.config import get_architecture
+    from ember_cpp_b200.engine import Engine
+    from ember_cpp_b200.parts import DecoderModel
+    from ember_cpp_b200.weights import random_tensors
+
+    W = max(3, args.warmup)
+    cfgd = xl_config()
+    full_layers = cfgd["n_layer"]
+    if args.layers:
+        cfgd["n_layer"] = args.layers
+    cfg = E.GPT2Config.from_dict({**cfgd, "architectures": ["GPT2LMHeadModel"]})
+    ctx = cfg.n_positions
+    K = args.steps if args.steps is not None else ctx - PROMPT_LEN - W
+    K = max(1, min(K, ctx - PROMPT_LEN - W))
+    pk = peaks()
+
+    t0 = time.time()
+    spec = get_architecture(cfg.architecture).build_spec(cfg)
+    tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=0, dtype=torch.bfloat16, device="cuda")
+    log(f"random weights: {sum(t.numel() for t in tensors.values()) / 1e9:.3f} G parameters in {time.time() - t0:.1f} s")
+    biggest = max(args.batch, 1 if args.no_points else 64)
+    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=biggest * ctx)
+    engine.config = cfg
+    del tensors
+    sampler = E.Sampler(engine.ops)
+    params = E.SamplingParams()  # ember.cpp's defaults: temperature 0.1, top_k 40, top_p 0.9
+    rng = np.random.default_rng(0)
+    d, L, F, V = cfg.n_embd, cfg.n_layer, cfg.inner, cfg.vocab_size
+    weight_bytes = L * (3 * d * d + d * d + 2 * d * F) * 2 + V * d * 2 + L * (3 * d + d + F + d + 4 * d) * 4 + 2 * d * 4
+    kv_bytes_per_pos = L * 2 * d * 2
+    clocks = ClockSampler()
+    clocks.start()
+    windows = []
+
+    def decode_run(B: int, warm: int, steps: int):
+        """Prefill B prompts of PROMPT_LEN, then warm + steps decode steps; times the last `steps`."""
+        slots = [engine.open() for _ in range(B)]
+        prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(B)]
+        logits = engine.step([(s, p, [PROMPT_LEN - 1]) for s, p in zip(slots, prompts)])
+        streams = torch.arange(B, dtype=torch.int32, device="cuda")
+        counters = torch.zeros(B, dtype=torch.int32, device="cuda")
+        toks = sampler.sample(logits, params, streams, counters).tolist()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        cache_bytes = 0
+        launches0 = 0
+        for i in range(warm + steps):
+            if i == warm:
+                torch.cuda.synchronize()
+                launches0 = engine.ops.launches
+                w0 = time.time()
+                start.record()
+            if i >= warm:
+                cache_bytes += sum(engine.length(s) + 1 for s in slots) * kv_bytes_per_pos
+            logits = engine.step([(s, [t], [0]) for s, t in zip(slots, toks)], borrow=True)
+            counters += 1
+            toks = sampler.sample(logits, params, streams, counters).tolist()
+        stop.record()
+        torch.cuda.synchronize()
+        windows.append((w0, time.time()))
+        ms = start.elapsed_time(stop)
+        launches = engine.ops.launches - launches0
+        for s in slots:
+            engine.close(s)
+        return {"tok_s": B * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches,
+                "bytes_per_step": weight_bytes + cache_bytes / steps}
+
+    log("main decode run ...")
+    main_run = decode_run(args.batch, W, K)
+    log(main_run)
+    points = {}
+    if not args.no_points:
+        for B in (1, 64):
+            r = decode_run(B, W, ctx - PROMPT_LEN - W)
+            points[f"decode_b{B}"] = round(r["tok_s"], 1)
+            log(f"batch {B}: {r}")
+
+    # prefill of 2,048 tokens: 2 prompts x 1,024, the last row's logits wanted
+    n_seq, plen = PREFILL
+    plen = min(plen, ctx)
+    T = n_seq * plen
+    times = []
+    for rep in range(2 + 5):
+        slots = [engine.open() for _ in range(n_seq)]
+        prompts = [rng.integers(0, V, plen).tolist() for _ in range(n_seq)]
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        a.record()
+        engine.step([(s, p, [plen - 1]) for s, p in zip(slots, prompts)])
+        b.record()
+        torch.cuda.synchronize()
+        if rep >= 2:
+            times.append(a.elapsed_time(b))
+            windows.append((w0, time.time()))
+        for s in slots:
+            engine.close(s)
+    pre_ms = statistics.median(times)
+    pre_flops = 2 * T * L * (3 * d * d + d * d + 2 * d * F) + n_seq * 2 * d * plen * (plen + 1) * L + 2 * n_seq * d * V
+    prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
+               "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # the same decode through the Python entry point: host ids in, host ids out
+    session = E.Session.from_engine(engine, max_batch_size=args.batch, seed=0)
+    stamps = []
+    session.set_token_callback(lambda i, tok: stamps.append(time.perf_counter()) if i == 0 else None)
+    prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(args.batch)]
+    w0 = time.time()
+    out = session.generate_batch(prompts, steps=W + K + 1, temperature=params.temperature, top_k=params.top_k,
+                                 top_p=params.top_p, stop_token_ids=[])
+    windows.append((w0, time.time()))
+    e2e_tok_s = args.batch * K / (stamps[-1] - stamps[-1 - K])
+    assert all(len(o) == W + K + 1 for o in out)
+    from ember_cpp_b200.engine import StepLayout
+    bucket = 1 << (args.batch - 1).bit_length()
+    h2d = StepLayout(bucket, bucket, bucket, engine.cache.max_blocks, len(engine.cache.groups)).size * 4
+    clocks.stop()
+
+    achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tok/s (GPT-2 XL shape, random weights)", "value": round(main_run["tok_s"], 1),
+        "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": round(main_run["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": "gpt2-xl-shape", "n_layer": L, "n_layer_of_config": full_layers, "n_embd": d,
+                   "n_head": cfg.n_head, "n_inner": F, "vocab_size": V, "n_positions": ctx, "global_batch": args.batch,
+                   "seq_len": ctx, "prompt_len": PROMPT_LEN, "context_end": PROMPT_LEN + W + K + 1,
+                   "parallelism": "single-gpu", "weights": "random seed 0 bf16", "sampling": "t0.1 k40 p0.9",
+                   "l2": "inputs>L2 (3.1 GB of weights per step)", "peaks": pk["source"]},
+        "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": args.batch * 4},
+        "gpu_launches": main_run["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks.summary(windows),
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

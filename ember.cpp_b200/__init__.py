@@ -8,5 +8,12 @@ from . import config, parts, weights, cache  # noqa: F401
 from . import architectures  # noqa: F401  (registers the built-in architectures)
 from .config import ConfigError, GPT2Config, load_config, register_architecture
 from .parts import ModelSpec, register_part
+from .engine import Engine, StepError
+from .engine.generate import Generation, GenerationParams, Generator
+from .sampling import Sampler, SamplingParams
+from .api import Session, TinyLlamaSession
+from .weights import WeightError, write_random_model
 
-__all__ = ["ConfigError", "GPT2Config", "ModelSpec", "load_config", "register_architecture", "register_part"]
+__all__ = ["ConfigError", "Engine", "GPT2Config", "Generation", "GenerationParams", "Generator", "ModelSpec", "Sampler",
+           "SamplingParams", "Session", "StepError", "TinyLlamaSession", "WeightError", "load_config",
+           "register_architecture", "register_part", "write_random_model"]

@@ -1,0 +1,153 @@
+// Writing keys and values into the paged cache, and the plain attention kernel over it.
+//
+// ember.cpp writes K[pos] = k, V[pos] = v per block (kv_write_kernel, graph_ir_cuda.cu:212-220)
+// and then runs, per (query, head), scores = (q.k_j)*scale over the keys up to the query's own
+// position, softmax, weighted sum of values (cpu_attention.cpp:92-211; baseline CUDA kernel
+// cuda_kernels.cu:1728-1896).  The plain kernel here does the same for any mix of sequences,
+// positions and lengths: one warp per (token, head), keys in groups of 32 counted from the first
+// visible key, an online softmax whose order depends on the key positions alone.  A token's
+// result therefore does not depend on the batch, the step's cut or the page numbers.  It is the
+// kernel of the 32-bit path and the twin that the faster kernels are tested against.
+//
+// Cache layout: page p of a layer is [kv_heads][64][head_dim]; a sequence's position j lives in
+// page pages[seq][j / 64] at row j % 64.
+#include "common.cuh"
+
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
+                                const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks,
+                                int q_width, int kv_heads, int hd) {
+  const int t = blockIdx.x;
+  const int s = token_seq[t];
+  if (seq_slot[s] < 0) return;
+  const int p = positions[t];
+  const int page = pages[s * max_blocks + p / kPage];
+  if (page < 0) return;
+  const int kv_width = kv_heads * hd;
+  const T* src = qkv + (size_t)t * (q_width + 2 * kv_width) + q_width;
+  for (int i = threadIdx.x; i < kv_width; i += blockDim.x) {
+    const int h = i / hd, d = i % hd;
+    const size_t dst = (((size_t)page * kv_heads + h) * kPage + (p % kPage)) * hd + d;
+    kc[dst] = src[i];
+    vc[dst] = src[kv_width + i];
+  }
+}
+
+EMBER_API int ember_kv_store(const void* qkv, void* kc, void* vc, const int* positions, const int* token_seq,
+                             const int* seq_slot, const int* pages, int max_blocks, int T, int n_heads, int kv_heads,
+                             int hd, int dtype, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && hd > 0 && max_blocks > 0, "kv_store: bad sizes");
+  const int qw = n_heads * hd;
+  if (dtype == EMBER_F32)
+    kv_store_kernel<float><<<T, 128, 0, stream>>>((const float*)qkv, (float*)kc, (float*)vc, positions, token_seq,
+                                                  seq_slot, pages, max_blocks, qw, kv_heads, hd);
+  else if (dtype == EMBER_BF16)
+    kv_store_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)kc,
+                                                          (__nv_bfloat16*)vc, positions, token_seq, seq_slot, pages,
+                                                          max_blocks, qw, kv_heads, hd);
+  else
+    return ember_fail("kv_store: element type %d", dtype);
+  EMBER_LAUNCH_OK("kv_store");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------- plain attention
+constexpr int kMaxHeadDim = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, const T* __restrict__ vc,
+                       T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                       const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks, int T_tokens,
+                       int n_heads, int kv_heads, int hd, float scale, int window) {
+  __shared__ float q_s[4][kMaxHeadDim];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 4 + warp;
+  if (item >= T_tokens * n_heads) return;  // whole warps leave together
+  const int t = item / n_heads, h = item % n_heads;
+  const int qkv_width = (n_heads + 2 * kv_heads) * hd;
+  T* o = out + (size_t)t * n_heads * hd + (size_t)h * hd;
+  const int s = token_seq[t];
+  if (seq_slot[s] < 0) {
+    for (int d = lane; d < hd; d += 32) o[d] = from_float<T>(0.f);
+    return;
+  }
+  const int p = positions[t];
+  const int g = h / (n_heads / kv_heads);
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int* my_pages = pages + (size_t)s * max_blocks;
+  const T* q = qkv + (size_t)t * qkv_width + (size_t)h * hd;
+  for (int d = lane; d < hd; d += 32) q_s[warp][d] = to_float(q[d]);
+  __syncwarp();
+
+  float m = -INFINITY, l = 0.f;
+  float acc[kMaxHeadDim / 32];
+#pragma unroll
+  for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
+
+  for (int base = lo; base <= p; base += 32) {
+    const int j = base + lane;
+    const int page = j <= p ? my_pages[j / kPage] : -1;
+    const bool valid = page >= 0;  // a page that is not held contributes nothing and is never read
+    size_t row = 0;  // element offset of key/value row j of head g
+    float sc = -INFINITY;
+    if (valid) {
+      row = (((size_t)page * kv_heads + g) * kPage + (j % kPage)) * hd;
+      const T* k = kc + row;
+      float dot = 0.f;
+      for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_float(k[d]), dot);
+      sc = dot * scale;
+    }
+    const float m_new = fmaxf(m, warp_max(sc));
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    const float pj = valid ? expf(sc - m_new) : 0.f;
+    l = l * corr + warp_sum(pj);
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= corr;
+    const int n_valid = min(32, p - base + 1);
+    for (int jj = 0; jj < n_valid; ++jj) {
+      const float pv = __shfl_sync(0xffffffffu, pj, jj);
+      const unsigned long long r = __shfl_sync(0xffffffffu, (unsigned long long)row, jj);
+      const T* v = vc + r;
+#pragma unroll
+      for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) acc[i] = fmaf(pv, to_float(v[d]), acc[i]);
+      }
+    }
+    m = m_new;
+  }
+  const float inv = 1.0f / l;
+#pragma unroll
+  for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+    const int d = lane + 32 * i;
+    if (d < hd) o[d] = from_float<T>(acc[i] * inv);
+  }
+}
+
+EMBER_API int ember_attention_plain(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
+                                    const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
+                                    int n_heads, int kv_heads, int hd, float scale, int window, int dtype,
+                                    cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention: bad sizes");
+  EMBER_CHECK(n_heads % kv_heads == 0, "attention: %d heads are not a multiple of %d key/value heads", n_heads,
+              kv_heads);
+  EMBER_CHECK(hd % 16 == 0 && hd >= 16 && hd <= kMaxHeadDim,
+              "attention: head size %d is not a multiple of 16 in [16, %d]", hd, kMaxHeadDim);
+  EMBER_CHECK(window >= 0, "attention: window %d", window);
+  const long long items = (long long)T * n_heads;
+  const int grid = (int)((items + 3) / 4);
+  if (dtype == EMBER_F32)
+    attention_plain_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, (const float*)kc, (const float*)vc,
+                                                            (float*)out, positions, token_seq, seq_slot, pages,
+                                                            max_blocks, T, n_heads, kv_heads, hd, scale, window);
+  else if (dtype == EMBER_BF16)
+    attention_plain_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
+        (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, positions,
+        token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, scale, window);
+  else
+    return ember_fail("attention: element type %d", dtype);
+  EMBER_LAUNCH_OK("attention_plain");
+  return 0;
+}

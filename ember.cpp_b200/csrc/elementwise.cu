@@ -1,0 +1,125 @@
+// Row kernels: token + position embedding, layer norm, row gather, and the error channel.
+//
+// ember.cpp runs these as separate float32 kernels (embedding and position add
+// graph_ir_cuda.cu:19-32, layer norm :47-65 with sums in double).  Here the embedding and the
+// position row are read and added in one kernel, and the norm keeps float32 statistics on the
+// float32 residual stream; each row's arithmetic depends on that row alone.
+#include <stdarg.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+int ember_fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return 1;
+}
+
+EMBER_API const char* ember_last_error() { return g_error; }
+
+// ---------------------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
+                             const T* __restrict__ table, const T* __restrict__ pos_table, float* __restrict__ x,
+                             int d) {
+  const int t = blockIdx.x;
+  const T* row = table + (size_t)tokens[t] * d;
+  const T* prow = pos_table ? pos_table + (size_t)positions[t] * d : nullptr;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float v = to_float(row[i]);
+    if (prow) v += to_float(prow[i]);
+    x[(size_t)t * d + i] = v;
+  }
+}
+
+EMBER_API int ember_embed(const int* tokens, const int* positions, const void* table, const void* pos_table, float* x,
+                          int T, int d, int dtype, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && d > 0, "embed: T = %d, width = %d", T, d);
+  if (dtype == EMBER_F32)
+    embed_kernel<float><<<T, 128, 0, stream>>>(tokens, positions, (const float*)table, (const float*)pos_table, x, d);
+  else if (dtype == EMBER_BF16)
+    embed_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(tokens, positions, (const __nv_bfloat16*)table,
+                                                       (const __nv_bfloat16*)pos_table, x, d);
+  else
+    return ember_fail("embed: element type %d", dtype);
+  EMBER_LAUNCH_OK("embed");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------- layer norm
+// One warp per row.  Two passes for mean and biased variance, a third to write.
+template <typename OutT>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                 OutT* __restrict__ out, int rows, int d, float eps) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float* r = x + (size_t)row * d;
+  float s = 0.f;
+  for (int i = lane; i < d; i += 32) s += r[i];
+  const float mean = warp_sum(s) / (float)d;
+  float q = 0.f;
+  for (int i = lane; i < d; i += 32) {
+    const float c = r[i] - mean;
+    q += c * c;
+  }
+  const float var = warp_sum(q) / (float)d;
+  const float inv = 1.0f / sqrtf(var + eps);
+  OutT* o = out + (size_t)row * d;
+  for (int i = lane; i < d; i += 32) o[i] = from_float<OutT>((r[i] - mean) * inv * w[i] + b[i]);
+}
+
+EMBER_API int ember_layernorm(const float* x, const float* w, const float* b, void* out, int rows, int d, float eps,
+                              int out_dtype, cudaStream_t stream) {
+  EMBER_CHECK(rows > 0 && d > 0, "layernorm: rows = %d, width = %d", rows, d);
+  const int warps = 4;
+  const int grid = (rows + warps - 1) / warps;
+  if (out_dtype == EMBER_F32)
+    layernorm_kernel<float><<<grid, warps * 32, 0, stream>>>(x, w, b, (float*)out, rows, d, eps);
+  else if (out_dtype == EMBER_BF16)
+    layernorm_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(x, w, b, (__nv_bfloat16*)out, rows, d, eps);
+  else
+    return ember_fail("layernorm: element type %d", out_dtype);
+  EMBER_LAUNCH_OK("layernorm");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------- row gather
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out,
+                                   int d) {
+  const float* src = x + (size_t)rows[blockIdx.x] * d;
+  float* dst = out + (size_t)blockIdx.x * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+}
+
+EMBER_API int ember_gather_rows(const float* x, const int* rows, float* out, int n_rows, int d, cudaStream_t stream) {
+  EMBER_CHECK(n_rows > 0 && d > 0, "gather_rows: rows = %d, width = %d", n_rows, d);
+  gather_rows_kernel<<<n_rows, 128, 0, stream>>>(x, rows, out, d);
+  EMBER_LAUNCH_OK("gather_rows");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------- activation in place
+// For the activation that the library product has no epilogue for (the erf GELU on the bfloat16
+// path): y = act(y), the bias already added by the product.
+template <typename T>
+__global__ void act_kernel(T* __restrict__ y, size_t n, int act) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = from_float<T>(apply_act(to_float(y[i]), act));
+}
+
+EMBER_API int ember_act_inplace(void* y, size_t n, int act, int dtype, cudaStream_t stream) {
+  EMBER_CHECK(n > 0, "activation: no elements");
+  const unsigned grid = (unsigned)((n + 255) / 256);
+  if (dtype == EMBER_F32)
+    act_kernel<float><<<grid, 256, 0, stream>>>((float*)y, n, act);
+  else if (dtype == EMBER_BF16)
+    act_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)y, n, act);
+  else
+    return ember_fail("activation: element type %d", dtype);
+  EMBER_LAUNCH_OK("activation");
+  return 0;
+}

@@ -1,0 +1,200 @@
+"""The kernels as the parts call them.
+
+`CudaOps` is the only implementation the library ships: it loads the shared library that
+build.py makes from this folder's CUDA sources and calls its C entry points on torch's current
+stream with raw device pointers.  There is no CPU path and no fallback to library model code; a
+missing compiler, a failed build or a missing GPU is an error at construction.
+
+Which kernel runs is decided here from the element types and the shape of the step:
+float32 operands take the float32 kernels (FFMA product in a fixed order, plain attention),
+bfloat16 operands take the tensor-core kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import build
+
+_F32, _BF16 = 0, 1
+_ACT = {None: 0, "gelu_tanh": 1, "gelu_erf": 2}
+_LT_WORKSPACE = 32 << 20
+
+_c_int, _c_float, _c_void, _c_size, _c_u64 = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint64
+
+_SIGNATURES = {
+    "ember_embed": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
+    "ember_layernorm": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ember_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
+    "ember_act_inplace": [_c_void, _c_size, _c_int, _c_int, _c_void],
+    "ember_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_linear_bf16": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_void, _c_size, _c_void],
+    "ember_kv_store": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_void],
+    "ember_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                              _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
+    "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_void],
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"element type {dtype} is neither float32 nor bfloat16")
+
+
+def load_library() -> ctypes.CDLL:
+    """Builds the library if needed and loads it; every failure is an error that says why."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is visible: this library runs models on a GPU only")
+    major, minor = torch.cuda.get_device_capability()
+    if major != 10:
+        raise KernelError(f"the kernels are built for sm_100a; this device is sm_{major}{minor}")
+    path = build.library_path()
+    lib = ctypes.CDLL(path)
+    lib.ember_last_error.restype = ctypes.c_char_p
+    for name, args in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = _c_int
+    lib._path = path
+    return lib
+
+
+class CudaOps:
+    name = "cuda-sm100a"
+
+    def __init__(self):
+        self.lib = load_library()
+        self._workspace = None
+        self._bias16: dict[int, torch.Tensor] = {}
+        self.launches = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _call(self, name: str, *args) -> None:
+        rc = getattr(self.lib, name)(*args, torch.cuda.current_stream().cuda_stream)
+        self.launches += 1
+        if rc != 0:
+            raise KernelError(self.lib.ember_last_error().decode())
+
+    @staticmethod
+    def _ptr(t):
+        return None if t is None else t.data_ptr()
+
+    @staticmethod
+    def _dense(t: torch.Tensor, what: str) -> torch.Tensor:
+        if not t.is_cuda or not t.is_contiguous():
+            raise KernelError(f"{what} must be a contiguous CUDA tensor")
+        return t
+
+    def _lt_workspace(self) -> torch.Tensor:
+        if self._workspace is None:
+            self._workspace = torch.empty(_LT_WORKSPACE, dtype=torch.uint8, device="cuda")
+        return self._workspace
+
+    def _bias_bf16(self, bias: torch.Tensor) -> torch.Tensor:
+        key = bias.data_ptr()
+        cached = self._bias16.get(key)
+        if cached is None or cached.shape != bias.shape:
+            cached = self._bias16[key] = bias.to(torch.bfloat16)
+        return cached
+
+    # ------------------------------------------------------------------ rows
+    def embed(self, tokens, positions, table, pos_table):
+        T, d = tokens.shape[0], table.shape[1]
+        if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != d):
+            raise KernelError("embed: the position table must have the token table's type and width")
+        x = torch.empty((T, d), dtype=torch.float32, device=table.device)
+        self._call("ember_embed", tokens.data_ptr(), positions.data_ptr(), self._dense(table, "token table").data_ptr(),
+                   self._ptr(pos_table), x.data_ptr(), T, d, _code(table.dtype))
+        return x
+
+    def layernorm(self, x, w, b, eps, out_dtype):
+        rows, d = x.shape
+        if x.dtype != torch.float32 or w.dtype != torch.float32 or b.dtype != torch.float32:
+            raise KernelError("layernorm: input, gain and bias are float32")
+        if w.shape[0] != d or b.shape[0] != d:
+            raise KernelError(f"layernorm: width {d} with gain {tuple(w.shape)} and bias {tuple(b.shape)}")
+        out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
+        self._call("ember_layernorm", self._dense(x, "layernorm input").data_ptr(), w.data_ptr(), b.data_ptr(),
+                   out.data_ptr(), rows, d, float(eps), _code(out_dtype))
+        return out
+
+    def gather_rows(self, x, rows, n_rows):
+        out = torch.empty((n_rows, x.shape[1]), dtype=torch.float32, device=x.device)
+        self._call("ember_gather_rows", self._dense(x, "rows").data_ptr(), rows.data_ptr(), out.data_ptr(), n_rows,
+                   x.shape[1])
+        return out
+
+    # ------------------------------------------------------------------ products
+    def linear(self, a, w, bias, act=None, residual=None, out_dtype=None):
+        """y = a w^T (+ bias) (activation) (+ residual).  `w` is [out, in].  With a residual the
+        sum is made in float32 into the residual's buffer, which is returned."""
+        if act not in _ACT:
+            raise KernelError(f"linear: activation {act!r}")
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise KernelError(f"linear: input width {K} does not match the weight's {tuple(w.shape)}")
+        if a.dtype != w.dtype:
+            raise KernelError(f"linear: input is {a.dtype}, weight is {w.dtype}")
+        if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != N):
+            raise KernelError("linear: the bias is float32 of the output's width")
+        if residual is not None and (residual.dtype != torch.float32 or tuple(residual.shape) != (M, N)):
+            raise KernelError("linear: the residual is float32 of the output's shape")
+        self._dense(a, "linear input")
+        self._dense(w, "linear weight")
+        if w.dtype == torch.float32:
+            out = residual if residual is not None else torch.empty((M, N), dtype=torch.float32, device=a.device)
+            self._call("ember_gemm_f32", a.data_ptr(), w.data_ptr(), self._ptr(bias), self._ptr(residual),
+                       out.data_ptr(), M, N, K, _ACT[act])
+            return out if out_dtype in (None, torch.float32) or residual is not None else out.to(out_dtype)
+        target = torch.float32 if residual is not None else (out_dtype or torch.bfloat16)
+        out = residual if residual is not None else torch.empty((M, N), dtype=target, device=a.device)
+        fused = _ACT[act] if act != "gelu_erf" else 0
+        ws = self._lt_workspace()
+        self._call("ember_linear_bf16", a.data_ptr(), w.data_ptr(), self._ptr(bias),
+                   None if bias is None else self._bias_bf16(bias).data_ptr(), self._ptr(residual), out.data_ptr(),
+                   M, N, K, fused, _code(target), ws.data_ptr(), ws.numel())
+        if act == "gelu_erf":
+            self._call("ember_act_inplace", out.data_ptr(), out.numel(), _ACT[act], _code(target))
+        return out
+
+    # ------------------------------------------------------------------ cache and attention
+    def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):
+        if qkv.dtype != cache.k.dtype:
+            raise KernelError(f"kv_store: activations are {qkv.dtype}, the cache is {cache.k.dtype}")
+        self._call("ember_kv_store", self._dense(qkv, "qkv").data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                   plan.positions.data_ptr(), plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(),
+                   plan.pages[cache.group_index].data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, head_dim,
+                   _code(qkv.dtype))
+
+    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype):
+        if qkv.dtype != cache.k.dtype or out_dtype != qkv.dtype:
+            raise KernelError("attention: activations, cache and output have one element type")
+        out = torch.empty((plan.T, n_heads * head_dim), dtype=out_dtype, device=qkv.device)
+        self._call("ember_attention_plain", self._dense(qkv, "qkv").data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                   out.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(),
+                   plan.pages[cache.group_index].data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, head_dim,
+                   float(scale), int(window), _code(qkv.dtype))
+        return out
+
+    # ------------------------------------------------------------------ sampling
+    def sample(self, logits, temperature, top_k, top_p, seed, streams, counters):
+        """One token per row of float32 logits.  `streams` and `counters` (int32, one per row) key
+        the uniform number of each row's draw."""
+        rows, V = logits.shape
+        if logits.dtype != torch.float32:
+            raise KernelError("sample: logits are float32")
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        self._call("ember_sample", self._dense(logits, "logits").data_ptr(), out.data_ptr(), rows, V, float(temperature),
+                   int(top_k), float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF, streams.data_ptr(), counters.data_ptr())
+        return out

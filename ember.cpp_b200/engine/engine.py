@@ -80,7 +80,7 @@ class Engine:
     """A model, its cache and the step function."""
 
     def __init__(self, model: DecoderModel, runtime: Runtime, max_tokens: int, max_slots: int | None = None,
-                 config: ModelConfig | None = None):
+                 config: ModelConfig | None = None, cuda_graphs: bool = True):
         self.model, self.runtime, self.config = model, runtime, config
         self.ops = runtime.ops
         spec = model.spec
@@ -90,12 +90,15 @@ class Engine:
         self.apps = [AppHandle(i, a.layer, self.cache.views[i], self.cache.writes[i], self.cache.states[i])
                      for i, a in enumerate(spec.schedule)]
         self._device_buffer = None
+        self._staging = _Staging(runtime.device)
+        self._graphs: dict[int, "_DecodeGraph"] = {}
+        self.cuda_graphs = bool(cuda_graphs) and runtime.device.type == "cuda"
         self.counters = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0}
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda", ops=None,
-                    max_slots: int | None = None) -> "Engine":
+                    max_slots: int | None = None, cuda_graphs: bool = True) -> "Engine":
         """Config, model class and weights from `<folder>/config.json` and `model.safetensors`."""
         config = load_config(folder)
         spec = get_architecture(config.architecture).build_spec(config)
@@ -103,16 +106,16 @@ class Engine:
         runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
         tensors = load_checked(folder, model.weight_specs(), spec.ignored_tensors)
         model.load(tensors, runtime)
-        return cls(model, runtime, max_tokens, max_slots, config)
+        return cls(model, runtime, max_tokens, max_slots, config, cuda_graphs)
 
     @classmethod
     def from_spec(cls, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096, device="cuda",
-                  ops=None, max_slots: int | None = None) -> "Engine":
+                  ops=None, max_slots: int | None = None, cuda_graphs: bool = True) -> "Engine":
         """A model given as data, with its tensors by name (how tests build toy models)."""
         model = DecoderModel(spec)
         runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
         model.load(check_tensors("tensors", tensors, model.weight_specs(), spec.ignored_tensors), runtime)
-        return cls(model, runtime, max_tokens, max_slots)
+        return cls(model, runtime, max_tokens, max_slots, None, cuda_graphs)
 
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
@@ -138,7 +141,7 @@ class Engine:
                 if not 0 <= int(w) < len(tokens):
                     raise StepError(f"slot {slot}: wanted place {w} is not among its {len(tokens)} new tokens")
 
-    def prepare(self, entries, pad_to: int = 0):
+    def prepare(self, entries, pad_to: int = 0, want_all: bool = False):
         """Checks a step, takes its pages and builds its description; launches nothing."""
         self.check_step(entries)
         shape = [(slot, len(tokens)) for slot, tokens, _ in entries]
@@ -147,33 +150,126 @@ class Engine:
         except CacheError as e:
             raise StepError(str(e)) from None
         tables = [g.table for g in self.cache.groups]
-        return build_step(entries, self.cache.lengths, tables, self.cache.max_blocks, pad_to), shape
+        return build_step(entries, self.cache.lengths, tables, self.cache.max_blocks, pad_to, want_all), shape
+
+    def _stage(self, staging: "_Staging", host, device_buffer) -> None:
+        """Host description -> pinned memory -> device, without racing an earlier copy."""
+        n = host.packed.shape[0]
+        staging.write(host.packed)
+        device_buffer[:n].copy_(staging.pinned[:n], non_blocking=True)
+        staging.copied()
 
     def upload(self, host) -> StepPlan:
         n = host.packed.shape[0]
         if self._device_buffer is None or self._device_buffer.numel() < n:
             self._device_buffer = torch.empty(max(n, 4096), dtype=torch.int32, device=self.runtime.device)
-        src = torch.from_numpy(host.packed)
-        if self.runtime.device.type == "cuda":
-            src = src.pin_memory()
-        self._device_buffer[:n].copy_(src, non_blocking=True)
+        self._stage(self._staging, host, self._device_buffer)
         return StepPlan(host, self._device_buffer)
 
-    def step(self, entries) -> torch.Tensor | None:
+    def step(self, entries, borrow: bool = False) -> torch.Tensor | None:
         """entries: (slot, tokens, want) per sequence; `want` lists the places among this step's
         tokens whose logits are returned.  Returns float32 [sum of wants, vocab] on the device,
-        in the order of the entries and of `want` (None if nothing is wanted)."""
+        in the order of the entries and of `want` (None if nothing is wanted).  With `borrow` the
+        result may be a view of a buffer that the next step overwrites."""
+        if self.cuda_graphs and all(len(t) == 1 for _, t, _ in entries):
+            return self._graph_step(entries, borrow)
         host, shape = self.prepare(entries)
         plan = self.upload(host)
         logits = self.run(plan)
+        self._account(host, shape)
+        return logits
+
+    def _account(self, host, shape) -> None:
         self.cache.commit(shape)
         self.counters["steps"] += 1
         self.counters["decode_tokens" if host.all_single else "prompt_tokens"] += sum(n for _, n in shape)
-        return logits
 
     def run(self, plan: StepPlan):
         ctx = StepContext(self.ops, self.runtime.dtype, plan, self.apps, self.model.position)
         return self.model.forward(ctx)
+
+    # ------------------------------------------------------------------ one token each, as a replayed graph
+    def _graph_step(self, entries, borrow: bool):
+        """A step in which every sequence brings one token runs as a CUDA graph captured once per
+        batch-size bucket (ember.cpp captures its one-token step once and replays it with
+        [token, pos, kv_row] in device memory, graph_ir.cpp:4306-4373).  The batch is padded to the
+        bucket with sequences of slot -1; the description of the step is the only thing that
+        changes between replays."""
+        n_real = len(entries)
+        bucket = 1
+        while bucket < n_real:
+            bucket *= 2
+        host, shape = self.prepare(entries, pad_to=bucket, want_all=True)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = self._graphs[bucket] = _DecodeGraph(self, host)
+        g.replay(self, host)
+        self._account(host, shape)
+        rows = [i for i, (_, _, want) in enumerate(entries) for _ in want]
+        if not rows:
+            return None
+        if rows == list(range(n_real)):
+            out = g.logits[:n_real]
+        else:
+            out = g.logits[torch.tensor(rows, device=g.logits.device)]
+            borrow = True
+        return out if borrow else out.clone()
+
+
+class _Staging:
+    """A pinned host buffer that is not rewritten before its last copy to the device has run."""
+
+    def __init__(self, device):
+        self.cuda = torch.device(device).type == "cuda"
+        self.pinned = None
+        self.event = None
+
+    def write(self, packed: np.ndarray) -> None:
+        n = packed.shape[0]
+        if self.event is not None:
+            self.event.synchronize()
+        if self.pinned is None or self.pinned.numel() < n:
+            self.pinned = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=self.cuda)
+        self.pinned[:n].numpy()[:] = packed
+
+    def copied(self) -> None:
+        if self.cuda:
+            if self.event is None:
+                self.event = torch.cuda.Event()
+            self.event.record()
+
+
+class _DecodeGraph:
+    def __init__(self, engine: Engine, host):
+        dev = engine.runtime.device
+        self.buffer = torch.zeros(host.packed.shape[0], dtype=torch.int32, device=dev)
+        self.staging = _Staging(dev)
+        self.size = host.packed.shape[0]
+        # launches are sized for the longest sequence the cache can hold, lengths come from the buffer
+        sized = dataclasses.replace(host, max_end=engine.cache.max_blocks * 64)
+        self.plan = StepPlan(sized, self.buffer)
+        engine._stage(self.staging, host, self.buffer)
+        if dev.type != "cuda":
+            self.graph = None
+            return
+        # once without capture: libraries choose their algorithms and allocate outside the graph
+        engine.run(self.plan)
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        before = engine.ops.launches
+        with torch.cuda.graph(self.graph):
+            self.logits = engine.run(self.plan)
+        self.launches = engine.ops.launches - before
+
+    def replay(self, engine: Engine, host) -> None:
+        if host.packed.shape[0] != self.size:
+            raise StepError("the step's description changed size under a captured graph")
+        engine._stage(self.staging, host, self.buffer)
+        if self.graph is None:
+            self.logits = engine.run(self.plan)
+        else:
+            self.graph.replay()
+            engine.ops.launches += self.launches
 
 
 def _cuda_ops():

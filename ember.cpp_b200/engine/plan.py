@@ -66,16 +66,17 @@ class HostStep:
     all_single: bool              # every sequence brings one token
 
 
-def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0) -> HostStep:
+def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, want_all: bool = False) -> HostStep:
     """entries: (slot, tokens, want) per sequence, `want` being indices into that sequence's new
     tokens.  lengths: slot -> positions held before the step.  page_tables: per group, a function
     (slots, width) -> int32 [n, width].  pad_to: pad a one-token-each batch with dummy sequences
-    up to this many (0: no padding)."""
+    up to this many (0: no padding).  want_all: every token's row is wanted, padding included, and
+    the entries' own `want` is left to the caller (the shape a replayed graph needs)."""
     n_real = len(entries)
     single = all(len(t) == 1 for _, t, _ in entries)
     n = max(n_real, pad_to) if (single and pad_to) else n_real
     T = sum(len(t) for _, t, _ in entries) + (n - n_real)
-    R = sum(len(w) for _, _, w in entries)
+    R = T if want_all else sum(len(w) for _, _, w in entries)
     lay = StepLayout(T, n, R, max_blocks, len(page_tables))
     buf = np.zeros(lay.size, dtype=np.int32)
     slots = []
@@ -98,7 +99,7 @@ def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0) 
         buf[lay.seq_start + i] = start
         buf[lay.seq_new + i] = k
         buf[lay.cu_new + i] = t0
-        for w in want:
+        for w in (range(k) if want_all else want):
             if not 0 <= w < k:
                 raise ValueError(f"sequence {i}: wanted place {w} is not among its {k} new tokens")
             buf[lay.want_rows + r0] = t0 + w

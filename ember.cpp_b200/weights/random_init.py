@@ -22,22 +22,25 @@ from ..parts.model import DecoderModel
 from .safetensors_io import write_file
 
 
-def _generator(seed: int, name: str) -> torch.Generator:
-    g = torch.Generator(device="cpu")
+def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
+    g = torch.Generator(device=device)
     g.manual_seed((int(seed) * 0x9E3779B1 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF)
     return g
 
 
-def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype) -> torch.Tensor:
+def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
+    """Drawn on `device`; the values of a seed are those of that device's generator (a model
+    folder is always written from the CPU's)."""
     if spec.integer:
         raise ValueError(f"random weights: no rule for the integer table {spec.name!r}")
-    t = torch.empty(spec.shape, dtype=torch.float32)
-    t.normal_(spec.mean, spec.std, generator=_generator(seed, spec.name))
+    t = torch.empty(spec.shape, dtype=torch.float32, device=device)
+    t.normal_(spec.mean, spec.std, generator=_generator(seed, spec.name, device))
     return t.to(dtype)
 
 
-def random_tensors(specs: list[WeightSpec], seed: int, dtype: torch.dtype = torch.bfloat16) -> dict[str, torch.Tensor]:
-    return {s.name: random_tensor(s, seed, dtype) for s in specs}
+def random_tensors(specs: list[WeightSpec], seed: int, dtype: torch.dtype = torch.bfloat16,
+                   device="cpu") -> dict[str, torch.Tensor]:
+    return {s.name: random_tensor(s, seed, dtype, device) for s in specs}
 
 
 def write_random_model(folder: str, config: ModelConfig, seed: int, dtype: torch.dtype = torch.bfloat16) -> str:

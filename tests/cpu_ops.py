@@ -81,3 +81,10 @@ class CpuOps:
 
     def gather_rows(self, x, rows, n_rows):
         return x[rows[:n_rows].long()]
+
+    def sample(self, logits, temperature, top_k, top_p, seed, streams, counters):
+        import plain_gpt2
+        out = [plain_gpt2.sample(logits[r].double().numpy(), temperature, top_k, top_p,
+                                 plain_gpt2.uniform01(seed, int(streams[r]), int(counters[r])))
+               for r in range(logits.shape[0])]
+        return torch.tensor(out, dtype=torch.int32)

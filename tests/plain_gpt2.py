@@ -256,7 +256,8 @@ def sample(row: np.ndarray, temperature: float, top_k: int, top_p: float, u: flo
     """ember.cpp's sampler (api.cpp:238-341) with the draw made by inverse CDF from a given
     uniform u: below temperature 0.05 the first maximal index; else p = softmax((l-max)/T);
     candidates ordered by (p, index) descending; the first top_k of them; then the shortest
-    prefix whose sum reaches top_p; renormalised; drawn in that order."""
+    prefix whose sum reaches top_p.  ember.cpp draws from that set with std::discrete_distribution;
+    the framework draws from the same set, renormalised, by inverse CDF in index order."""
     row = np.asarray(row, dtype=np.float64)
     V = row.shape[0]
     if temperature < 0.05:
@@ -277,11 +278,11 @@ def sample(row: np.ndarray, temperature: float, top_k: int, top_p: float, u: flo
     total = sum(p[i] for i in keep)
     target = u * total
     acc = 0.0
-    for i in keep:
+    for i in sorted(keep):
         acc += p[i]
         if acc > target:
             return i
-    return keep[-1]
+    return max(keep)
 
 
 def generate(m: PlainGPT2, prompt, max_new_tokens: int, temperature: float = 0.0, top_k: int = 0, top_p: float = 1.0,
