@@ -125,14 +125,14 @@ class SequenceCache:
 
         keys: dict[CacheNeed, list[int]] = {}
         for i, (need, _) in enumerate(needs):
-            if need is not None:
+            if need is not None and cache_of[i] is None:   # an entry that reads another's cache has none of its own
                 keys.setdefault(need, []).append(i)
         self.groups = [CacheGroup(need, apps, self.n_pages, self.n_slots, dtype, device) for need, apps in keys.items()]
         self.views: list[CacheView | None] = [None] * len(needs)
         for gi, g in enumerate(self.groups):
             for local, app in enumerate(g.apps):
                 self.views[app] = CacheView(gi, g, local)
-        self.writes = [needs[i][0] is not None for i in range(len(needs))]
+        self.writes = [needs[i][0] is not None and cache_of[i] is None for i in range(len(needs))]
         for i, src in enumerate(cache_of):
             if src is not None:
                 if self.views[src] is None:

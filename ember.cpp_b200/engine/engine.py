@@ -92,7 +92,10 @@ class Engine:
         self._device_buffer = None
         self._staging = _Staging(runtime.device)
         self._graphs: dict[int, "_DecodeGraph"] = {}
-        self.cuda_graphs = bool(cuda_graphs) and runtime.device.type == "cuda"
+        # a part whose forward does work on the host (reads a value back, loops over tokens in
+        # Python) cannot be replayed from a captured graph; it says so with graph_safe = False
+        self.cuda_graphs = (bool(cuda_graphs) and runtime.device.type == "cuda"
+                            and all(getattr(p, "graph_safe", True) for p in model.all_parts()))
         self.counters = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0}
 
     # ------------------------------------------------------------------ construction

@@ -54,6 +54,9 @@ class StateNeed:
 
 class Part:
     role = ""
+    # False for a part whose forward works on the host (reads device values back, loops in Python):
+    # an engine with such a part runs every step launch by launch instead of replaying a graph
+    graph_safe = True
 
     def __init__(self, prefix: str = ""):
         self.prefix = prefix

@@ -1,0 +1,179 @@
+"""The engine on the GPU against the plain implementation: each request alone and whole, long
+decoding, the first tokens of a sequence, batches that follow one another in the same slots, and
+generation through the Python entry point and the command line."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import ember_cpp_b200 as E
+import plain_gpt2
+from conftest import ROOT, TOL, random_ids, rel_error, run_batch
+from ember_cpp_b200.engine import Engine
+
+pytestmark = pytest.mark.gpu
+NAMES = ["tiny_a", "tiny_b"]
+DTYPES = ["float32", "bfloat16"]
+
+
+@pytest.fixture(scope="module")
+def engines(tiny_folders):
+    return {(n, d): Engine.from_folder(tiny_folders[n], dtype=d, max_tokens=2048) for n in NAMES for d in DTYPES}
+
+
+def test_the_kernels_are_the_librarys_own(engines):
+    eng = engines[("tiny_a", "bfloat16")]
+    assert eng.ops.name == "cuda-sm100a" and os.path.isfile(eng.ops.lib._path)
+    with open("/proc/self/maps") as f:
+        assert "libember_kernels.so" in f.read()
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_each_request_alone_and_whole(engines, plains, name, dtype):
+    eng, plain = engines[(name, dtype)], plains[name]
+    for i, n in enumerate((1, 2, 31, 64, 65, plain.n_positions)):
+        ids = random_ids(100 + i, plain.vocab, n)
+        rows, _ = run_batch(eng, [ids], (n,))
+        ref = plain.logits(ids)
+        assert rel_error(rows[0], ref) < TOL[dtype]
+        if dtype == "float32":
+            assert (rows[0].argmax(-1) == ref.argmax(-1)).all()
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_and_first_tokens(engines, plains, name, dtype):
+    """From a one-token prompt to the last position, one token at a time: every row, the first
+    ones (positions 0, 1, 2) and the ones at page edges (63, 64) included."""
+    eng, plain = engines[(name, dtype)], plains[name]
+    ids = random_ids(7, plain.vocab, plain.n_positions)
+    rows, _ = run_batch(eng, [ids], (1,))
+    ref = plain.logits(ids)
+    per_row = [rel_error(rows[0][t], ref[t]) for t in range(len(ids))]
+    assert max(per_row) < TOL[dtype], int(np.argmax(per_row))
+    if dtype == "float32":
+        whole, _ = run_batch(eng, [ids], (len(ids),))
+        assert np.array_equal(whole[0], rows[0])
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batches_of_unequal_lengths_one_after_another(engines, plains, name, dtype):
+    eng, plain = engines[(name, dtype)], plains[name]
+    P = plain.n_positions
+    plans = [((P, 30, 1, 70, 64), (P // 2, 9, 1, 33, 63)),        # the shorter ones end earlier
+             ((65, P - 1, 17), (64, 1, 17)),                      # the slots of the first batch, other lengths
+             ((12, 12, 12, 12, 12, 12, 12), (3, 3, 3, 3, 3, 3, 3))]
+    used = []
+    for b, (lengths, prompts) in enumerate(plans):
+        seqs = [random_ids(200 + 10 * b + i, plain.vocab, n) for i, n in enumerate(lengths)]
+        rows, slots = run_batch(eng, seqs, prompts)
+        used.append(set(slots))
+        for ids, got in zip(seqs, rows):
+            assert rel_error(got, plain.logits(ids)) < TOL[dtype]
+        eng.cache.check()
+        assert eng.cache.slots.held == 0 and eng.cache.groups[0].pages.held == 0
+    assert used[1] <= used[0]                  # slots are used again
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_changes_no_result(engines, plains, dtype):
+    """Three sequences decode in a graph padded to four; the same sequences alone give the same
+    rows (bit for bit in 32-bit)."""
+    eng, plain = engines[("tiny_b", dtype)], plains["tiny_b"]
+    seqs = [random_ids(300 + i, plain.vocab, 40) for i in range(3)]
+    together, _ = run_batch(eng, seqs, (20, 20, 20))
+    for ids, got in zip(seqs, together):
+        alone, _ = run_batch(eng, [ids], (20,))
+        if dtype == "float32":
+            assert np.array_equal(alone[0], got)
+        else:
+            assert rel_error(alone[0], got) < TOL[dtype]
+
+
+def test_graph_replay_equals_launch_by_launch(tiny_folders, plains):
+    plain = plains["tiny_a"]
+    seqs = [random_ids(400 + i, plain.vocab, 50) for i in range(3)]
+    out = []
+    for graphs in (True, False):
+        eng = Engine.from_folder(tiny_folders["tiny_a"], dtype="float32", max_tokens=512, cuda_graphs=graphs)
+        out.append(run_batch(eng, seqs, (10, 1, 30))[0])
+    for a, b in zip(*out):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_entry_point(tiny_folders, plains, name):
+    plain = plains[name]
+    prompts = [random_ids(500 + i, plain.vocab, n) for i, n in enumerate((5, 17, 32, 1, plain.n_positions - 4))]
+    session = E.Session(tiny_folders[name], max_batch_size=3, dtype="float32", max_tokens=1024)
+    got = session.generate_detailed(prompts, steps=16, temperature=0.0)
+    for p, g in zip(prompts, got):
+        want, why = plain_gpt2.generate(plain, p, 16)
+        assert g.tokens == want and g.finish_reason == why
+    assert got[-1].finish_reason == "context"
+    # bfloat16: the same ids wherever the 32-bit logits decide clearly
+    s16 = E.Session(tiny_folders[name], max_batch_size=3, dtype="bfloat16", max_tokens=1024)
+    for p, g in zip(prompts, s16.generate_detailed(prompts, steps=16, temperature=0.0)):
+        ids = list(p)
+        for tok in g.tokens:
+            row = plain.logits(ids)[-1]
+            best = np.sort(row)[-2:]
+            if best[1] - best[0] > 4 * TOL["bfloat16"] * (row.max() - row.min()):
+                assert tok == int(row.argmax())
+            if len(ids) < plain.n_positions:
+                ids.append(tok)
+    assert session.engine.cache.slots.held == 0 and s16.engine.cache.slots.held == 0
+
+
+def test_temperature_generation_equals_plain(tiny_folders, plains):
+    plain = plains["tiny_b"]
+    prompts = [random_ids(600 + i, plain.vocab, n) for i, n in enumerate((1, 9, 40, 63))]
+    session = E.Session(tiny_folders["tiny_b"], max_batch_size=4, dtype="float32", max_tokens=1024, seed=7)
+    got = session.generate_detailed(prompts, steps=24, temperature=0.8, top_k=0, top_p=1.0, stop_token_ids=[])
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        want, why = plain_gpt2.generate(plain, p, 24, 0.8, 0, 1.0, seed=7, stream=i)
+        assert g.tokens == want and g.finish_reason == why
+
+
+def test_command_line(tiny_folders, plains, tmp_path):
+    plain = plains["tiny_a"]
+    prompt = random_ids(700, plain.vocab, 6)
+    cli = [sys.executable, os.path.join(ROOT, "bin", "ember")]
+    r = subprocess.run(cli + [tiny_folders["tiny_a"], "-", "1", "prompt", " ".join(map(str, prompt)), "-mt", "5", "-t", "0",
+                              "--dtype", "float32"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert [int(t) for t in r.stdout.split()] == plain_gpt2.generate(plain, prompt, 5)[0]
+    r = subprocess.run(cli + [tiny_folders["tiny_a"], "-", "1", "batch", "--batch-prompts", "1 2 3", "4 5", "-mt", "3",
+                              "--temperature", "0", "--dtype", "float32", "-mbs", "2"], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stderr
+    assert "--- Prompt 2 ---" in r.stdout
+    want = " ".join(map(str, plain_gpt2.generate(plain, [4, 5], 3)[0]))
+    assert f"Output: {want}" in r.stdout
+    # the random-weights mode writes a folder that loads
+    cfg = tmp_path / "cfg.json"
+    cfg.write_text('{"architectures": ["GPT2LMHeadModel"], "vocab_size": 50, "n_positions": 16, "n_embd": 32, '
+                   '"n_layer": 1, "n_head": 2}')
+    out = tmp_path / "model"
+    r = subprocess.run(cli + [str(out), "-", "1", "random-weights", "--config", str(cfg), "--seed", "3"],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and (out / "model.safetensors").is_file() and (out / "config.json").is_file()
+    r = subprocess.run(cli + [str(out), "-", "1", "prompt", "1 2", "-mt", "2"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and len(r.stdout.split()) == 2
+    r = subprocess.run(cli + [str(out), "-", "1", "prompt", "1 99"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 1 and "vocabulary" in r.stderr
+
+
+def test_missing_extension_is_an_error(monkeypatch):
+    """No silent fallback: without a compiler and a built library there is no engine."""
+    from ember_cpp_b200.csrc import build
+    monkeypatch.setattr(build, "find_nvcc", lambda: (_ for _ in ()).throw(build.BuildError("nvcc was not found")))
+    monkeypatch.setattr(build, "_digest", lambda: "0" * 16)      # makes the built library look stale
+    with pytest.raises(build.BuildError, match="nvcc"):
+        from ember_cpp_b200.csrc.ops import CudaOps
+        CudaOps()

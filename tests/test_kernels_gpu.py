@@ -1,0 +1,334 @@
+"""Each kernel alone against a plain float32/float64 restatement of the same operation in torch, at
+sizes that the engine's own models do not use (widths and vocabularies that are no power of two,
+head sizes from 16 to 256, grouped key/value heads, windows, pages in scrambled order)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2
+from ember_cpp_b200.cache import PAGE, SequenceCache
+from ember_cpp_b200.engine import StepPlan, build_step
+from ember_cpp_b200.parts import CacheNeed
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# against a float64 evaluation of the same inputs: float32 kernels differ by accumulation order
+# only; bfloat16 outputs carry one rounding to 8 bits of mantissa (2^-9 relative) on top
+ATOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from ember_cpp_b200.csrc.ops import CudaOps
+    return CudaOps()
+
+
+def gen(shape, seed, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).cuda()
+
+
+# ------------------------------------------------------------------------------ rows
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d", [48, 1600, 100])
+def test_embed(ops, dtype, d):
+    table, pos = gen((301, d), 0, DT[dtype]), gen((77, d), 1, DT[dtype])
+    tokens = torch.tensor([300, 0, 17, 17, 255], dtype=torch.int32).cuda()
+    positions = torch.tensor([76, 0, 5, 6, 7], dtype=torch.int32).cuda()
+    x = ops.embed(tokens, positions, table, pos)
+    assert x.dtype == torch.float32
+    assert torch.equal(x, table[tokens.long()].float() + pos[positions.long()].float())
+    assert torch.equal(ops.embed(tokens, positions, table, None), table[tokens.long()].float())
+
+
+@pytest.mark.parametrize("out", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows, d, eps", [(1, 64, 1e-5), (7, 1600, 1e-6), (130, 100, 1e-3), (3, 24, 1e-5)])
+def test_layernorm(ops, out, rows, d, eps):
+    x = gen((rows, d), 2) * 3 + 0.7
+    w, b = gen((d,), 3) + 1, gen((d,), 4)
+    got = ops.layernorm(x, w, b, eps, DT[out]).double()
+    want = torch.nn.functional.layer_norm(x.double(), (d,), w.double(), b.double(), eps)
+    tol = 2e-6 if out == "float32" else 2 ** -8
+    assert ((got - want).abs() / (want.abs() + 1)).max().item() < tol
+
+
+def test_layernorm_statistics_are_per_row(ops):
+    """A row's result does not depend on its neighbours or on the number of rows."""
+    x = gen((9, 200), 5)
+    w, b = gen((200,), 6), gen((200,), 7)
+    whole = ops.layernorm(x, w, b, 1e-5, torch.float32)
+    for r in (0, 4, 8):
+        assert torch.equal(ops.layernorm(x[r:r + 1].contiguous(), w, b, 1e-5, torch.float32)[0], whole[r])
+
+
+def test_gather_rows(ops):
+    x = gen((11, 72), 8)
+    rows = torch.tensor([10, 0, 3, 3], dtype=torch.int32).cuda()
+    assert torch.equal(ops.gather_rows(x, rows, 4), x[rows.long()])
+    assert torch.equal(ops.gather_rows(x, rows, 2), x[rows[:2].long()])
+
+
+# ------------------------------------------------------------------------------ products
+def linear_ref(a, w, bias, act, residual):
+    y = a.double() @ w.double().t()
+    if bias is not None:
+        y = y + bias.double()
+    if act == "gelu_tanh":
+        y = torch.nn.functional.gelu(y, approximate="tanh")
+    elif act == "gelu_erf":
+        y = torch.nn.functional.gelu(y)
+    if residual is not None:
+        y = y + residual.double()
+    return y
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("M, N, K", [(1, 40, 24), (5, 4800, 1600), (130, 1000, 96), (64, 200, 320), (3, 50257, 64)])
+@pytest.mark.parametrize("act, with_bias, with_res", [(None, True, False), ("gelu_tanh", True, False),
+                                                      ("gelu_erf", True, False), (None, True, True), (None, False, False)])
+def test_linear(ops, dtype, M, N, K, act, with_bias, with_res):
+    a, w = gen((M, K), 9, DT[dtype]), gen((N, K), 10, DT[dtype], 0.1)
+    bias = gen((N,), 11) if with_bias else None
+    res = gen((M, N), 12) if with_res else None
+    want = linear_ref(a, w, bias, act, res)
+    got = ops.linear(a, w, bias, act=act, residual=None if res is None else res.clone(),
+                     out_dtype=torch.float32 if with_res else DT[dtype])
+    assert got.dtype == (torch.float32 if with_res else DT[dtype])
+    scale = want.abs().max().item() + 1e-6
+    tol = 1e-5 if dtype == "float32" else (2e-3 if with_res else 2 ** -7)
+    assert (got.double() - want).abs().max().item() / scale < tol
+
+
+def test_linear_float32_rows_do_not_depend_on_the_batch(ops):
+    """The 32-bit product adds each output element in one fixed order: a row computed alone is
+    bit-identical to the same row of a large batch."""
+    a, w, bias = gen((150, 200), 13), gen((333, 200), 14, scale=0.1), gen((333,), 15)
+    whole = ops.linear(a, w, bias, act="gelu_tanh", out_dtype=torch.float32)
+    for r in (0, 63, 64, 149):
+        assert torch.equal(ops.linear(a[r:r + 1].contiguous(), w, bias, act="gelu_tanh", out_dtype=torch.float32)[0],
+                           whole[r])
+
+
+def test_linear_refuses_mismatches(ops):
+    from ember_cpp_b200.csrc.ops import KernelError
+    a, w = gen((4, 32), 0), gen((8, 16), 1)
+    with pytest.raises(KernelError, match="width"):
+        ops.linear(a, w, None)
+    with pytest.raises(KernelError, match="float32"):
+        ops.linear(a, gen((8, 32), 1, torch.bfloat16), None)
+    with pytest.raises(KernelError, match="activation"):
+        ops.linear(a, gen((8, 32), 1), None, act="relu")
+
+
+# ------------------------------------------------------------------------------ cache and attention
+def make_step(seqs, heads, kv_heads, hd, dtype, window=0, scramble=True, seed=0, poison=None):
+    """seqs: (already cached, new) positions per sequence.  Returns plan, cache view, qkv and the
+    dense K/V per sequence that the cache holds after the store."""
+    need = CacheNeed("window" if window else "full", kv_heads, hd, window)
+    total = sum(-(-(a + b) // PAGE) for a, b in seqs) + 3
+    cache = SequenceCache([(need, None)], [None], total * PAGE, None, DT[dtype], "cuda")
+    if scramble:                       # take the pages in a scrambled order
+        order = np.random.default_rng(seed).permutation(cache.n_pages)[::1].tolist()
+        cache.groups[0].pages._free = order
+    view = cache.views[0]
+    if poison is not None:
+        view.k.fill_(poison)
+        view.v.fill_(poison)
+    width = (heads + 2 * kv_heads) * hd
+    slots = [cache.open() for _ in seqs]
+    dense = []
+    g = torch.Generator().manual_seed(seed)
+    # fill what is already cached by storing it through a first step
+    return cache, view, slots, width, g
+
+
+def attention_ref(q, k, v, heads, kv_heads, hd, scale, window, start):
+    """q: [n, heads*hd] at positions start.., k/v: [start+n, kv*hd].  float64."""
+    n = q.shape[0]
+    out = torch.zeros(n, heads * hd, dtype=torch.float64)
+    q, k, v = q.double().cpu(), k.double().cpu(), v.double().cpu()
+    rep = heads // kv_heads
+    for t in range(n):
+        p = start + t
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(heads):
+            g = h // rep
+            s = (k[lo:p + 1, g * hd:(g + 1) * hd] @ q[t, h * hd:(h + 1) * hd]) * scale
+            out[t, h * hd:(h + 1) * hd] = torch.softmax(s, 0) @ v[lo:p + 1, g * hd:(g + 1) * hd]
+    return out
+
+
+def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poison=None, qkv_fn=None):
+    """Stores `cached` positions per sequence in one step, then runs the step of `new` positions;
+    returns (got, want) for the second step's tokens."""
+    cache, view, slots, width, g = make_step(seqs, heads, kv_heads, hd, dtype, window, True, seed, poison)
+    scale = 0.37 / math.sqrt(hd)
+    tables = [cache.groups[0].table]
+    data = [torch.randn(a + b, width, generator=g) for a, b in seqs]
+    if qkv_fn is not None:
+        data = qkv_fn(data)
+    data = [d.to(DT[dtype]) for d in data]
+
+    def step(entries, rows):
+        cache.reserve([(s, n) for s, n in entries])
+        host = build_step([(s, [0] * n, []) for s, n in entries], cache.lengths, tables, cache.max_blocks)
+        plan = StepPlan(host, torch.from_numpy(host.packed).cuda())
+        qkv = torch.cat(rows).cuda().contiguous()
+        ops.kv_store(qkv, view, plan, heads, kv_heads, hd)
+        out = ops.attention(qkv, view, plan, heads, kv_heads, hd, scale, window, DT[dtype])
+        cache.commit([(s, n) for s, n in entries])
+        return out
+
+    first = [(s, a) for s, (a, b) in zip(slots, seqs) if a > 0]
+    if first:
+        step(first, [d[:a] for d, (a, b) in zip(data, seqs) if a > 0])
+    got = step([(s, b) for s, (a, b) in zip(slots, seqs)], [d[a:] for d, (a, b) in zip(data, seqs)])
+    want = []
+    qw, kw = heads * hd, kv_heads * hd
+    for d, (a, b) in zip(data, seqs):
+        d = d.float()
+        want.append(attention_ref(d[a:, :qw], d[:, qw:qw + kw], d[:, qw + kw:], heads, kv_heads, hd, scale, window, a))
+    return got.double().cpu(), torch.cat(want)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, kv_heads, hd", [(4, 4, 16), (25, 25, 64), (6, 2, 32), (3, 1, 80), (2, 2, 128),
+                                                 (5, 5, 256), (8, 4, 48)])
+def test_attention_prompts_of_unequal_length(ops, dtype, heads, kv_heads, hd):
+    got, want = run_attention(ops, [(0, 70), (0, 1), (0, 129), (0, 64)], heads, kv_heads, hd, dtype, seed=hd)
+    assert (got - want).abs().max().item() < ATOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, kv_heads, hd", [(4, 4, 16), (25, 25, 64), (6, 2, 32), (3, 1, 80), (4, 2, 128)])
+def test_attention_one_token_each_over_the_cache(ops, dtype, heads, kv_heads, hd):
+    seqs = [(199, 1), (63, 1), (64, 1), (0, 1), (300, 1), (127, 1), (128, 1)]
+    got, want = run_attention(ops, seqs, heads, kv_heads, hd, dtype, seed=hd + 1, poison=1e30)
+    assert (got - want).abs().max().item() < ATOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_tokens_added_to_a_cache(ops, dtype):
+    """More than one new token on top of cached ones: the general case of the step function."""
+    got, want = run_attention(ops, [(50, 30), (64, 64), (1, 5)], 6, 3, 32, dtype, seed=3)
+    assert (got - want).abs().max().item() < ATOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window", [1, 7, 64, 100])
+def test_attention_window(ops, dtype, window):
+    got, want = run_attention(ops, [(0, 150), (130, 1), (90, 20)], 4, 2, 32, dtype, window=window, seed=window)
+    assert (got - want).abs().max().item() < ATOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """One early key is made to stand out (its score far above the rest): every later query must
+    return that key's value.  A kernel that skips, misplaces or double-counts a tile shows here."""
+    heads, hd, far = 2, 64, 37
+
+    def shape(data):
+        for d in data:
+            n = d.shape[0]
+            d[:, :2 * heads * hd] *= 0.05                     # q and k small ...
+            d[far, heads * hd:2 * heads * hd] = 4.0           # ... but key `far` large in every head
+            d[far + 1:, :heads * hd] = 4.0                    # and the later queries aligned with it
+            d[:, 2 * heads * hd:] = torch.arange(n)[:, None].float() / 8   # value row j = j / 8
+        return data
+
+    got, want = run_attention(ops, [(0, 700), (650, 1)], heads, heads, hd, dtype, seed=5, qkv_fn=shape)
+    later = torch.cat([got[far + 1:700], got[700:]])
+    assert (later - far / 8).abs().max().item() < (1e-4 if dtype == "float32" else 5e-2)
+    assert (got - want).abs().max().item() < (1e-4 if dtype == "float32" else 5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_window_edge(ops, dtype):
+    """The key just outside the window stands out and must be ignored; in a second run the key
+    just inside does and must be found."""
+    heads, hd, window, p = 2, 32, 40, 199
+    for offset, seen in ((window, False), (window - 1, True)):
+        j = p - offset
+
+        def shape(data):
+            d = data[0]
+            d[:, :2 * heads * hd] *= 0.05
+            d[j, heads * hd:2 * heads * hd] = 4.0
+            d[p, :heads * hd] = 4.0
+            d[:, 2 * heads * hd:] = 0.0
+            d[j, 2 * heads * hd:] = 100.0
+            return data
+
+        got, want = run_attention(ops, [(p, 1)], heads, heads, hd, dtype, window=window, seed=6, qkv_fn=shape)
+        assert (got - want).abs().max().item() < 1e-1
+        assert (got.min().item() > 99.0) if seen else (got.abs().max().item() < 1e-3)
+
+
+def test_attention_refuses_sizes_it_cannot_run(ops):
+    from ember_cpp_b200.csrc.ops import KernelError
+    for heads, kv, hd in [(4, 4, 24), (4, 3, 32), (2, 2, 512)]:
+        with pytest.raises((KernelError, ValueError)):
+            run_attention(ops, [(0, 4)], heads, kv, hd, "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_kv_store_writes_only_its_rows(ops, dtype):
+    heads, kv_heads, hd = 3, 3, 16
+    cache, view, slots, width, g = make_step([(0, 70)], heads, kv_heads, hd, dtype, poison=7.0)
+    cache.reserve([(slots[0], 70)])
+    host = build_step([(slots[0], [0] * 70, [])], cache.lengths, [cache.groups[0].table], cache.max_blocks)
+    plan = StepPlan(host, torch.from_numpy(host.packed).cuda())
+    qkv = torch.randn(70, width, generator=g).to(DT[dtype]).cuda()
+    ops.kv_store(qkv, view, plan, heads, kv_heads, hd)
+    pages = cache.groups[0].held[slots[0]]
+    k = torch.cat([view.k[p] for p in pages], dim=1)          # [kv_heads, 128, hd]
+    assert torch.equal(k[:, :70].transpose(0, 1).reshape(70, -1), qkv[:, heads * hd:(heads + kv_heads) * hd])
+    assert (k[:, 70:] == 7.0).all()
+    untouched = [p for p in range(cache.n_pages) if p not in pages]
+    assert (view.k[untouched] == 7.0).all() and (view.v[untouched] == 7.0).all()
+
+
+# ------------------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("V", [512, 1000, 50257])
+def test_sample_equals_plain(ops, V):
+    rows = 6
+    logits = gen((rows, V), 20, scale=2.0)
+    streams = torch.arange(rows, dtype=torch.int32).cuda() + 3
+    counters = torch.arange(rows, dtype=torch.int32).cuda() * 5
+    host = logits.cpu().numpy()
+    assert ops.sample(logits, 0.0, 0, 1.0, 1, streams, counters).tolist() == [int(r.argmax()) for r in host]
+    for T, k, p in [(0.8, 0, 1.0), (0.1, 40, 0.9), (1.0, 40, 0.9), (0.7, 5, 1.0), (1.3, 0, 0.5), (2.0, 1, 1.0),
+                    (1.0, 0, 0.0), (1.0, V + 5, 0.999)]:
+        got = ops.sample(logits, T, k, p, 11, streams, counters).tolist()
+        want = [plain_gpt2.sample(host[r], T, k, p, plain_gpt2.uniform01(11, 3 + r, 5 * r)) for r in range(rows)]
+        assert got == want, (T, k, p)
+
+
+def test_sample_first_maximum_and_ties(ops):
+    logits = torch.zeros(3, 300).cuda()
+    logits[0, [17, 250]] = 5.0           # the first of two maxima
+    logits[1, :] = float("-inf")
+    logits[1, 299] = -3.0
+    logits[2, 5] = float("nan")          # a NaN never wins
+    logits[2, 9] = 1.0
+    z = torch.zeros(3, dtype=torch.int32).cuda()
+    assert ops.sample(logits, 0.0, 0, 1.0, 0, z, z).tolist() == [17, 299, 9]
+    # ties at the edge of top_k: the larger indices are kept (pairs ordered by (p, index) descending)
+    flat = torch.zeros(1, 10).cuda()
+    seen = {ops.sample(flat, 1.0, 3, 1.0, s, z[:1], z[:1]).item() for s in range(64)}
+    assert seen == {7, 8, 9}
+
+
+def test_sample_distribution(ops):
+    probs = torch.tensor([0.05, 0.4, 0.05, 0.3, 0.2])
+    n = 4000
+    logits = probs.log().repeat(n, 1).cuda()
+    streams = torch.zeros(n, dtype=torch.int32).cuda()
+    counters = torch.arange(n, dtype=torch.int32).cuda()
+    got = torch.bincount(ops.sample(logits, 1.0, 0, 1.0, 5, streams, counters).long().cpu(), minlength=5) / n
+    assert (got - probs).abs().max().item() < 0.03
+    top2 = torch.bincount(ops.sample(logits, 1.0, 2, 1.0, 5, streams, counters).long().cpu(), minlength=5) / n
+    assert top2[[0, 2, 4]].sum() == 0 and abs(top2[1].item() - 4 / 7) < 0.03

@@ -1,0 +1,276 @@
+"""Each part alone against the plain implementation's function for it, and models put together from
+parts in ways GPT-2 does not use: grouped key/value heads, a window, a layer that runs twice, a
+layer that reads another layer's cache, and a toy mixer with state of its own that is defined and
+registered here, without a change to the library's files."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2
+from conftest import TOL, random_ids, rel_error, run_batch
+from ember_cpp_b200.cache import SequenceCache
+from ember_cpp_b200.engine import Engine, Runtime, StepContext, StepPlan, build_step
+from ember_cpp_b200.engine.engine import AppHandle
+from ember_cpp_b200.parts import (Application, DecoderModel, LayerSpec, Mixer, ModelSpec, PartSpec, StateNeed, build_block,
+                                  build_part, register_part)
+from ember_cpp_b200.weights import random_tensors
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+PART_TOL = {"float32": 2e-5, "bfloat16": 3e-2}      # absolute, on outputs of order one
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from ember_cpp_b200.csrc.ops import CudaOps
+    return CudaOps()
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+def loaded(role, spec, runtime, seed=0, std=None):
+    part = build_part(role, spec)
+    tensors = random_tensors(part.weight_specs(), seed, torch.bfloat16)
+    if std is not None:
+        tensors = {k: (v.float() * std / 0.02).to(torch.bfloat16) if v.ndim == 2 else v for k, v in tensors.items()}
+    part.load(tensors.__getitem__, runtime)
+    return part, {k: f64(v) for k, v in tensors.items()}
+
+
+def context(ops, runtime, part_or_model_needs, seq_lengths, position=None):
+    """A cache, a step of whole prompts of the given lengths, and the context parts run in."""
+    cache = SequenceCache(part_or_model_needs, [None] * len(part_or_model_needs), 1024, None, runtime.dtype, "cuda")
+    slots = [cache.open() for _ in seq_lengths]
+    cache.reserve(list(zip(slots, seq_lengths)))
+    host = build_step([(s, [0] * n, []) for s, n in zip(slots, seq_lengths)], cache.lengths,
+                      [g.table for g in cache.groups], cache.max_blocks)
+    plan = StepPlan(host, torch.from_numpy(host.packed).cuda())
+    apps = [AppHandle(i, i, cache.views[i], cache.writes[i], cache.states[i]) for i in range(len(part_or_model_needs))]
+    return StepContext(ops, runtime.dtype, plan, apps, position or build_part("position", PartSpec("none")))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layernorm_part(ops, dtype):
+    rt = Runtime(dtype, "cuda", ops)
+    part, w = loaded("norm", PartSpec("layernorm", "ln.", {"width": 96, "eps": 1e-6}), rt)
+    x = torch.randn(13, 96, generator=torch.Generator().manual_seed(1)).cuda() * 2 + 0.3
+    got = part.forward(StepContext(ops, rt.dtype, None, [], None), x, rt.dtype)
+    want = plain_gpt2.layer_norm(f64(x), w["ln.weight"], w["ln.bias"], 1e-6)
+    assert got.dtype == rt.dtype and np.abs(f64(got) - want).max() < PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("activation", ["gelu_tanh", "gelu_erf"])
+def test_feed_forward_part(ops, dtype, activation):
+    rt = Runtime(dtype, "cuda", ops)
+    spec = PartSpec("dense", "mlp.", {"width": 96, "inner": 320, "activation": activation, "stored": "in_out"})
+    part, w = loaded("ffn", spec, rt, std=0.1)
+    g = torch.Generator().manual_seed(2)
+    h, res = torch.randn(9, 96, generator=g).to(rt.dtype).cuda(), torch.randn(9, 96, generator=g).cuda()
+    got = part.forward(StepContext(ops, rt.dtype, None, [], None), h, res.clone())
+    want = f64(res) + plain_gpt2.mlp(f64(h), w["mlp.c_fc.weight"].T, w["mlp.c_fc.bias"], w["mlp.c_proj.weight"].T,
+                                     w["mlp.c_proj.bias"], activation[5:])
+    assert got.dtype == torch.float32 and np.abs(f64(got) - want).max() < PART_TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, kv_heads, hd, window, stored", [(3, 3, 32, 0, "in_out"), (6, 2, 16, 0, "out_in"),
+                                                                 (4, 1, 48, 20, "in_out")])
+def test_attention_part(ops, dtype, heads, kv_heads, hd, window, stored):
+    rt = Runtime(dtype, "cuda", ops)
+    width, scale = 72, 0.5 / math.sqrt(hd)
+    spec = PartSpec("causal_attention", "attn.", {"width": width, "n_heads": heads, "kv_heads": kv_heads, "head_dim": hd,
+                                                  "scale": scale, "window": window, "stored": stored})
+    part, w = loaded("mixer", spec, rt, std=0.1)
+    lengths = [37, 1, 70]
+    ctx = context(ops, rt, [(part.cache_need(), None)], lengths)
+    g = torch.Generator().manual_seed(3)
+    h = torch.randn(sum(lengths), width, generator=g).to(rt.dtype).cuda()
+    res = torch.randn(sum(lengths), width, generator=g).cuda()
+    got = f64(part.forward(ctx, h, res.clone(), ctx.apps[0]))
+    t = (lambda a: a.T) if stored == "in_out" else (lambda a: a)
+    at = 0
+    for n in lengths:
+        hh = f64(h[at:at + n])
+        qkv = plain_gpt2.linear(hh, t(w["attn.c_attn.weight"]), w["attn.c_attn.bias"])
+        q, k, v = plain_gpt2.split_qkv(qkv, heads, kv_heads, hd)
+        a = plain_gpt2.attention(q, k, v, heads, kv_heads, hd, scale, window)
+        want = f64(res[at:at + n]) + plain_gpt2.linear(a, t(w["attn.c_proj.weight"]), w["attn.c_proj.bias"])
+        assert np.abs(got[at:at + n] - want).max() < PART_TOL[dtype]
+        at += n
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_position_part_and_embedding(ops, dtype):
+    rt = Runtime(dtype, "cuda", ops)
+    pos, w = loaded("position", PartSpec("learned_absolute", "wpe.", {"width": 40, "n_positions": 50}), rt)
+    assert pos.max_positions() == 50 and build_part("position", PartSpec("none")).embedding_table() is None
+    table = torch.randn(30, 40, generator=torch.Generator().manual_seed(4)).to(rt.dtype).cuda()
+    tokens = torch.tensor([29, 0, 7], dtype=torch.int32).cuda()
+    positions = torch.tensor([49, 0, 3], dtype=torch.int32).cuda()
+    got = f64(ops.embed(tokens, positions, table, pos.embedding_table()))
+    ids = tokens.tolist()
+    for r, (i, p) in enumerate(zip(ids, positions.tolist())):
+        want = plain_gpt2.position_embedding(plain_gpt2.token_embedding(f64(table), [i]), w["wpe.weight"], p)
+        assert np.abs(got[r] - want[0]).max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_block_arrangement(ops, dtype, tiny_folders, plains):
+    """One pre-norm block of tiny B (its second layer, so that the per-layer scale shows)."""
+    plain = plains["tiny_b"]
+    rt = Runtime(dtype, "cuda", ops)
+    from ember_cpp_b200.config import get_architecture, load_config
+    spec = get_architecture("GPT2LMHeadModel").build_spec(load_config(tiny_folders["tiny_b"]))
+    layer = spec.layers[1]
+    block = build_block(layer.block, build_part("norm", layer.norm1), build_part("mixer", layer.mixer),
+                        build_part("norm", layer.norm2), build_part("ffn", layer.ffn))
+    from ember_cpp_b200.weights import read_folder
+    stored = read_folder(tiny_folders["tiny_b"])
+    for p in block.parts():
+        p.load(stored.__getitem__, rt)
+    lengths = [20, 64]
+    ctx = context(ops, rt, [(block.mixer.cache_need(), None)], lengths)
+    x = torch.randn(sum(lengths), 96, generator=torch.Generator().manual_seed(5)).cuda()
+    got = f64(block.forward(ctx, x.clone(), ctx.apps[0]))
+    assert np.abs(got[:20] - plain_gpt2.block(plain, 1, f64(x[:20]))).max() < PART_TOL[dtype]
+    assert np.abs(got[20:] - plain_gpt2.block(plain, 1, f64(x[20:]))).max() < PART_TOL[dtype]
+
+
+# ------------------------------------------------------------------------------ models GPT-2 is not
+class ToyDecay(Mixer):
+    """A mixer with state of its own and no cache: s <- decay * s + h W^T per token, output s.
+    Its loop runs on the host, so an engine that holds it does not replay graphs."""
+    graph_safe = False
+
+    def __init__(self, prefix, width, decay):
+        super().__init__(prefix)
+        self.width, self.decay = width, decay
+
+    def weight_specs(self):
+        from ember_cpp_b200.parts import WeightSpec
+        return [WeightSpec(self.prefix + "mix.weight", (self.width, self.width), std=0.05)]
+
+    def load(self, get, runtime):
+        self.w = runtime.matrix(get(self.prefix + "mix.weight"))
+
+    def state_need(self):
+        return StateNeed((self.width,), init=0.25)
+
+    def forward(self, ctx, h, residual, app):
+        u = ctx.ops.linear(h, self.w, None, out_dtype=ctx.dtype).float()
+        plan = ctx.plan
+        slots, cu = plan.seq_slot.tolist(), plan.cu_new.tolist()
+        out = torch.empty_like(u)
+        for i, slot in enumerate(slots):
+            if slot < 0:
+                continue
+            s = app.state[slot]
+            for t in range(cu[i], cu[i + 1]):
+                s = self.decay * s + u[t]
+                out[t] = s
+            app.state[slot] = s
+        return residual + out
+
+
+def toy_spec(width, vocab, n_pos, mixers, schedule, eps=1e-5):
+    """mixers: per layer ("attn", heads, kv_heads, hd, window) or ("decay", decay)."""
+    layers = []
+    for i, m in enumerate(mixers):
+        p = f"layers.{i}."
+        if m[0] == "attn":
+            _, heads, kv, hd, window = m
+            mixer = PartSpec("causal_attention", p + "attn.", {"width": width, "n_heads": heads, "kv_heads": kv,
+                                                               "head_dim": hd, "scale": 1 / math.sqrt(hd), "window": window,
+                                                               "qkv": "qkv", "out": "o", "stored": "out_in",
+                                                               "init_std": 0.08, "out_init_std": 0.08})
+        else:
+            mixer = PartSpec("toy_decay", p + "decay.", {"width": width, "decay": m[1]})
+        layers.append(LayerSpec("pre_norm", PartSpec("layernorm", p + "n1.", {"width": width, "eps": eps}), mixer,
+                                PartSpec("layernorm", p + "n2.", {"width": width, "eps": eps}),
+                                PartSpec("dense", p + "ffn.", {"width": width, "inner": 2 * width + 8,
+                                                               "activation": "gelu_tanh", "up": "up", "down": "down",
+                                                               "stored": "out_in", "init_std": 0.08, "down_init_std": 0.08})))
+    return ModelSpec(width=width, vocab_size=vocab, token_table="embed.weight",
+                     position=PartSpec("learned_absolute", "pos.", {"width": width, "n_positions": n_pos}),
+                     layers=tuple(layers), schedule=tuple(Application(*a) for a in schedule),
+                     final_norm=PartSpec("layernorm", "norm.", {"width": width, "eps": eps}), head="head.weight",
+                     table_init_std=0.3)
+
+
+def toy_plain(spec, mixers, w, ids):
+    """The toy model on a whole sequence, from the plain implementation's functions."""
+    x = plain_gpt2.position_embedding(plain_gpt2.token_embedding(w["embed.weight"], ids), w["pos.weight"])
+    kv = {}
+    for a, app in enumerate(spec.schedule):
+        i, m, p = app.layer, mixers[app.layer], f"layers.{app.layer}."
+        eps = spec.layers[i].norm1.params["eps"]
+        h = plain_gpt2.layer_norm(x, w[p + "n1.weight"], w[p + "n1.bias"], eps)
+        if m[0] == "attn":
+            _, heads, kvh, hd, window = m
+            qkv = plain_gpt2.linear(h, w[p + "attn.qkv.weight"], w[p + "attn.qkv.bias"])
+            q, k, v = plain_gpt2.split_qkv(qkv, heads, kvh, hd)
+            kv[a] = (k, v)
+            if app.cache_of is not None:
+                k, v = kv[app.cache_of]
+            att = plain_gpt2.attention(q, k, v, heads, kvh, hd, 1 / math.sqrt(hd), window)
+            x = x + plain_gpt2.linear(att, w[p + "attn.o.weight"], w[p + "attn.o.bias"])
+        else:
+            u = h @ w[p + "decay.mix.weight"].T
+            s = np.full(x.shape[1], 0.25)
+            out = np.zeros_like(u)
+            for t in range(len(ids)):
+                s = m[1] * s + u[t]
+                out[t] = s
+            x = x + out
+        h = plain_gpt2.layer_norm(x, w[p + "n2.weight"], w[p + "n2.bias"], eps)
+        x = x + plain_gpt2.mlp(h, w[p + "ffn.up.weight"], w[p + "ffn.up.bias"], w[p + "ffn.down.weight"],
+                               w[p + "ffn.down.bias"], "tanh")
+    h = plain_gpt2.layer_norm(x, w["norm.weight"], w["norm.bias"], spec.final_norm.params["eps"])
+    return h @ w["head.weight"].T
+
+
+TOYS = {
+    # grouped heads; a window layer beside full ones (two cache groups); layer 0 runs twice
+    "groups_window_twice": (dict(width=80, vocab=300, n_pos=200),
+                            [("attn", 10, 2, 16, 0), ("attn", 5, 5, 16, 24), ("attn", 4, 1, 32, 0)],
+                            [(0,), (1,), (0,), (2,)]),
+    # the last entry runs layer 1 again and reads the cache that entry 1 wrote
+    "shared_cache": (dict(width=64, vocab=200, n_pos=160), [("attn", 4, 4, 16, 0), ("attn", 2, 2, 32, 0)],
+                     [(0,), (1,), (0,), (1, 1)]),
+    # a mixer with state of its own between attention layers, and run twice
+    "state_of_its_own": (dict(width=48, vocab=150, n_pos=160), [("attn", 3, 3, 16, 0), ("decay", 0.8), ("attn", 3, 1, 16, 10)],
+                         [(0,), (1,), (2,), (1,)]),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("toy", list(TOYS))
+def test_toy_models_step_like_whole_sequences(ops, dtype, toy):
+    register_part("mixer", "toy_decay", ToyDecay)            # a part of the test's own
+    sizes, mixers, schedule = TOYS[toy]
+    spec = toy_spec(sizes["width"], sizes["vocab"], sizes["n_pos"], mixers, schedule)
+    tensors = random_tensors(DecoderModel(spec).weight_specs(), 3, torch.bfloat16)
+    w = {k: f64(v) for k, v in tensors.items()}
+    eng = Engine.from_spec(spec, tensors, dtype=dtype, max_tokens=1024, ops=ops)
+    assert eng.cuda_graphs == (toy != "state_of_its_own")
+    if toy == "groups_window_twice":
+        assert len(eng.cache.groups) == 3 and sorted(len(g.apps) for g in eng.cache.groups) == [1, 1, 2]
+    if toy == "shared_cache":
+        assert eng.cache.views[3] is eng.cache.views[1] and not eng.apps[3].writes_cache
+    if toy == "state_of_its_own":
+        assert eng.apps[1].state is not None and eng.apps[3].state is not None
+        assert eng.apps[1].state.data_ptr() != eng.apps[3].state.data_ptr()
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    seqs = [random_ids(i, sizes["vocab"], n) for i, n in enumerate((150, 33, 70))]
+    for batch in ((40, 1, 70), (100, 20, 5)):                 # the second batch reuses slots and state rows
+        rows, _ = run_batch(eng, seqs, batch)
+        for ids, got in zip(seqs, rows):
+            assert rel_error(got, toy_plain(spec, mixers, w, ids)) < tol
+        eng.cache.check()
+        assert eng.cache.slots.held == 0
+        assert all(g.pages.free == g.pages.size for g in eng.cache.groups)
