@@ -1,0 +1,208 @@
+// Decode attention over the paged cache in bfloat16: one new token per sequence, the keys of a
+// sequence split into chunks of pages that separate blocks work through, and the partial results
+// merged.
+//
+// ember.cpp's decode attention is split-K too: a block per (head, chunk) scores its keys, takes
+// the chunk's softmax and weighted value sum and writes (m, l, acc[head_dim]) to a scratch array;
+// a second kernel merges the chunks in a fixed order,
+// out = sum_c e^(m_c - M) acc_c / sum_c e^(m_c - M) l_c (decode_attn_tiled.cuh:58-185,
+// cuda_kernels.cu:3117-3134).  This kernel is built for a batch of sequences of unequal length in
+// pages and for streaming HBM: grid (chunk, head, token); 128 threads form 16 to 64 independent
+// key streams (a key is read by hd/8 lanes, 16 bytes each, K and V in the same pass with an
+// online softmax per stream), the streams are merged in shared memory, and the block that
+// finishes a (token, head) last merges its chunks, so there is no second launch.  A chunk that
+// lies past the token's position or before its window does nothing.
+//
+// Scratch (given by the caller, reused by every call): per (token, head, chunk) m, l and
+// acc[head_dim] in float32, and one counter per (token, head) that is zero between calls.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 128;
+
+__device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 v = __bfloat1622float2(h[i]);
+    f[2 * i] = v.x;
+    f[2 * i + 1] = v.y;
+  }
+}
+
+template <int LPK>  // lanes per key; each lane owns 8 consecutive dims
+__global__ void __launch_bounds__(kThreads)
+attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ kc,
+                        const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
+                        float* __restrict__ part_ml, float* __restrict__ part_acc, int* __restrict__ counters,
+                        const int* __restrict__ positions, const int* __restrict__ token_seq,
+                        const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks, int n_heads,
+                        int kv_heads, int hd, float scale, int window, int pages_per_chunk, int n_chunks) {
+  constexpr int kGroups = 32 / LPK;           // key streams per warp
+  constexpr int kStreams = 4 * kGroups;       // per block
+  __shared__ float s_m[kStreams], s_l[kStreams];
+  __shared__ float s_acc[kStreams][LPK * 8 + 1];
+  __shared__ float s_w[kStreams];
+  __shared__ int s_last;
+
+  const int c = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
+  const int s = token_seq[t];
+  __nv_bfloat16* o = out + ((size_t)t * n_heads + h) * hd;
+  if (seq_slot[s] < 0) {  // padding: a defined output, nothing read
+    if (c == 0)
+      for (int d = threadIdx.x; d < hd; d += kThreads) o[d] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int p = positions[t];
+  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int chunk_keys = pages_per_chunk * kPage;
+  const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
+  if (c < first_chunk || c > last_chunk) return;
+  const int begin = max(lo, c * chunk_keys), end = min(p + 1, (c + 1) * chunk_keys);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sid = warp * kGroups + lane / LPK, sub = lane % LPK;
+  const bool dims = sub * 8 < hd;
+  const int g = h / (n_heads / kv_heads);
+  const int qkv_width = (n_heads + 2 * kv_heads) * hd;
+  const int* my_pages = pages + (size_t)s * max_blocks;
+
+  float q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = 0.f;
+  if (dims) unpack8(*reinterpret_cast<const uint4*>(qkv + (size_t)t * qkv_width + (size_t)h * hd + sub * 8), q);
+
+  float m = -INFINITY, l = 0.f, acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+
+  // every lane of a warp makes the same number of trips (the shuffles below name all 32 lanes)
+  for (int j0 = begin; j0 < end; j0 += kStreams) {
+    const int j = j0 + sid;
+    const int page = j < end ? my_pages[j / kPage] : -1;
+    const size_t row = (((size_t)max(page, 0) * kv_heads + g) * kPage + (j % kPage)) * hd + sub * 8;
+    float k[8], v[8];
+    uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
+    if (dims && page >= 0) {
+      kraw = *reinterpret_cast<const uint4*>(kc + row);
+      vraw = *reinterpret_cast<const uint4*>(vc + row);
+    }
+    unpack8(kraw, k);
+    unpack8(vraw, v);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dot = fmaf(q[i], k[i], dot);
+#pragma unroll
+    for (int off = LPK / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+    const float sc = page >= 0 ? dot * scale : -INFINITY;
+    const float m_new = fmaxf(m, sc);
+    const float corr = m_new == -INFINITY ? 0.f : __expf(m - m_new);
+    const float pj = m_new == -INFINITY ? 0.f : __expf(sc - m_new);
+    l = l * corr + pj;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(pj, v[i], acc[i] * corr);
+    m = m_new;
+  }
+
+  // merge the block's streams
+  if (sub == 0) {
+    s_m[sid] = m;
+    s_l[sid] = l;
+  }
+  if (dims) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_acc[sid][sub * 8 + i] = acc[i];
+  }
+  __syncthreads();
+  float M = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kStreams; ++i) M = fmaxf(M, s_m[i]);
+  if (threadIdx.x < kStreams) s_w[threadIdx.x] = s_m[threadIdx.x] == -INFINITY ? 0.f : __expf(s_m[threadIdx.x] - M);
+  __syncthreads();
+  float L = 0.f;
+#pragma unroll
+  for (int i = 0; i < kStreams; ++i) L += s_l[i] * s_w[i];
+  const int n_valid = last_chunk - first_chunk + 1;
+  const size_t item = ((size_t)t * n_heads + h) * n_chunks;
+  for (int d = threadIdx.x; d < hd; d += kThreads) {
+    float A = 0.f;
+#pragma unroll
+    for (int i = 0; i < kStreams; ++i) A += s_acc[i][d] * s_w[i];
+    if (n_valid == 1)
+      o[d] = __float2bfloat16_rn(A / L);
+    else
+      part_acc[(item + c) * hd + d] = A;
+  }
+  if (n_valid == 1) return;
+  if (threadIdx.x == 0) {
+    part_ml[(item + c) * 2] = M;
+    part_ml[(item + c) * 2 + 1] = L;
+  }
+
+  // the block that finishes this (token, head) last merges its chunks
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int done = atomicAdd(&counters[t * n_heads + h], 1);
+    s_last = done == n_valid - 1;
+    if (s_last) counters[t * n_heads + h] = 0;  // zero again for the next call
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  float MM = -INFINITY;
+  for (int cc = first_chunk; cc <= last_chunk; ++cc) MM = fmaxf(MM, __ldcg(&part_ml[(item + cc) * 2]));
+  float LL = 0.f;
+  for (int cc = first_chunk; cc <= last_chunk; ++cc)
+    LL += __ldcg(&part_ml[(item + cc) * 2 + 1]) * __expf(__ldcg(&part_ml[(item + cc) * 2]) - MM);
+  for (int d = threadIdx.x; d < hd; d += kThreads) {
+    float A = 0.f;
+    for (int cc = first_chunk; cc <= last_chunk; ++cc)
+      A += __ldcg(&part_acc[(item + cc) * hd + d]) * __expf(__ldcg(&part_ml[(item + cc) * 2]) - MM);
+    o[d] = __float2bfloat16_rn(A / LL);
+  }
+}
+
+}  // namespace
+
+// Bytes of scratch a call needs: partials for every (token, head, chunk) and a counter per (token, head).
+EMBER_API size_t ember_attention_decode_scratch(int T, int n_heads, int hd, int n_chunks) {
+  const size_t items = (size_t)T * n_heads;
+  return items * n_chunks * (hd + 2) * sizeof(float) + items * sizeof(int);
+}
+
+// scratch: ember_attention_decode_scratch(...) bytes, 16-byte aligned; its counters (the last
+// T * n_heads ints) must be zero before the first call and are left zero by every call.
+EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void* vc, void* out, void* scratch,
+                                     const int* positions, const int* token_seq, const int* seq_slot, const int* pages,
+                                     int max_blocks, int T, int n_heads, int kv_heads, int hd, float scale, int window,
+                                     int pages_per_chunk, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention_decode: bad sizes");
+  EMBER_CHECK(n_heads % kv_heads == 0, "attention_decode: %d heads are not a multiple of %d key/value heads", n_heads,
+              kv_heads);
+  EMBER_CHECK(hd % 16 == 0 && hd >= 16 && hd <= 256, "attention_decode: head size %d is not a multiple of 16 in [16, 256]",
+              hd);
+  EMBER_CHECK(window >= 0 && pages_per_chunk > 0, "attention_decode: window %d, pages per chunk %d", window,
+              pages_per_chunk);
+  EMBER_CHECK(T <= 65535 && n_heads <= 65535, "attention_decode: %d tokens x %d heads exceed one launch", T, n_heads);
+  const int n_chunks = (max_blocks + pages_per_chunk - 1) / pages_per_chunk;
+  const size_t items = (size_t)T * n_heads;
+  float* part_ml = (float*)scratch;
+  float* part_acc = part_ml + items * n_chunks * 2;
+  int* counters = (int*)(part_acc + items * n_chunks * hd);
+  dim3 grid(n_chunks, n_heads, T);
+#define EMBER_DECODE(LPK)                                                                                            \
+  attention_decode_kernel<LPK><<<grid, kThreads, 0, stream>>>(                                                       \
+      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_ml,   \
+      part_acc, counters, positions, token_seq, seq_slot, pages, max_blocks, n_heads, kv_heads, hd, scale, window,  \
+      pages_per_chunk, n_chunks)
+  if (hd <= 16) EMBER_DECODE(2);
+  else if (hd <= 32) EMBER_DECODE(4);
+  else if (hd <= 64) EMBER_DECODE(8);
+  else if (hd <= 128) EMBER_DECODE(16);
+  else EMBER_DECODE(32);
+#undef EMBER_DECODE
+  EMBER_LAUNCH_OK("attention_decode");
+  return 0;
+}
