@@ -161,7 +161,7 @@ def main() -> int:
     tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=0, dtype=torch.bfloat16, device="cuda")
     log(f"random weights: {sum(t.numel() for t in tensors.values()) / 1e9:.3f} G parameters in {time.time() - t0:.1f} s")
     biggest = max(args.batch, 1 if args.no_points else 64)
-    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=biggest * ctx)
+    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=max(biggest, PREFILL[0]) * ctx)
     engine.config = cfg
     del tensors
     sampler = E.Sampler(engine.ops)

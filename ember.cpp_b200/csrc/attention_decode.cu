@@ -15,6 +15,8 @@
 //
 // Scratch (given by the caller, reused by every call): per (token, head, chunk) m, l and
 // acc[head_dim] in float32, and one counter per (token, head) that is zero between calls.
+// The grid covers the pages a sequence can hold at most, so a captured graph serves every length
+// up to that.
 #include "common.cuh"
 
 namespace {
@@ -166,19 +168,23 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
 
 }  // namespace
 
-// Bytes of scratch a call needs: partials for every (token, head, chunk) and a counter per (token, head).
-EMBER_API size_t ember_attention_decode_scratch(int T, int n_heads, int hd, int n_chunks) {
-  const size_t items = (size_t)T * n_heads;
-  return items * n_chunks * (hd + 2) * sizeof(float) + items * sizeof(int);
+// Floats of partial results a call needs: (m, l, acc[hd]) for every (token, head, chunk).
+EMBER_API size_t ember_attention_decode_partials(int T, int n_heads, int hd, int n_blocks, int pages_per_chunk) {
+  const size_t n_chunks = (size_t)((n_blocks + pages_per_chunk - 1) / pages_per_chunk);
+  return (size_t)T * n_heads * n_chunks * (hd + 2);
 }
 
-// scratch: ember_attention_decode_scratch(...) bytes, 16-byte aligned; its counters (the last
-// T * n_heads ints) must be zero before the first call and are left zero by every call.
-EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void* vc, void* out, void* scratch,
-                                     const int* positions, const int* token_seq, const int* seq_slot, const int* pages,
-                                     int max_blocks, int T, int n_heads, int kv_heads, int hd, float scale, int window,
-                                     int pages_per_chunk, cudaStream_t stream) {
-  EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention_decode: bad sizes");
+// max_blocks: entries per sequence in `pages`.  n_blocks <= max_blocks: the pages that the
+// longest sequence of this call can hold; the grid has a chunk for each pages_per_chunk of them.
+// partials: ember_attention_decode_partials(...) floats of scratch, contents irrelevant.
+// counters: T * n_heads ints of scratch that are zero before the first call; every call leaves
+// them zero.  Calls that share scratch must not overlap on the device.
+EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void* vc, void* out, float* partials,
+                                     int* counters, const int* positions, const int* token_seq, const int* seq_slot,
+                                     const int* pages, int max_blocks, int n_blocks, int T, int n_heads, int kv_heads,
+                                     int hd, float scale, int window, int pages_per_chunk, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0 && n_blocks > 0 && n_blocks <= max_blocks,
+              "attention_decode: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_decode: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
   EMBER_CHECK(hd % 16 == 0 && hd >= 16 && hd <= 256, "attention_decode: head size %d is not a multiple of 16 in [16, 256]",
@@ -186,11 +192,10 @@ EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void
   EMBER_CHECK(window >= 0 && pages_per_chunk > 0, "attention_decode: window %d, pages per chunk %d", window,
               pages_per_chunk);
   EMBER_CHECK(T <= 65535 && n_heads <= 65535, "attention_decode: %d tokens x %d heads exceed one launch", T, n_heads);
-  const int n_chunks = (max_blocks + pages_per_chunk - 1) / pages_per_chunk;
+  const int n_chunks = (n_blocks + pages_per_chunk - 1) / pages_per_chunk;
   const size_t items = (size_t)T * n_heads;
-  float* part_ml = (float*)scratch;
+  float* part_ml = partials;
   float* part_acc = part_ml + items * n_chunks * 2;
-  int* counters = (int*)(part_acc + items * n_chunks * hd);
   dim3 grid(n_chunks, n_heads, T);
 #define EMBER_DECODE(LPK)                                                                                            \
   attention_decode_kernel<LPK><<<grid, kThreads, 0, stream>>>(                                                       \

@@ -13,11 +13,14 @@
 // page pages[seq][j / 64] at row j % 64.
 #include "common.cuh"
 
+// One block per token; 16 bytes (4 float32 or 8 bfloat16 values, never across a head since head
+// sizes are multiples of 16) per thread and trip, all of a thread's loads before its stores.
 template <typename T>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                                 const int* __restrict__ positions, const int* __restrict__ token_seq,
                                 const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks,
                                 int q_width, int kv_heads, int hd) {
+  constexpr int kVec = 16 / (int)sizeof(T);
   const int t = blockIdx.x;
   const int s = token_seq[t];
   if (seq_slot[s] < 0) return;
@@ -26,11 +29,13 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T
   if (page < 0) return;
   const int kv_width = kv_heads * hd;
   const T* src = qkv + (size_t)t * (q_width + 2 * kv_width) + q_width;
-  for (int i = threadIdx.x; i < kv_width; i += blockDim.x) {
+  for (int i = threadIdx.x * kVec; i < kv_width; i += blockDim.x * kVec) {
     const int h = i / hd, d = i % hd;
     const size_t dst = (((size_t)page * kv_heads + h) * kPage + (p % kPage)) * hd + d;
-    kc[dst] = src[i];
-    vc[dst] = src[kv_width + i];
+    const uint4 k = *reinterpret_cast<const uint4*>(src + i);
+    const uint4 v = *reinterpret_cast<const uint4*>(src + kv_width + i);
+    *reinterpret_cast<uint4*>(kc + dst) = k;
+    *reinterpret_cast<uint4*>(vc + dst) = v;
   }
 }
 
@@ -38,6 +43,7 @@ EMBER_API int ember_kv_store(const void* qkv, void* kc, void* vc, const int* pos
                              const int* seq_slot, const int* pages, int max_blocks, int T, int n_heads, int kv_heads,
                              int hd, int dtype, cudaStream_t stream) {
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && hd > 0 && max_blocks > 0, "kv_store: bad sizes");
+  EMBER_CHECK(hd % 16 == 0, "kv_store: head size %d is not a multiple of 16", hd);
   const int qw = n_heads * hd;
   if (dtype == EMBER_F32)
     kv_store_kernel<float><<<T, 128, 0, stream>>>((const float*)qkv, (float*)kc, (float*)vc, positions, token_seq,

@@ -272,6 +272,7 @@ EMBER_API int ember_attention_prefill(const void* qkv, const void* kc, const voi
   EMBER_CHECK(n_seqs <= 65535 && n_heads <= 65535, "attention_prefill: %d sequences x %d heads exceed one launch", n_seqs,
               n_heads);
   EMBER_CHECK(window >= 0, "attention_prefill: window %d", window);
+  EMBER_CHECK(scale > 0.f, "attention_prefill: scale %g is not positive", (double)scale);
 #define EMBER_PREFILL(HD)                                                                                           \
   case HD:                                                                                                          \
     return launch<HD>(qkv, kc, vc, out, seq_slot, seq_start, seq_new, cu_new, pages, max_blocks, n_seqs, max_new,   \

@@ -50,7 +50,24 @@ EMBER_API int ember_embed(const int* tokens, const int* positions, const void* t
 }
 
 // ---------------------------------------------------------------------------- layer norm
-// One warp per row.  Two passes for mean and biased variance, a third to write.
+// One warp per row.  Two passes for mean and biased variance, a third to write.  A row of up to
+// 2048 values is read once and held in registers (float4 per lane), so that its loads are in
+// flight together; longer or oddly sized rows are read three times.
+constexpr int kRowVecs = 16;
+
+template <typename OutT>
+__device__ __forceinline__ void store4(OutT* dst, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(dst);
+  d2[0] = __floats2bfloat162_rn(a, b);
+  d2[1] = __floats2bfloat162_rn(c, d);
+}
+
 template <typename OutT>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                                  OutT* __restrict__ out, int rows, int d, float eps) {
@@ -58,6 +75,39 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const float* r = x + (size_t)row * d;
+  OutT* o = out + (size_t)row * d;
+  if ((d & 3) == 0 && d <= 128 * kRowVecs) {
+    const int nv = d >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(r);
+    float4 v[kRowVecs];
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowVecs; ++j) {
+      const int i = lane + 32 * j;
+      v[j] = i < nv ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+    }
+    const float mean = warp_sum(s) / (float)d;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRowVecs; ++j) {
+      if (lane + 32 * j < nv) {
+        const float a0 = v[j].x - mean, a1 = v[j].y - mean, a2 = v[j].z - mean, a3 = v[j].w - mean;
+        q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+      }
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)d + eps);
+#pragma unroll
+    for (int j = 0; j < kRowVecs; ++j) {
+      const int i = lane + 32 * j;
+      if (i < nv) {
+        const float4 gm = reinterpret_cast<const float4*>(w)[i], bt = reinterpret_cast<const float4*>(b)[i];
+        store4<OutT>(o + 4 * i, (v[j].x - mean) * inv * gm.x + bt.x, (v[j].y - mean) * inv * gm.y + bt.y,
+                     (v[j].z - mean) * inv * gm.z + bt.z, (v[j].w - mean) * inv * gm.w + bt.w);
+      }
+    }
+    return;
+  }
   float s = 0.f;
   for (int i = lane; i < d; i += 32) s += r[i];
   const float mean = warp_sum(s) / (float)d;
@@ -68,7 +118,6 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
   }
   const float var = warp_sum(q) / (float)d;
   const float inv = 1.0f / sqrtf(var + eps);
-  OutT* o = out + (size_t)row * d;
   for (int i = lane; i < d; i += 32) o[i] = from_float<OutT>((r[i] - mean) * inv * w[i] + b[i]);
 }
 

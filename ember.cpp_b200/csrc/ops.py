@@ -31,16 +31,37 @@ _SIGNATURES = {
     "ember_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_bf16": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_void, _c_size, _c_void],
+    "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
+                            _c_int, _c_int, _c_void],
     "ember_kv_store": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_void],
     "ember_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
                               _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
+    "ember_attention_decode": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
+    "ember_attention_prefill": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
+                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_void],
 }
 
 
 class KernelError(RuntimeError):
     pass
+
+
+SMALL_M = 16          # rows up to which the weight-streaming product is used instead of the library's
+
+
+class LazyNorm:
+    """A layer norm that has not run yet: the next linear layer applies it in its own prologue.
+    Only `CudaOps.linear` takes one; `materialize()` gives the tensor."""
+
+    def __init__(self, ops, x, w, b, eps, out_dtype):
+        self.ops, self.x, self.w, self.b, self.eps, self.dtype = ops, x, w, b, eps, out_dtype
+        self.shape = x.shape
+
+    def materialize(self):
+        return self.ops.layernorm(self.x, self.w, self.b, self.eps, self.dtype)
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -76,14 +97,30 @@ class CudaOps:
         self.lib = load_library()
         self._workspace = None
         self._bias16: dict[int, torch.Tensor] = {}
+        self._partials = None          # scratch of the decode attention: partial results ...
+        self._counters = None          # ... and its per-(token, head) counters, zero between calls
+        self._retired = []             # outgrown scratch stays alive: captured graphs may still name it
         self.launches = 0
+        self.decode_ctas = 6000        # blocks the decode attention aims for (about four waves of 148 SMs x 10)
 
     # ------------------------------------------------------------------ helpers
-    def _call(self, name: str, *args) -> None:
+    def _call(self, name: str, *args, allow=()) -> int:
         rc = getattr(self.lib, name)(*args, torch.cuda.current_stream().cuda_stream)
+        if rc in allow:
+            return rc
         self.launches += 1
         if rc != 0:
             raise KernelError(self.lib.ember_last_error().decode())
+        return 0
+
+    def _decode_scratch(self, n_partials: int, n_counters: int):
+        if self._partials is None or self._partials.numel() < n_partials:
+            self._retired.append(self._partials)
+            self._partials = torch.empty(max(n_partials, 1 << 20), dtype=torch.float32, device="cuda")
+        if self._counters is None or self._counters.numel() < n_counters:
+            self._retired.append(self._counters)
+            self._counters = torch.zeros(max(n_counters, 1 << 16), dtype=torch.int32, device="cuda")
+        return self._partials, self._counters
 
     @staticmethod
     def _ptr(t):
@@ -117,8 +154,14 @@ class CudaOps:
                    self._ptr(pos_table), x.data_ptr(), T, d, _code(table.dtype))
         return x
 
-    def layernorm(self, x, w, b, eps, out_dtype):
+    def layernorm(self, x, w, b, eps, out_dtype, lazy=False):
+        """Layer norm of float32 rows.  With `lazy` the caller promises to hand the result to
+        `linear` and nothing else; for a few rows in bfloat16 the norm then runs inside that
+        product's kernel and a LazyNorm is returned in place of a tensor."""
         rows, d = x.shape
+        if (lazy and out_dtype == torch.bfloat16 and rows <= SMALL_M and d % 8 == 0 and d <= 8192
+                and x.dtype == torch.float32 and x.is_contiguous()):
+            return LazyNorm(self, x, w, b, eps, out_dtype)
         if x.dtype != torch.float32 or w.dtype != torch.float32 or b.dtype != torch.float32:
             raise KernelError("layernorm: input, gain and bias are float32")
         if w.shape[0] != d or b.shape[0] != d:
@@ -140,11 +183,17 @@ class CudaOps:
         sum is made in float32 into the residual's buffer, which is returned."""
         if act not in _ACT:
             raise KernelError(f"linear: activation {act!r}")
+        norm = None
+        if isinstance(a, LazyNorm):
+            if w.dtype == torch.bfloat16:
+                norm, a = a, a.x
+            else:
+                a = a.materialize()
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K:
             raise KernelError(f"linear: input width {K} does not match the weight's {tuple(w.shape)}")
-        if a.dtype != w.dtype:
+        if norm is None and a.dtype != w.dtype:
             raise KernelError(f"linear: input is {a.dtype}, weight is {w.dtype}")
         if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != N):
             raise KernelError("linear: the bias is float32 of the output's width")
@@ -159,6 +208,14 @@ class CudaOps:
             return out if out_dtype in (None, torch.float32) or residual is not None else out.to(out_dtype)
         target = torch.float32 if residual is not None else (out_dtype or torch.bfloat16)
         out = residual if residual is not None else torch.empty((M, N), dtype=target, device=a.device)
+        if M <= SMALL_M and K % 8 == 0:
+            self._call("ember_linear_decode", a.data_ptr(), None if norm is None else norm.w.data_ptr(),
+                       None if norm is None else norm.b.data_ptr(), 0.0 if norm is None else float(norm.eps),
+                       w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(), M, N, K, _ACT[act],
+                       _code(target))
+            return out
+        if norm is not None:
+            a = norm.materialize()
         fused = _ACT[act] if act != "gelu_erf" else 0
         ws = self._lt_workspace()
         self._call("ember_linear_bf16", a.data_ptr(), w.data_ptr(), self._ptr(bias),
@@ -178,12 +235,35 @@ class CudaOps:
                    _code(qkv.dtype))
 
     def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype):
+        """Causal attention of the step's tokens over the cache (their own keys already stored).
+        float32: the plain kernel, whose sums depend on positions alone.  bfloat16: one token per
+        sequence takes the split decode kernel; anything else the tensor-core prefill kernel, or
+        the plain kernel for head sizes that one has no instantiation for."""
         if qkv.dtype != cache.k.dtype or out_dtype != qkv.dtype:
             raise KernelError("attention: activations, cache and output have one element type")
+        self._dense(qkv, "qkv")
         out = torch.empty((plan.T, n_heads * head_dim), dtype=out_dtype, device=qkv.device)
-        self._call("ember_attention_plain", self._dense(qkv, "qkv").data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+        pages = plan.pages[cache.group_index]
+        if qkv.dtype == torch.bfloat16 and plan.all_single:
+            blocks = min(plan.max_blocks, max(1, -(-plan.max_end // 64)))
+            per_chunk = max(1, min(blocks, plan.T * n_heads * blocks // self.decode_ctas))
+            n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
+            partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
+            self._call("ember_attention_decode", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
+                       partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(),
+                       plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, blocks, plan.T, n_heads, kv_heads,
+                       head_dim, float(scale), int(window), per_chunk)
+            return out
+        if qkv.dtype == torch.bfloat16 and scale > 0:
+            rc = self._call("ember_attention_prefill", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                            out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),
+                            plan.cu_new.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.n, plan.max_new, n_heads,
+                            kv_heads, head_dim, float(scale), int(window), allow=(2,))
+            if rc == 0:
+                return out
+        self._call("ember_attention_plain", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                    out.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(),
-                   plan.pages[cache.group_index].data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, head_dim,
+                   pages.data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, head_dim,
                    float(scale), int(window), _code(qkv.dtype))
         return out
 

@@ -64,6 +64,7 @@ class HostStep:
     max_end: int                  # longest sequence after the step
     all_from_zero: bool           # every real sequence starts at position 0
     all_single: bool              # every sequence brings one token
+    wants_every_row: bool = False # the wanted rows are all rows, in order
 
 
 def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, want_all: bool = False) -> HostStep:
@@ -112,7 +113,8 @@ def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, 
     buf[lay.cu_new + n] = t0
     for g, table in enumerate(page_tables):
         buf[lay.pages[g]: lay.pages[g] + n * max_blocks] = table(slots, max_blocks).reshape(-1)
-    return HostStep(lay, buf, T, n, R, max_new, max_end, from_zero, single)
+    every = R == T and bool((buf[lay.want_rows:lay.want_rows + R] == np.arange(T)).all())
+    return HostStep(lay, buf, T, n, R, max_new, max_end, from_zero, single, every)
 
 
 class StepPlan:
@@ -125,6 +127,7 @@ class StepPlan:
         self.T, self.n, self.n_want = host.T, host.n, host.n_want
         self.max_new, self.max_end, self.max_blocks = host.max_new, host.max_end, lay.max_blocks
         self.all_from_zero, self.all_single = host.all_from_zero, host.all_single
+        self.wants_every_row = host.wants_every_row
 
         def view(start, count):
             return device_buffer[start:start + count]

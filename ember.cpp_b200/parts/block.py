@@ -12,9 +12,9 @@ from .base import Block, register_part
 
 class PreNormBlock(Block):
     def forward(self, ctx, x, app):
-        h = self.norm1.forward(ctx, x, ctx.dtype)
+        h = self.norm1.forward(ctx, x, ctx.dtype, lazy=self.mixer.takes_lazy_norm)
         x = self.mixer.forward(ctx, h, x, app)
-        h = self.norm2.forward(ctx, x, ctx.dtype)
+        h = self.norm2.forward(ctx, x, ctx.dtype, lazy=self.ffn.takes_lazy_norm)
         return self.ffn.forward(ctx, h, x)
 
 

@@ -80,6 +80,6 @@ class DecoderModel:
             x = self.blocks[app.layer].forward(ctx, x, app)
         if plan.n_want == 0:
             return None
-        rows = ops.gather_rows(x, plan.want_rows, plan.n_want)
-        h = self.final_norm.forward(ctx, rows, ctx.dtype)
+        rows = x if plan.wants_every_row else ops.gather_rows(x, plan.want_rows, plan.n_want)
+        h = self.final_norm.forward(ctx, rows, ctx.dtype, lazy=True)
         return ops.linear(h, self.head, None, out_dtype=torch.float32)

@@ -26,8 +26,10 @@ class LayerNorm(Norm):
         self.w = runtime.vector(get(self.weight_name))
         self.b = runtime.vector(get(self.bias_name))
 
-    def forward(self, ctx, x, out_dtype):
-        return ctx.ops.layernorm(x, self.w, self.b, self.eps, out_dtype)
+    def forward(self, ctx, x, out_dtype, lazy=False):
+        """`lazy`: the caller hands the result to `ops.linear` only, which may then run the norm in
+        its own kernel (the value is the same)."""
+        return ctx.ops.layernorm(x, self.w, self.b, self.eps, out_dtype, lazy=lazy)
 
 
 register_part("norm", "layernorm", LayerNorm)

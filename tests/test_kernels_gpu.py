@@ -102,6 +102,46 @@ def test_linear(ops, dtype, M, N, K, act, with_bias, with_res):
     assert (got.double() - want).abs().max().item() / scale < tol
 
 
+@pytest.mark.parametrize("M, N, K", [(1, 1600, 1600), (8, 100, 40), (9, 50, 72), (16, 4800, 1600), (3, 17, 104),
+                                     (16, 1600, 6400), (2, 50257, 96)])
+@pytest.mark.parametrize("act, with_bias, with_res, out", [(None, True, False, "bfloat16"), ("gelu_tanh", True, False, "bfloat16"),
+                                                           ("gelu_erf", False, False, "bfloat16"), (None, True, True, "float32"),
+                                                           (None, False, False, "float32")])
+def test_linear_few_rows_streams_the_weights(ops, M, N, K, act, with_bias, with_res, out):
+    """Up to 16 rows take the weight-streaming kernel (tensor cores with the operands swapped):
+    every tile shape, tails in N and K, both batch tiles."""
+    a, w = gen((M, K), 30, torch.bfloat16), gen((N, K), 31, torch.bfloat16, 0.1)
+    bias = gen((N,), 32) if with_bias else None
+    res = gen((M, N), 33) if with_res else None
+    want = linear_ref(a, w, bias, act, res)
+    got = ops.linear(a, w, bias, act=act, residual=None if res is None else res.clone(), out_dtype=DT[out])
+    assert got.dtype == DT[out]
+    scale = want.abs().max().item() + 1e-6
+    assert (got.double() - want).abs().max().item() / scale < (2e-4 if out == "float32" else 2 ** -7)
+
+
+@pytest.mark.parametrize("M, N, K", [(1, 4800, 1600), (7, 100, 96), (16, 1000, 64), (11, 320, 2056), (4, 64, 4104)])
+def test_linear_with_the_norm_in_its_prologue(ops, M, N, K):
+    """The layer norm run inside the product's kernel gives what the separate kernel gives."""
+    from ember_cpp_b200.csrc.ops import LazyNorm
+    x = gen((M, K), 34) * 2 + 0.5
+    gw, gb = gen((K,), 35) * 0.1 + 1, gen((K,), 36) * 0.1
+    w, bias = gen((N, K), 37, torch.bfloat16, 0.1), gen((N,), 38)
+    lazy = ops.layernorm(x, gw, gb, 1e-5, torch.bfloat16, lazy=True)
+    assert isinstance(lazy, LazyNorm)
+    fused = ops.linear(lazy, w, bias, act="gelu_tanh", out_dtype=torch.bfloat16)
+    h = ops.layernorm(x, gw, gb, 1e-5, torch.bfloat16)
+    apart = ops.linear(h, w, bias, act="gelu_tanh", out_dtype=torch.bfloat16)
+    want = linear_ref(h, w, bias, "gelu_tanh", None)
+    scale = want.abs().max().item()
+    assert (fused.double() - want).abs().max().item() / scale < 2 ** -7
+    assert (fused.double() - apart.double()).abs().max().item() / scale < 2 ** -7
+    assert torch.equal(lazy.materialize(), h)
+    # more rows than the streaming kernel takes: the norm runs on its own
+    assert torch.is_tensor(ops.layernorm(gen((17, K), 39), gw, gb, 1e-5, torch.bfloat16, lazy=True))
+    assert torch.is_tensor(ops.layernorm(x, gw, gb, 1e-5, torch.float32, lazy=True))
+
+
 def test_linear_float32_rows_do_not_depend_on_the_batch(ops):
     """The 32-bit product adds each output element in one fixed order: a row computed alone is
     bit-identical to the same row of a large batch."""
@@ -198,7 +238,7 @@ def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poiso
 @pytest.mark.parametrize("heads, kv_heads, hd", [(4, 4, 16), (25, 25, 64), (6, 2, 32), (3, 1, 80), (2, 2, 128),
                                                  (5, 5, 256), (8, 4, 48)])
 def test_attention_prompts_of_unequal_length(ops, dtype, heads, kv_heads, hd):
-    got, want = run_attention(ops, [(0, 70), (0, 1), (0, 129), (0, 64)], heads, kv_heads, hd, dtype, seed=hd)
+    got, want = run_attention(ops, [(0, 70), (0, 1), (0, 129), (0, 64)], heads, kv_heads, hd, dtype, seed=hd, poison=1e30)
     assert (got - want).abs().max().item() < ATOL[dtype]
 
 
@@ -213,7 +253,7 @@ def test_attention_one_token_each_over_the_cache(ops, dtype, heads, kv_heads, hd
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_tokens_added_to_a_cache(ops, dtype):
     """More than one new token on top of cached ones: the general case of the step function."""
-    got, want = run_attention(ops, [(50, 30), (64, 64), (1, 5)], 6, 3, 32, dtype, seed=3)
+    got, want = run_attention(ops, [(50, 30), (64, 64), (1, 5), (100, 130)], 6, 3, 32, dtype, seed=3, poison=1e30)
     assert (got - want).abs().max().item() < ATOL[dtype]
 
 
