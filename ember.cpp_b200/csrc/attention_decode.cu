@@ -40,7 +40,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
                         float* __restrict__ part_ml, float* __restrict__ part_acc, int* __restrict__ counters,
                         const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks, int n_heads,
-                        int kv_heads, int hd, float scale, int window, int pages_per_chunk, int n_chunks) {
+                        int kv_heads, int hd, float scale, int window, int pages_per_chunk, int n_chunks,
+                        __nv_bfloat16* __restrict__ k_store, __nv_bfloat16* __restrict__ v_store) {
   constexpr int kGroups = 32 / LPK;           // key streams per warp
   constexpr int kStreams = 4 * kGroups;       // per block
   __shared__ float s_m[kStreams], s_l[kStreams];
@@ -48,6 +49,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   __shared__ float s_w[kStreams];
   __shared__ int s_last;
 
+  pdl_trigger();
+  pdl_wait();
   const int c = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
   const int s = token_seq[t];
   __nv_bfloat16* o = out + ((size_t)t * n_heads + h) * hd;
@@ -62,12 +65,32 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
   if (c < first_chunk || c > last_chunk) return;
   const int begin = max(lo, c * chunk_keys), end = min(p + 1, (c + 1) * chunk_keys);
+  const int kvh = h / (n_heads / kv_heads);
+  const int width = (n_heads + 2 * kv_heads) * hd;
+  if (k_store && c == last_chunk) {
+    // The token's own key and value go into the cache here (no separate launch): the block that
+    // reads position p writes it first.  Blocks of other heads of the same group write the same
+    // bytes.
+    const int page = pages[(size_t)s * max_blocks + p / kPage];
+    if (page >= 0) {
+      const size_t dst = (((size_t)page * kv_heads + kvh) * kPage + (p % kPage)) * hd;
+      const __nv_bfloat16* src = qkv + (size_t)t * width + (size_t)(n_heads + kvh) * hd;
+      const int vecs = hd / 8;
+      for (int i = threadIdx.x; i < 2 * vecs; i += kThreads) {
+        const bool is_v = i >= vecs;
+        const int j = (is_v ? i - vecs : i) * 8;
+        const uint4 val = *reinterpret_cast<const uint4*>(src + (is_v ? kv_heads * hd : 0) + j);
+        *reinterpret_cast<uint4*>((is_v ? v_store : k_store) + dst + j) = val;
+      }
+    }
+    __syncthreads();
+  }
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sid = warp * kGroups + lane / LPK, sub = lane % LPK;
   const bool dims = sub * 8 < hd;
-  const int g = h / (n_heads / kv_heads);
-  const int qkv_width = (n_heads + 2 * kv_heads) * hd;
+  const int g = kvh;
+  const int qkv_width = width;
   const int* my_pages = pages + (size_t)s * max_blocks;
 
   float q[8];
@@ -176,13 +199,15 @@ EMBER_API size_t ember_attention_decode_partials(int T, int n_heads, int hd, int
 
 // max_blocks: entries per sequence in `pages`.  n_blocks <= max_blocks: the pages that the
 // longest sequence of this call can hold; the grid has a chunk for each pages_per_chunk of them.
+// store_kv: write each token's own key and value (from qkv) into the cache before attending.
 // partials: ember_attention_decode_partials(...) floats of scratch, contents irrelevant.
 // counters: T * n_heads ints of scratch that are zero before the first call; every call leaves
 // them zero.  Calls that share scratch must not overlap on the device.
 EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void* vc, void* out, float* partials,
                                      int* counters, const int* positions, const int* token_seq, const int* seq_slot,
                                      const int* pages, int max_blocks, int n_blocks, int T, int n_heads, int kv_heads,
-                                     int hd, float scale, int window, int pages_per_chunk, cudaStream_t stream) {
+                                     int hd, float scale, int window, int pages_per_chunk, int store_kv,
+                                     cudaStream_t stream) {
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0 && n_blocks > 0 && n_blocks <= max_blocks,
               "attention_decode: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_decode: %d heads are not a multiple of %d key/value heads", n_heads,
@@ -197,17 +222,19 @@ EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void
   float* part_ml = partials;
   float* part_acc = part_ml + items * n_chunks * 2;
   dim3 grid(n_chunks, n_heads, T);
-#define EMBER_DECODE(LPK)                                                                                            \
-  attention_decode_kernel<LPK><<<grid, kThreads, 0, stream>>>(                                                       \
-      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_ml,   \
-      part_acc, counters, positions, token_seq, seq_slot, pages, max_blocks, n_heads, kv_heads, hd, scale, window,  \
-      pages_per_chunk, n_chunks)
+  cudaError_t e;
+#define EMBER_DECODE(LPK)                                                                                           \
+  e = launch_pdl(attention_decode_kernel<LPK>, grid, dim3(kThreads), 0, stream, (const __nv_bfloat16*)qkv,          \
+                 (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_ml, part_acc, counters, \
+                 positions, token_seq, seq_slot, pages, max_blocks, n_heads, kv_heads, hd, scale, window,           \
+                 pages_per_chunk, n_chunks, store_kv ? (__nv_bfloat16*)kc : (__nv_bfloat16*)nullptr,                 \
+                 store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr)
   if (hd <= 16) EMBER_DECODE(2);
   else if (hd <= 32) EMBER_DECODE(4);
   else if (hd <= 64) EMBER_DECODE(8);
   else if (hd <= 128) EMBER_DECODE(16);
   else EMBER_DECODE(32);
 #undef EMBER_DECODE
-  EMBER_LAUNCH_OK("attention_decode");
+  if (e != cudaSuccess) return ember_fail("attention_decode: %s", cudaGetErrorString(e));
   return 0;
 }

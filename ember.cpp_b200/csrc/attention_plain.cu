@@ -21,6 +21,8 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T
                                 const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks,
                                 int q_width, int kv_heads, int hd) {
   constexpr int kVec = 16 / (int)sizeof(T);
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int s = token_seq[t];
   if (seq_slot[s] < 0) return;
@@ -45,16 +47,17 @@ EMBER_API int ember_kv_store(const void* qkv, void* kc, void* vc, const int* pos
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && hd > 0 && max_blocks > 0, "kv_store: bad sizes");
   EMBER_CHECK(hd % 16 == 0, "kv_store: head size %d is not a multiple of 16", hd);
   const int qw = n_heads * hd;
+  cudaError_t e;
   if (dtype == EMBER_F32)
-    kv_store_kernel<float><<<T, 128, 0, stream>>>((const float*)qkv, (float*)kc, (float*)vc, positions, token_seq,
-                                                  seq_slot, pages, max_blocks, qw, kv_heads, hd);
+    e = launch_pdl(kv_store_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)qkv, (float*)kc, (float*)vc,
+                   positions, token_seq, seq_slot, pages, max_blocks, qw, kv_heads, hd);
   else if (dtype == EMBER_BF16)
-    kv_store_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>((const __nv_bfloat16*)qkv, (__nv_bfloat16*)kc,
-                                                          (__nv_bfloat16*)vc, positions, token_seq, seq_slot, pages,
-                                                          max_blocks, qw, kv_heads, hd);
+    e = launch_pdl(kv_store_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)qkv,
+                   (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, positions, token_seq, seq_slot, pages, max_blocks, qw,
+                   kv_heads, hd);
   else
     return ember_fail("kv_store: element type %d", dtype);
-  EMBER_LAUNCH_OK("kv_store");
+  if (e != cudaSuccess) return ember_fail("kv_store: %s", cudaGetErrorString(e));
   return 0;
 }
 

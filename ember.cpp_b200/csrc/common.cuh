@@ -10,6 +10,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define EMBER_API extern "C" __attribute__((visibility("default")))
 
@@ -67,4 +68,36 @@ __device__ __forceinline__ float apply_act(float v, int act) {
   if (act == EMBER_ACT_GELU_TANH) return gelu_tanh(v);
   if (act == EMBER_ACT_GELU_ERF) return gelu_erf(v);
   return v;
+}
+
+// Programmatic dependent launch.  A kernel launched with launch_pdl may begin while the kernel
+// before it in the stream is still running; it must call pdl_wait() before it reads anything
+// that kernel wrote and before it writes anything at all.  pdl_trigger() lets the kernel after
+// this one begin early in the same way.  In a kernel that was launched the ordinary way both are
+// no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+// EMBER_PDL=0 in the environment launches these kernels the ordinary way (for measurements).
+inline int pdl_allowed() {
+  static const int on = [] {
+    const char* v = getenv("EMBER_PDL");
+    return (v && v[0] == '0') ? 0 : 1;
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr.val.programmaticStreamSerializationAllowed = pdl_allowed();
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }

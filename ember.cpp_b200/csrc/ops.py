@@ -38,7 +38,7 @@ _SIGNATURES = {
     "ember_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
                               _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
     "ember_attention_decode": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
-                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void],
     "ember_attention_prefill": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_void],
@@ -234,8 +234,9 @@ class CudaOps:
                    plan.pages[cache.group_index].data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, head_dim,
                    _code(qkv.dtype))
 
-    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype):
-        """Causal attention of the step's tokens over the cache (their own keys already stored).
+    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False):
+        """Causal attention of the step's tokens over the cache.  With `store` their own keys and
+        values are written into the cache first (in the same launch where a kernel can).
         float32: the plain kernel, whose sums depend on positions alone.  bfloat16: one token per
         sequence takes the split decode kernel; anything else the tensor-core prefill kernel, or
         the plain kernel for head sizes that one has no instantiation for."""
@@ -252,8 +253,10 @@ class CudaOps:
             self._call("ember_attention_decode", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
                        partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(),
                        plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, blocks, plan.T, n_heads, kv_heads,
-                       head_dim, float(scale), int(window), per_chunk)
+                       head_dim, float(scale), int(window), per_chunk, 1 if store else 0)
             return out
+        if store:
+            self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim)
         if qkv.dtype == torch.bfloat16 and scale > 0:
             rc = self._call("ember_attention_prefill", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),

@@ -9,20 +9,22 @@
 //
 // One block per row; nothing is sorted.  Each candidate has the 64-bit key (bits of p, index);
 // the k-th largest key and the key at which the running mass reaches top_p are found by radix
-// selection, 8 bits a pass, over counts and over masses held as integers (p * 2^40, so that sums
-// do not depend on the order of addition).  Candidates are recomputed from the logits in each
-// pass instead of being stored.
+// selection over counts and over masses held as integers (p * 2^40, so that sums do not depend on
+// the order of addition), 11 bits a pass, stopping as soon as the bucket holds one candidate.  The
+// row's p values are kept in shared memory when the vocabulary fits (up to about 51,000 entries);
+// otherwise they are recomputed from the logits in each pass.
 #include "common.cuh"
 
 namespace {
 
 constexpr int kThreads = 512;
+constexpr int kBins = 2048;
 constexpr double kMassScale = 1099511627776.0;  // 2^40
+typedef unsigned long long u64;
 
-__device__ __forceinline__ unsigned long long splitmix_uniform24(unsigned long long seed, unsigned long long stream,
-                                                                 unsigned long long counter) {
-  unsigned long long z = seed * 0x9E3779B97F4A7C15ull + stream * 0xBF58476D1CE4E5B9ull +
-                         counter * 0x94D049BB133111EBull + 0x2545F4914F6CDD1Dull;
+__device__ __forceinline__ u64 splitmix_uniform24(u64 seed, u64 stream, u64 counter) {
+  u64 z = seed * 0x9E3779B97F4A7C15ull + stream * 0xBF58476D1CE4E5B9ull + counter * 0x94D049BB133111EBull +
+          0x2545F4914F6CDD1Dull;
   z ^= z >> 30;
   z *= 0xBF58476D1CE4E5B9ull;
   z ^= z >> 27;
@@ -31,107 +33,174 @@ __device__ __forceinline__ unsigned long long splitmix_uniform24(unsigned long l
   return z >> 40;  // 24 bits
 }
 
-struct Cand {
-  unsigned long long key;
-  unsigned long long mass;
+struct Row {
+  const float* logits;  // global
+  const float* cached;  // shared, or null
+  float mx, inv_t;
+  __device__ __forceinline__ float p(int i) const {
+    if (cached) return cached[i];
+    const float l = logits[i];
+    return (l == l) ? expf((l - mx) * inv_t) : 0.f;  // a NaN logit gets no mass
+  }
 };
 
-__device__ __forceinline__ Cand candidate(const float* row, int i, float mx, float inv_t) {
-  const float l = row[i];
-  float p = (l == l) ? expf((l - mx) * inv_t) : 0.f;  // a NaN logit gets no mass
-  Cand c;
-  c.key = ((unsigned long long)__float_as_uint(p) << 32) | (unsigned)i;
-  c.mass = (unsigned long long)((double)p * kMassScale);
-  return c;
-}
+__device__ __forceinline__ u64 key_of(float p, int i) { return ((u64)__float_as_uint(p) << 32) | (unsigned)i; }
+__device__ __forceinline__ u64 mass_of(float p) { return (u64)((double)p * kMassScale); }
 
-__device__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long* scratch) {
+// Sum over the block; every thread gets the total.  scratch: kThreads / 32 entries.
+__device__ u64 block_sum(u64 v, u64* scratch) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
   __syncthreads();
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
   __syncthreads();
-  unsigned long long t = 0;
+  u64 t = 0;
   for (int w = 0; w < kThreads / 32; ++w) t += scratch[w];
   return t;
 }
 
-// Radix selection over the keys, from the top byte down.  by_mass = false: the key of the
-// `need`-th largest candidate.  by_mass = true: the key at which the running mass, taken in
-// descending key order, first reaches `need`.
-__device__ unsigned long long radix_select(const float* row, int V, float mx, float inv_t, bool by_mass,
-                                           unsigned long long need, unsigned* cnt, unsigned long long* mass,
-                                           unsigned long long* shared_prefix, unsigned long long* shared_need) {
-  unsigned long long prefix = 0;
-  for (int pass = 0; pass < 8; ++pass) {
-    const int shift = 56 - 8 * pass;
-    for (int b = threadIdx.x; b < 256; b += kThreads) {
+struct Pick {
+  int bin;      // chosen bucket
+  u64 before;   // weight of the buckets above it
+  unsigned count;  // candidates in it
+  bool none;       // no bucket reached the need: `bin` is the lowest non-empty one, everything is kept
+};
+
+// Walks the buckets from the highest down and finds the first non-empty one at which the running
+// weight (counts, or masses) reaches `need`.  If none does, the lowest non-empty bucket with
+// `before` = need (so that the caller's remaining need becomes 0: everything is kept).
+__device__ Pick find_bucket(const unsigned* cnt, const u64* mass, bool by_mass, u64 need, u64* scratch, int* s_hit,
+                            u64* s_before) {
+  constexpr int kPer = kBins / kThreads;  // 4 buckets per thread, in descending order
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  u64 w[kPer], local = 0;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int b = kBins - 1 - (threadIdx.x * kPer + j);
+    w[j] = by_mass ? mass[b] : (u64)cnt[b];
+    local += w[j];
+  }
+  // exclusive prefix of `local` over threads (thread 0 owns the highest buckets)
+  u64 incl = local;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const u64 up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  if (threadIdx.x == 0) {
+    *s_hit = 0x7fffffff;
+    *s_before = 0;
+  }
+  __syncthreads();
+  if (lane == 31) scratch[warp] = incl;
+  __syncthreads();
+  u64 base = 0;
+  for (int i = 0; i < warp; ++i) base += scratch[i];
+  u64 run = base + incl - local;
+  int lowest = -1;
+#pragma unroll
+  for (int j = 0; j < kPer; ++j) {
+    const int slot = threadIdx.x * kPer + j;
+    const int b = kBins - 1 - slot;
+    if (cnt[b]) {
+      lowest = slot;
+      if (run + w[j] >= need) atomicMin(s_hit, slot);
+    }
+    run += w[j];
+  }
+  __syncthreads();
+  int hit = *s_hit;
+  const bool none = hit == 0x7fffffff;
+  __syncthreads();
+  if (none) {  // nothing reaches the need: the lowest non-empty bucket
+    if (threadIdx.x == 0) *s_hit = -1;
+    __syncthreads();
+    if (lowest >= 0) atomicMax(s_hit, lowest);
+    __syncthreads();
+    hit = *s_hit;
+  }
+  // the owner of the chosen bucket publishes the weight above it
+  if (hit >= 0 && hit / kPer == (int)threadIdx.x) {
+    u64 r = base + incl - local;
+    for (int j = 0; j < hit % kPer; ++j) r += w[j];
+    *s_before = none ? need : r;
+  }
+  __syncthreads();
+  Pick pick;
+  pick.bin = kBins - 1 - max(hit, 0);
+  pick.before = *s_before;
+  pick.count = cnt[pick.bin];
+  pick.none = none;
+  __syncthreads();
+  return pick;
+}
+
+// Radix selection over the keys from the top bits down.  by_mass = false: the key of the
+// `need`-th largest candidate.  by_mass = true: the key at which the running mass, in descending
+// key order, first reaches `need`.  Returns a threshold: the candidates to keep are those with
+// key >= threshold.
+__device__ u64 radix_select(const Row& row, int V, bool by_mass, u64 need, unsigned* cnt, u64* mass, u64* scratch,
+                            int* s_hit, u64* s_before) {
+  const int shifts[6] = {53, 42, 32, 21, 10, 0};
+  const int widths[6] = {11, 11, 10, 11, 11, 10};
+  u64 prefix = 0;
+  for (int pass = 0; pass < 6; ++pass) {
+    const int shift = shifts[pass];
+    if (pass >= 3 && ((u64)(V - 1) >> shift) == 0 && shift > 0) continue;  // no index has a bit here
+    const u64 high_mask = pass == 0 ? 0ull : ~0ull << (shift + widths[pass]);
+    const unsigned digit_mask = (1u << widths[pass]) - 1;
+    for (int b = threadIdx.x; b < kBins; b += kThreads) {
       cnt[b] = 0;
       mass[b] = 0;
     }
     __syncthreads();
-    const unsigned long long high_mask = pass == 0 ? 0ull : ~0ull << (shift + 8);
     for (int i = threadIdx.x; i < V; i += kThreads) {
-      const Cand c = candidate(row, i, mx, inv_t);
-      if ((c.key & high_mask) == prefix) {
-        const int b = (int)((c.key >> shift) & 0xff);
-        atomicAdd(&cnt[b], 1u);
-        if (by_mass && c.mass) atomicAdd(&mass[b], c.mass);
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      unsigned long long run = 0;
-      int chosen = -1, lowest = -1;
-      for (int b = 255; b >= 0; --b) {
-        if (!cnt[b]) continue;
-        lowest = b;
-        const unsigned long long w = by_mass ? mass[b] : cnt[b];
-        if (run + w >= need) {
-          chosen = b;
-          break;
+      const float p = row.p(i);
+      const u64 key = key_of(p, i);
+      if ((key & high_mask) == prefix) {
+        const int b = (int)((key >> shift) & digit_mask);
+        // lanes that hit the same bucket add once (a peaked row puts most candidates into one bucket)
+        const unsigned peers = __match_any_sync(__activemask(), b);
+        if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[b], (unsigned)__popc(peers));
+        if (by_mass) {
+          const u64 m = mass_of(p);
+          if (m) atomicAdd(&mass[b], m);
         }
-        run += w;
       }
-      if (chosen < 0) {  // the remaining mass does not reach the target: keep everything
-        chosen = lowest;
-        run = 0;
-        need = 0;
-      } else {
-        need -= run;
-      }
-      *shared_prefix = prefix | ((unsigned long long)chosen << shift);
-      *shared_need = need;
     }
     __syncthreads();
-    prefix = *shared_prefix;
-    need = *shared_need;
-    __syncthreads();
+    const Pick pick = find_bucket(cnt, mass, by_mass, need, scratch, s_hit, s_before);
+    prefix |= (u64)pick.bin << shift;
+    if (pick.none) return prefix;  // the remaining weight does not reach the need: keep everything
+    need -= pick.before;
+    // one candidate left, or (by count) the whole bucket is wanted: every key in the bucket is kept
+    if (pick.count == 1 || (!by_mass && (u64)pick.count == need)) return prefix;
   }
   return prefix;
 }
 
+template <bool CACHED>
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float temperature, int top_k,
-              float top_p, unsigned long long seed, const int* __restrict__ streams,
-              const int* __restrict__ counters) {
+              float top_p, u64 seed, const int* __restrict__ streams, const int* __restrict__ counters) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  u64* s_mass = reinterpret_cast<u64*>(smem_raw);                 // [kBins]; also the segment sums at the end
+  unsigned* s_cnt = reinterpret_cast<unsigned*>(s_mass + kBins);  // [kBins]
+  float* s_p = reinterpret_cast<float*>(s_cnt + kBins);           // [V] if CACHED
   __shared__ float s_val[kThreads / 32];
   __shared__ int s_idx[kThreads / 32];
-  __shared__ unsigned long long s_u64[kThreads / 32];
-  __shared__ unsigned s_cnt[256];
-  __shared__ unsigned long long s_mass[256];
-  __shared__ unsigned long long s_prefix, s_need;
-  __shared__ unsigned long long s_seg[kThreads];
-  __shared__ int s_result;
+  __shared__ u64 s_u64[kThreads / 32];
+  __shared__ u64 s_before;
+  __shared__ int s_hit, s_result;
 
-  const float* row = logits + (size_t)blockIdx.x * V;
+  const float* rowp = logits + (size_t)blockIdx.x * V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
   // first maximal index; NaN never wins
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   for (int i = threadIdx.x; i < V; i += kThreads) {
-    const float l = row[i];
+    const float l = rowp[i];
     if (l > best || (l == best && i < best_i)) {
       best = l;
       best_i = i;
@@ -164,48 +233,58 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
     return;
   }
 
-  const float inv_t = 1.0f / temperature;
+  Row row;
+  row.logits = rowp;
+  row.cached = nullptr;
+  row.mx = best;
+  row.inv_t = 1.0f / temperature;
   if (top_k <= 0 || top_k > V) top_k = V;
 
-  unsigned long long z = 0;
-  for (int i = threadIdx.x; i < V; i += kThreads) z += candidate(row, i, best, inv_t).mass;
-  z = block_sum_u64(z, s_u64);
+  u64 z = 0;
+  for (int i = threadIdx.x; i < V; i += kThreads) {
+    const float p = row.p(i);
+    if (CACHED) s_p[i] = p;
+    z += mass_of(p);
+  }
+  z = block_sum(z, s_u64);  // its barriers also publish s_p
+  if (CACHED) row.cached = s_p;
 
-  unsigned long long thr = 0;
-  if (top_k < V) thr = radix_select(row, V, best, inv_t, false, (unsigned long long)top_k, s_cnt, s_mass, &s_prefix, &s_need);
+  u64 thr = 0;
+  if (top_k < V) thr = radix_select(row, V, false, (u64)top_k, s_cnt, s_mass, s_u64, &s_hit, &s_before);
   if (top_p < 1.0f) {
     const double target = ceil((double)fmaxf(top_p, 0.f) * (double)z);
-    const unsigned long long thr_p =
-        radix_select(row, V, best, inv_t, true, (unsigned long long)target, s_cnt, s_mass, &s_prefix, &s_need);
+    const u64 thr_p = radix_select(row, V, true, (u64)target, s_cnt, s_mass, s_u64, &s_hit, &s_before);
     if (thr_p > thr) thr = thr_p;
   }
 
   // inverse CDF in index order over the kept candidates: thread t owns a contiguous segment
+  u64* s_seg = s_mass;
   const int seg = (V + kThreads - 1) / kThreads;
   const int lo = threadIdx.x * seg, hi = min(V, lo + seg);
-  unsigned long long mine = 0;
+  u64 mine = 0;
   for (int i = lo; i < hi; ++i) {
-    const Cand c = candidate(row, i, best, inv_t);
-    if (c.key >= thr) mine += c.mass;
+    const float p = row.p(i);
+    if (key_of(p, i) >= thr) mine += mass_of(p);
   }
+  __syncthreads();
   s_seg[threadIdx.x] = mine;
   if (threadIdx.x == 0) s_result = best_i;  // if nothing is drawn (no mass at all), the maximum
   __syncthreads();
-  unsigned long long before = 0, total = 0;
+  u64 before = 0, total = 0;
   for (int t = 0; t < kThreads; ++t) {
-    if (t < (int)threadIdx.x) before += s_seg[t];
-    total += s_seg[t];
+    const u64 v = s_seg[t];
+    if (t < (int)threadIdx.x) before += v;
+    total += v;
   }
-  const unsigned long long u24 = splitmix_uniform24(seed, (unsigned long long)streams[blockIdx.x],
-                                                    (unsigned long long)counters[blockIdx.x]);
+  const u64 u24 = splitmix_uniform24(seed, (u64)streams[blockIdx.x], (u64)counters[blockIdx.x]);
   // target = floor(total * u24 / 2^24), exact in 128 bits
-  const unsigned long long target = (__umul64hi(total, u24) << 40) | ((total * u24) >> 24);
+  const u64 target = (__umul64hi(total, u24) << 40) | ((total * u24) >> 24);
   if (total > 0 && before <= target && target < before + mine) {
-    unsigned long long run = before;
+    u64 run = before;
     for (int i = lo; i < hi; ++i) {
-      const Cand c = candidate(row, i, best, inv_t);
-      if (c.key >= thr) {
-        run += c.mass;
+      const float p = row.p(i);
+      if (key_of(p, i) >= thr) {
+        run += mass_of(p);
         if (run > target) {
           s_result = i;
           break;
@@ -223,7 +302,22 @@ EMBER_API int ember_sample(const float* logits, int* out, int rows, int V, float
                            unsigned long long seed, const int* streams, const int* counters, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && V > 0, "sample: rows = %d, vocabulary = %d", rows, V);
   EMBER_CHECK(temperature >= 0.f, "sample: temperature %g is negative", (double)temperature);
-  sample_kernel<<<rows, kThreads, 0, stream>>>(logits, out, V, temperature, top_k, top_p, seed, streams, counters);
+  const size_t bins = kBins * (sizeof(u64) + sizeof(unsigned));
+  const size_t cached = bins + (size_t)V * sizeof(float);
+  static bool configured = false;
+  const size_t limit = 226 * 1024;  // of the 227 KB a block may have; the kernel's static arrays take the rest
+  if (cached <= limit) {
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(sample_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)limit);
+      if (e != cudaSuccess) return ember_fail("sample: %s", cudaGetErrorString(e));
+      configured = true;
+    }
+    sample_kernel<true><<<rows, kThreads, cached, stream>>>(logits, out, V, temperature, top_k, top_p, seed, streams,
+                                                            counters);
+  } else {
+    sample_kernel<false><<<rows, kThreads, bins, stream>>>(logits, out, V, temperature, top_k, top_p, seed, streams,
+                                                           counters);
+  }
   EMBER_LAUNCH_OK("sample");
   return 0;
 }

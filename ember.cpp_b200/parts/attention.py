@@ -61,10 +61,8 @@ class CausalAttention(Mixer):
         ops = ctx.ops
         qkv = ops.linear(h, self.w_qkv, self.b_qkv, out_dtype=ctx.dtype)
         ctx.position.apply_qk(ctx, qkv, self.n_heads, self.kv_heads, self.head_dim)
-        if app.writes_cache:
-            ops.kv_store(qkv, app.cache, ctx.plan, self.n_heads, self.kv_heads, self.head_dim)
         a = ops.attention(qkv, app.cache, ctx.plan, self.n_heads, self.kv_heads, self.head_dim, self.scale,
-                          self.window, out_dtype=ctx.dtype)
+                          self.window, out_dtype=ctx.dtype, store=app.writes_cache)
         return ops.linear(a, self.w_out, self.b_out, residual=residual)
 
 

@@ -57,7 +57,9 @@ class CpuOps:
             cache.k[page, :, p % PAGE, :] = qkv[t, q_w:q_w + kv_w].view(kv_heads, head_dim).to(cache.k.dtype)
             cache.v[page, :, p % PAGE, :] = qkv[t, q_w + kv_w:].view(kv_heads, head_dim).to(cache.v.dtype)
 
-    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype):
+    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False):
+        if store:
+            self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim)
         g = cache.group_index
         out = torch.zeros(plan.T, n_heads * head_dim)
         rep = n_heads // kv_heads

@@ -217,8 +217,7 @@ def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poiso
         host = build_step([(s, [0] * n, []) for s, n in entries], cache.lengths, tables, cache.max_blocks)
         plan = StepPlan(host, torch.from_numpy(host.packed).cuda())
         qkv = torch.cat(rows).cuda().contiguous()
-        ops.kv_store(qkv, view, plan, heads, kv_heads, hd)
-        out = ops.attention(qkv, view, plan, heads, kv_heads, hd, scale, window, DT[dtype])
+        out = ops.attention(qkv, view, plan, heads, kv_heads, hd, scale, window, DT[dtype], store=True)
         cache.commit([(s, n) for s, n in entries])
         return out
 
