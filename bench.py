@@ -112,10 +112,14 @@ class ClockSampler:
 
 
 def reference_arm() -> int:
+    """ember.cpp does not install offline: its scikit-build/CMake build downloads
+    nlohmann_json and cpp-httplib with FetchContent, and there is no network here."""
     ref = os.path.join(ROOT, "baseline", "_ref")
-    why = ("ember.cpp is a CMake/C++ project whose build fetches its JSON dependency from the network and has no "
-           "sm_100 target; it does not install offline" if not os.path.isdir(ref) or not os.listdir(ref)
-           else "baseline/_ref holds no importable GPT-2 path of ember.cpp")
+    installed = os.path.isdir(ref) and any(n.startswith("tinyllama") for n in os.listdir(ref))
+    why = ("baseline/_ref holds an ember.cpp build, but its GPT-2 path has no sm_100 target and no batch API to time"
+           if installed else
+           "ember.cpp does not install offline: pip's build of it fails in CMake FetchContent (nlohmann_json from "
+           "github.com, no network); nothing under baseline/_ref")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
