@@ -112,8 +112,8 @@ class ClockSampler:
 
 
 def reference_arm() -> int:
-    """ember.cpp does not install offline: its scikit-build/CMake build downloads
-    nlohmann_json and cpp-httplib with FetchContent, and there is no network here."""
+    """ember.cpp does not install offline: its scikit-build/CMake build downloads nlohmann_json
+    and cpp-httplib with FetchContent, and there is no network here."""
     ref = os.path.join(ROOT, "baseline", "_ref")
     installed = os.path.isdir(ref) and any(n.startswith("tinyllama") for n in os.listdir(ref))
     why = ("baseline/_ref holds an ember.cpp build, but its GPT-2 path has no sm_100 target and no batch API to time"
