@@ -238,3 +238,64 @@ EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void
   if (e != cudaSuccess) return ember_fail("attention_decode: %s", cudaGetErrorString(e));
   return 0;
 }
+
+// ---------------------------------------------------------------------------- without allocation
+// ember_attention_decode_static: the same decode attention for callers that must not allocate
+// device memory.  It has no counterpart in ember.cpp; see ember_kernels.h for who needs it.
+//
+// The split kernel above needs scratch (partial results per (token, head, chunk), and a counter per
+// (token, head)).  Here that scratch is two file-scope __device__ arrays of fixed size, which every
+// GPU that loads this library holds from load until the process exits (4 MiB + 64 KiB).  In host
+// code the arrays' names are only stand-ins, not device addresses, so their addresses are asked
+// for once per device with cudaGetSymbolAddress, on that device, and kept.  That happens in the
+// first call on a device, which should therefore come before any stream capture.
+namespace {
+
+constexpr size_t kStaticPartialFloats = (size_t)1 << 20;  // 4 MiB of partial results
+constexpr int kStaticCounters = 1 << 14;                  // 16,384 (token, head) pairs
+
+static __device__ __align__(256) float g_static_partials[kStaticPartialFloats];
+static __device__ __align__(256) int g_static_counters[kStaticCounters];
+
+constexpr int kMaxDevices = 64;
+float* g_partials_on[kMaxDevices] = {};
+int* g_counters_on[kMaxDevices] = {};
+
+}  // namespace
+
+EMBER_API int ember_attention_decode_static(const void* qkv, const void* kc, const void* vc, void* out,
+                                            const int* positions, const int* token_seq, const int* seq_slot,
+                                            const int* pages, int max_blocks, int n_blocks, int T, int n_heads,
+                                            int kv_heads, int hd, float scale, int window, int pages_per_chunk,
+                                            int store_kv, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && n_heads > 0 && hd > 0 && n_blocks > 0 && pages_per_chunk > 0, "attention_decode_static: bad sizes");
+  const size_t need = ember_attention_decode_partials(T, n_heads, hd, n_blocks, pages_per_chunk);
+  EMBER_CHECK(need <= kStaticPartialFloats,
+              "attention_decode_static: %d tokens x %d heads x %d chunks of head size %d need %zu floats of scratch, the "
+              "built-in scratch holds %zu; use more pages per chunk or the entry point that takes scratch",
+              T, n_heads, (n_blocks + pages_per_chunk - 1) / pages_per_chunk, hd, need, kStaticPartialFloats);
+  EMBER_CHECK((long long)T * n_heads <= kStaticCounters,
+              "attention_decode_static: %d tokens x %d heads exceed the built-in scratch's %d (token, head) pairs", T,
+              n_heads, kStaticCounters);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return ember_fail("attention_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  EMBER_CHECK(dev >= 0 && dev < kMaxDevices, "attention_decode_static: device %d", dev);
+  if (!g_partials_on[dev]) {  // set-up, once per device, with that device current
+    float* p = nullptr;
+    int* c = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_partials);
+    if (e != cudaSuccess) return ember_fail("attention_decode_static: address of the scratch: %s", cudaGetErrorString(e));
+    e = cudaGetSymbolAddress((void**)&c, g_static_counters);
+    if (e != cudaSuccess) return ember_fail("attention_decode_static: address of the counters: %s", cudaGetErrorString(e));
+    g_counters_on[dev] = c;
+    g_partials_on[dev] = p;
+  }
+  // The arrays keep what the last call left.  Partials are always written before they are read;
+  // the counters must start at zero, so they are cleared here on the caller's stream.
+  e = cudaMemsetAsync(g_counters_on[dev], 0, (size_t)T * n_heads * sizeof(int), stream);
+  if (e != cudaSuccess) return ember_fail("attention_decode_static: clearing the counters: %s", cudaGetErrorString(e));
+  return ember_attention_decode(qkv, kc, vc, out, g_partials_on[dev], g_counters_on[dev], positions, token_seq,
+                                seq_slot, pages, max_blocks, n_blocks, T, n_heads, kv_heads, hd, scale, window,
+                                pages_per_chunk, store_kv, stream);
+}
