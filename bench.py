@@ -133,6 +133,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each prompt before decoding starts")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -150,14 +151,15 @@ def main() -> int:
     from ember_cpp_b200.weights import random_tensors
 
     W = max(3, args.warmup)
+    prompt_len = args.prompt_len
     cfgd = xl_config()
     full_layers = cfgd["n_layer"]
     if args.layers:
         cfgd["n_layer"] = args.layers
     cfg = E.GPT2Config.from_dict({**cfgd, "architectures": ["GPT2LMHeadModel"]})
     ctx = cfg.n_positions
-    K = args.steps if args.steps is not None else ctx - PROMPT_LEN - W
-    K = max(1, min(K, ctx - PROMPT_LEN - W))
+    K = args.steps if args.steps is not None else ctx - prompt_len - W
+    K = max(1, min(K, ctx - prompt_len - W))
     pk = peaks()
 
     t0 = time.time()
@@ -179,10 +181,10 @@ def main() -> int:
     windows = []
 
     def decode_run(B: int, warm: int, steps: int):
-        """Prefill B prompts of PROMPT_LEN, then warm + steps decode steps; times the last `steps`."""
+        """Prefill B prompts of prompt_len, then warm + steps decode steps; times the last `steps`."""
         slots = [engine.open() for _ in range(B)]
-        prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(B)]
-        logits = engine.step([(s, p, [PROMPT_LEN - 1]) for s, p in zip(slots, prompts)])
+        prompts = [rng.integers(0, V, prompt_len).tolist() for _ in range(B)]
+        logits = engine.step([(s, p, [prompt_len - 1]) for s, p in zip(slots, prompts)])
         streams = torch.arange(B, dtype=torch.int32, device="cuda")
         counters = torch.zeros(B, dtype=torch.int32, device="cuda")
         toks = sampler.sample(logits, params, streams, counters).tolist()
@@ -216,7 +218,7 @@ def main() -> int:
     points = {}
     if not args.no_points:
         for B in (1, 64):
-            r = decode_run(B, W, ctx - PROMPT_LEN - W)
+            r = decode_run(B, W, ctx - prompt_len - W)
             points[f"decode_b{B}"] = round(r["tok_s"], 1)
             log(f"batch {B}: {r}")
 
@@ -249,7 +251,7 @@ def main() -> int:
     session = E.Session.from_engine(engine, max_batch_size=args.batch, seed=0)
     stamps = []
     session.set_token_callback(lambda i, tok: stamps.append(time.perf_counter()) if i == 0 else None)
-    prompts = [rng.integers(0, V, PROMPT_LEN).tolist() for _ in range(args.batch)]
+    prompts = [rng.integers(0, V, prompt_len).tolist() for _ in range(args.batch)]
     w0 = time.time()
     out = session.generate_batch(prompts, steps=W + K + 1, temperature=params.temperature, top_k=params.top_k,
                                  top_p=params.top_p, stop_token_ids=[])
@@ -269,7 +271,7 @@ def main() -> int:
         "impl": "ours",
         "config": {"model": "gpt2-xl-shape", "n_layer": L, "n_layer_of_config": full_layers, "n_embd": d,
                    "n_head": cfg.n_head, "n_inner": F, "vocab_size": V, "n_positions": ctx, "global_batch": args.batch,
-                   "seq_len": ctx, "prompt_len": PROMPT_LEN, "context_end": PROMPT_LEN + W + K + 1,
+                   "seq_len": ctx, "prompt_len": prompt_len, "context_end": prompt_len + W + K + 1,
                    "parallelism": "single-gpu", "weights": "random seed 0 bf16", "sampling": "t0.1 k40 p0.9",
                    "l2": "inputs>L2 (3.1 GB of weights per step)", "peaks": pk["source"]},
         "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
