@@ -71,6 +71,8 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float 
 template <typename OutT>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                                  OutT* __restrict__ out, int rows, int d, float eps) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -124,15 +126,17 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 EMBER_API int ember_layernorm(const float* x, const float* w, const float* b, void* out, int rows, int d, float eps,
                               int out_dtype, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && d > 0, "layernorm: rows = %d, width = %d", rows, d);
-  const int warps = 4;
+  const int warps = rows < 64 ? 1 : 4;  // a few rows: a block each, so that they run on different SMs
   const int grid = (rows + warps - 1) / warps;
+  cudaError_t e;
   if (out_dtype == EMBER_F32)
-    layernorm_kernel<float><<<grid, warps * 32, 0, stream>>>(x, w, b, (float*)out, rows, d, eps);
+    e = launch_pdl(layernorm_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b, (float*)out, rows, d, eps);
   else if (out_dtype == EMBER_BF16)
-    layernorm_kernel<__nv_bfloat16><<<grid, warps * 32, 0, stream>>>(x, w, b, (__nv_bfloat16*)out, rows, d, eps);
+    e = launch_pdl(layernorm_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b,
+                   (__nv_bfloat16*)out, rows, d, eps);
   else
     return ember_fail("layernorm: element type %d", out_dtype);
-  EMBER_LAUNCH_OK("layernorm");
+  if (e != cudaSuccess) return ember_fail("layernorm: %s", cudaGetErrorString(e));
   return 0;
 }
 

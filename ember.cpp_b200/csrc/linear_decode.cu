@@ -9,24 +9,27 @@
 //
 // The product runs on the tensor cores with the operands swapped: the 16 rows of an mma.sync
 // m16n8k16 tile are 16 output features (weight rows), its 8 columns are 8 sequences of the batch.
-// Each lane loads 16 bytes (8 consecutive k) of weight rows g and g+8 straight from global memory:
-// those registers are the A fragments of two MMAs under a fixed relabelling of k inside a 32-wide
-// slice, and the matching 8 values of X for sequence g, relabelled the same way, are the B
-// fragment.
+// Under a fixed relabelling of k inside a 32-wide slice, 16 consecutive bytes of weight rows g and
+// g+8 are the A fragments of two MMAs and the matching 8 values of X for sequence g are the B
+// fragment, so no value is shuffled between lanes.
 //
 // Work is cut so that a few-megabyte matrix still occupies the whole chip: a tile is 16 weight
-// rows; a thread-block cluster of 1, 2 or 4 blocks shares a tile and splits K between its blocks;
-// inside a block 8 warps take interleaved slices.  Warps are summed in shared memory in warp order,
-// the cluster's blocks are summed in block order through distributed shared memory into block 0,
-// which applies the epilogue: no atomics, so a result does not depend on timing.
+// rows; a thread-block cluster of 1, 2 or 4 blocks shares a tile and splits K between its blocks.
+// A block asks for its whole share of the matrix at once (cp.async into shared memory, about 50 KB,
+// three or four blocks to an SM), so the matrix is in flight from the first instruction and the
+// kernel runs at the speed of HBM, not of its own round trips.  Inside a block 8 warps take
+// interleaved slices; warps are summed in shared memory in warp order, the cluster's blocks in
+// block order through distributed shared memory into block 0, which applies the epilogue: no
+// atomics, so a result does not depend on timing.
 //
-// The kernel is launched with programmatic stream serialization: it asks for its first weight
-// slices at once and only then waits for the kernel before it (griddepcontrol.wait), so that
-// weights stream while the producer of X is still finishing.  Nothing is written before the wait.
+// The kernel is launched with programmatic stream serialization: the weight copies are issued
+// first, and only then does it wait for the kernel before it (griddepcontrol.wait), so that
+// weights stream while the producer of X is still finishing.  Nothing is written to global memory
+// before the wait.
 //
-// Input modes: float32 rows with a layer norm (statistics in float32 per row, the normalised
-// slice rounded to bfloat16 into shared memory, the values the separate norm kernel writes), or
-// bfloat16 rows read as they are.
+// Input modes: float32 rows with a layer norm (statistics in float32 per row, each value
+// normalised and rounded to bfloat16 as it enters an MMA: the values the separate norm kernel
+// writes), or bfloat16 rows read as they are.
 #include <cooperative_groups.h>
 
 #include "common.cuh"
@@ -42,15 +45,24 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint4 ldg_stream(const void* p) {  // weights are read once: do not keep them in L1
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-  return v;
+constexpr int kWarps = 8;
+constexpr int kRowVecs = 16;  // float4 per lane of a row held in registers (K <= 2048)
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
 }
 
-constexpr int kWarps = 8;
-constexpr int kDepth = 4;  // weight slices a warp keeps in flight
+__device__ __forceinline__ unsigned pack2(float a, float b) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+// Row stride of the weight tile in shared memory, in elements: the slice plus a pad that puts
+// consecutive rows 64 bytes apart modulo 128, so that the 16-byte reads of a quarter warp (two rows,
+// four chunks each) fall into distinct banks.
+__host__ __device__ inline int tile_stride(int per_block) { return per_block * 32 + ((per_block & 1) ? 0 : 32); }
 
 // MT: batch tiles of 8 sequences (1 or 2).  LN: float32 input with a fused layer norm.
 template <int MT, bool LN>
@@ -58,7 +70,6 @@ __global__ void __launch_bounds__(kWarps * 32, 3)
 linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gamma, const float* __restrict__ beta,
                      float eps, const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
                      const float* residual, void* out, int M, int N, int K, int act, int out_f32, int k_split) {
-  constexpr int U = kDepth;
   constexpr int kTile = 16 * 8 * MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -70,29 +81,27 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   const int per_block = (all_steps + k_split - 1) / k_split;
   const int step_lo = rank * per_block, step_hi = min(all_steps, step_lo + per_block);
   const int k_lo = step_lo * 32;
-  // shared memory: [red: kWarps x kTile][gather: k_split x kTile][xs: M x ldx bf16 (LN only)]
-  float* red = reinterpret_cast<float*>(smem_raw);
+  const int ldw = tile_stride(per_block);
+  // shared memory: [wt: 16 x ldw bf16][red: kWarps x kTile][gather: k_split x kTile][stats: 2 x 16]
+  __nv_bfloat16* wt = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  float* red = reinterpret_cast<float*>(wt + 16 * ldw);
   float* gather = red + kWarps * kTile;
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(gather + k_split * kTile);
-  const int ldx = per_block * 32 + 8;
+  float* stats = gather + k_split * kTile;
 
-  // weight rows of this lane; rows past N read row N-1 and are dropped at the end
-  const __nv_bfloat16* w_lo = W + (size_t)min(row0 + g, N - 1) * K + c * 8;
-  const __nv_bfloat16* w_hi = W + (size_t)min(row0 + g + 8, N - 1) * K + c * 8;
-
-  // The first weight slices are asked for before anything else: they do not depend on the kernel
-  // before this one, whose completion is awaited only after that.
-  uint4 wl[U], wh[U];
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-    const int s = step_lo + warp + u * kWarps;
-    const bool ok = s < step_hi && s * 32 + c * 8 < K;
-    wl[u] = ok ? ldg_stream(w_lo + s * 32) : make_uint4(0, 0, 0, 0);
-    wh[u] = ok ? ldg_stream(w_hi + s * 32) : make_uint4(0, 0, 0, 0);
+  // The block's whole share of the matrix is asked for before anything else: it does not depend
+  // on the kernel before this one, whose completion is awaited only after that.
+  {
+    const int chunks = (step_hi - step_lo) * 4;  // 16-byte chunks per row
+    for (int i = threadIdx.x; i < 16 * chunks; i += kWarps * 32) {
+      const int r = i / chunks, ch = i % chunks;
+      const int k = k_lo + ch * 8;
+      const int row = min(row0 + r, N - 1);  // rows past N repeat the last row and are dropped at the end
+      cp_async_16(wt + r * ldw + ch * 8, W + (size_t)row * K + min(k, K - 8), k < K);
+    }
+    asm volatile("cp.async.commit_group;\n" ::);
   }
   if (LN) {
-    // the norm's gain and bias are constants too: bring their lines into L1 now, so that the third
-    // pass over a row finds them there
+    // the norm's gain and bias are constants too: bring their lines into L1 now
     const int lines = (K * (int)sizeof(float) + 127) / 128;
     for (int i = threadIdx.x; i < 2 * lines; i += kWarps * 32) {
       const float* p = (i < lines ? gamma : beta) + (size_t)(i % lines) * 32;
@@ -102,21 +111,6 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   pdl_trigger();
   pdl_wait();
 
-  uint4 xb[LN ? 1 : U][MT];
-  if (!LN) {
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int s = step_lo + warp + u * kWarps;
-      const int k = s * 32 + c * 8;
-#pragma unroll
-      for (int t = 0; t < MT; ++t) {
-        const int m = t * 8 + g;
-        xb[u][t] = (s < step_hi && k < K && m < M)
-                       ? *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)m * K + k)
-                       : make_uint4(0, 0, 0, 0);
-      }
-    }
-  }
   // the element of the output tile that this thread finishes (block 0 of the cluster only)
   const int e_r = threadIdx.x % 16, e_m = threadIdx.x / 16;
   const int e_n = row0 + e_r;
@@ -126,53 +120,59 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
 
   if (LN) {
     const float* x = static_cast<const float*>(xin);
-    const int k_hi = min(K, step_hi * 32);
-    // One warp per row: mean, then biased variance over the whole row, then this block's slice of
-    // the normalised row in bfloat16.  The row is read three times; after the first from L1.
+    // One warp per row: mean, then biased variance, over the whole row.  A row of up to 2048
+    // values is read once into registers, all its loads in flight together (one trip to L2);
+    // longer rows are read twice in pieces.
     for (int m = warp; m < M; m += kWarps) {
-      __nv_bfloat16* dst = xs + m * ldx;
       const float* r = x + (size_t)m * K;
-      float mean, inv;
-      if ((K & 3) == 0) {
-        const int nv = K >> 2;
-        const float4* r4 = reinterpret_cast<const float4*>(r);
+      const int nv = K >> 2;
+      const float4* r4 = reinterpret_cast<const float4*>(r);
+      float mean, var;
+      if (nv <= 32 * kRowVecs) {
+        float4 v[kRowVecs];
         float sum = 0.f;
-#pragma unroll 4
+#pragma unroll
+        for (int j = 0; j < kRowVecs; ++j) {
+          const int i = lane + 32 * j;
+          v[j] = i < nv ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < kRowVecs; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        mean = warp_sum(sum) / (float)K;
+        float sq = 0.f;
+#pragma unroll
+        for (int j = 0; j < kRowVecs; ++j) {
+          if (lane + 32 * j < nv) {
+            const float a0 = v[j].x - mean, a1 = v[j].y - mean, a2 = v[j].z - mean, a3 = v[j].w - mean;
+            sq += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+          }
+        }
+        var = warp_sum(sq) / (float)K;
+      } else {
+        float sum = 0.f;
+#pragma unroll 8
         for (int i = lane; i < nv; i += 32) {
           const float4 v = r4[i];
           sum += (v.x + v.y) + (v.z + v.w);
         }
         mean = warp_sum(sum) / (float)K;
         float sq = 0.f;
-#pragma unroll 4
+#pragma unroll 8
         for (int i = lane; i < nv; i += 32) {
           const float4 v = r4[i];
           const float a0 = v.x - mean, a1 = v.y - mean, a2 = v.z - mean, a3 = v.w - mean;
           sq += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
         }
-        inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + eps);
-      } else {
-        float sum = 0.f;
-        for (int i = lane; i < K; i += 32) sum += r[i];
-        mean = warp_sum(sum) / (float)K;
-        float sq = 0.f;
-        for (int i = lane; i < K; i += 32) {
-          const float dlt = r[i] - mean;
-          sq += dlt * dlt;
-        }
-        inv = 1.0f / sqrtf(warp_sum(sq) / (float)K + eps);
+        var = warp_sum(sq) / (float)K;
       }
-      // k_lo is a multiple of 32 and K of 8, so the slice is whole groups of 4
-      for (int i = k_lo + lane * 4; i < k_hi; i += 128) {
-        const float4 v = *reinterpret_cast<const float4*>(r + i);
-        const float4 gm = *reinterpret_cast<const float4*>(gamma + i), bt = *reinterpret_cast<const float4*>(beta + i);
-        __nv_bfloat162* d2 = reinterpret_cast<__nv_bfloat162*>(dst + (i - k_lo));
-        d2[0] = __floats2bfloat162_rn((v.x - mean) * inv * gm.x + bt.x, (v.y - mean) * inv * gm.y + bt.y);
-        d2[1] = __floats2bfloat162_rn((v.z - mean) * inv * gm.z + bt.z, (v.w - mean) * inv * gm.w + bt.w);
+      if (lane == 0) {
+        stats[2 * m] = mean;
+        stats[2 * m + 1] = 1.0f / sqrtf(var + eps);
       }
     }
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_all;\n" ::: "memory");
+  __syncthreads();
 
   float acc[MT][4];
 #pragma unroll
@@ -180,43 +180,33 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
 
-  for (int s0 = step_lo + warp; s0 < step_hi; s0 += U * kWarps) {
+#pragma unroll 2
+  for (int s = step_lo + warp; s < step_hi; s += kWarps) {
+    const int k = s * 32 + c * 8;
+    const bool ok = k < K;
+    const uint4 a_lo = *reinterpret_cast<const uint4*>(wt + g * ldw + (k - k_lo));
+    const uint4 a_hi = *reinterpret_cast<const uint4*>(wt + (g + 8) * ldw + (k - k_lo));
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int s = s0 + u * kWarps;
-      const int k = s * 32 + c * 8;
-      const uint4 a_lo = wl[u], a_hi = wh[u];
-      uint4 b[MT];
-#pragma unroll
-      for (int t = 0; t < MT; ++t) {
-        if (LN)
-          b[t] = (s < step_hi && k < K && t * 8 + g < M)
-                     ? *reinterpret_cast<const uint4*>(xs + (t * 8 + g) * ldx + (k - k_lo))
-                     : make_uint4(0, 0, 0, 0);
-        else
-          b[t] = xb[u][t];
-      }
-      // refill this slot with the slice U rounds ahead
-      const int sn = s + U * kWarps;
-      const int kn = sn * 32 + c * 8;
-      const bool okn = sn < step_hi && kn < K;
-      wl[u] = okn ? ldg_stream(w_lo + sn * 32) : make_uint4(0, 0, 0, 0);
-      wh[u] = okn ? ldg_stream(w_hi + sn * 32) : make_uint4(0, 0, 0, 0);
-      if (!LN) {
-#pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          const int m = t * 8 + g;
-          xb[u][t] = (okn && m < M)
-                         ? *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)m * K + kn)
-                         : make_uint4(0, 0, 0, 0);
+    for (int t = 0; t < MT; ++t) {
+      const int m = t * 8 + g;
+      uint4 b = make_uint4(0, 0, 0, 0);
+      if (ok && m < M) {
+        if (LN) {
+          const float* r = static_cast<const float*>(xin) + (size_t)m * K + k;
+          const float4 v0 = *reinterpret_cast<const float4*>(r), v1 = *reinterpret_cast<const float4*>(r + 4);
+          const float4 g0 = *reinterpret_cast<const float4*>(gamma + k), g1 = *reinterpret_cast<const float4*>(gamma + k + 4);
+          const float4 b0 = *reinterpret_cast<const float4*>(beta + k), b1 = *reinterpret_cast<const float4*>(beta + k + 4);
+          const float mean = stats[2 * m], inv = stats[2 * m + 1];
+          b.x = pack2((v0.x - mean) * inv * g0.x + b0.x, (v0.y - mean) * inv * g0.y + b0.y);
+          b.y = pack2((v0.z - mean) * inv * g0.z + b0.z, (v0.w - mean) * inv * g0.w + b0.w);
+          b.z = pack2((v1.x - mean) * inv * g1.x + b1.x, (v1.y - mean) * inv * g1.y + b1.y);
+          b.w = pack2((v1.z - mean) * inv * g1.z + b1.z, (v1.w - mean) * inv * g1.w + b1.w);
+        } else {
+          b = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)m * K + k);
         }
       }
-      if (s >= step_hi) continue;  // uniform across the warp
-#pragma unroll
-      for (int t = 0; t < MT; ++t) {
-        mma_bf16(acc[t], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b[t].x, b[t].y);
-        mma_bf16(acc[t], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b[t].z, b[t].w);
-      }
+      mma_bf16(acc[t], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+      mma_bf16(acc[t], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
     }
   }
 
@@ -261,15 +251,17 @@ int launch(const void* xin, const float* gamma, const float* beta, float eps, co
            const float* residual, void* out, int M, int N, int K, int act, int out_dtype, cudaStream_t stream) {
   const int tiles = (N + 15) / 16;
   const int all_steps = (K + 31) / 32;
-  // split K over a cluster while the blocks still fit the chip at once (three to an SM) and each
-  // block keeps at least two slices per warp
+  // Split K over a cluster (1, 2 or 4 blocks) so that a block's share of the matrix fits the
+  // shared memory three blocks can have on an SM (about 56 KB of weights each), and further while
+  // the blocks still fit the chip at once and keep at least two slices per warp.
   int k_split = 1;
+  while (k_split < 4 && all_steps / k_split > 54) k_split *= 2;
   while (k_split < 4 && tiles * k_split * 2 <= 3 * 148 && all_steps / (k_split * 2) >= 2 * kWarps) k_split *= 2;
   const int per_block = (all_steps + k_split - 1) / k_split;
-  size_t smem = (size_t)(kWarps + k_split) * 16 * 8 * MT * sizeof(float);
-  if (LN) smem += (size_t)M * (per_block * 32 + 8) * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)16 * tile_stride(per_block) * sizeof(__nv_bfloat16) +
+                      (size_t)(kWarps + k_split) * 16 * 8 * MT * sizeof(float) + 2 * 16 * sizeof(float);
   if (smem > 200 * 1024)
-    return ember_fail("linear_decode: a fused norm over K = %d needs %zu bytes of shared memory", K, smem);
+    return ember_fail("linear_decode: K = %d needs %zu bytes of shared memory per block", K, smem);
   static size_t configured = 0;
   if (smem > 48 * 1024 && smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(linear_decode_kernel<MT, LN>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -123,7 +123,9 @@ def test_linear_few_rows_streams_the_weights(ops, M, N, K, act, with_bias, with_
 @pytest.mark.parametrize("M, N, K", [(1, 4800, 1600), (7, 100, 96), (16, 1000, 64), (11, 320, 2056), (4, 64, 4104)])
 def test_linear_with_the_norm_in_its_prologue(ops, M, N, K):
     """The layer norm run inside the product's kernel gives what the separate kernel gives."""
-    from ember_cpp_b200.csrc.ops import LazyNorm
+    from ember_cpp_b200.csrc.ops import CudaOps, LazyNorm
+    ops = CudaOps()
+    ops.fuse_norm = True          # off by default: a separate norm kernel measured faster
     x = gen((M, K), 34) * 2 + 0.5
     gw, gb = gen((K,), 35) * 0.1 + 1, gen((K,), 36) * 0.1
     w, bias = gen((N, K), 37, torch.bfloat16, 0.1), gen((N,), 38)
