@@ -22,6 +22,8 @@
 namespace {
 
 constexpr int kThreads = 128;
+constexpr int kUnroll = 4;          // keys a stream has in flight
+constexpr int kMaxChunkPages = 64;  // page numbers of a chunk kept in shared memory
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -33,8 +35,30 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float* f) {
   }
 }
 
+// One key (its 16-byte part of K and of V) folded into a stream's running softmax.
+template <int LPK>
+__device__ __forceinline__ void fold_key(const uint4& kraw, const uint4& vraw, bool have, const float (&q)[8], float scale,
+                                         float& m, float& l, float (&acc)[8]) {
+  float k[8], v[8];
+  unpack8(kraw, k);
+  unpack8(vraw, v);
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) dot = fmaf(q[i], k[i], dot);
+#pragma unroll
+  for (int off = LPK / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+  const float sc = have ? dot * scale : -INFINITY;
+  const float m_new = fmaxf(m, sc);
+  const float corr = m_new == -INFINITY ? 0.f : __expf(m - m_new);
+  const float pj = m_new == -INFINITY ? 0.f : __expf(sc - m_new);
+  l = l * corr + pj;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = fmaf(pj, v[i], acc[i] * corr);
+  m = m_new;
+}
+
 template <int LPK>  // lanes per key; each lane owns 8 consecutive dims
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 8)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ kc,
                         const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ part_ml, float* __restrict__ part_acc, int* __restrict__ counters,
@@ -48,13 +72,19 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   __shared__ float s_acc[kStreams][LPK * 8 + 1];
   __shared__ float s_w[kStreams];
   __shared__ int s_last;
+  __shared__ int s_pages[kMaxChunkPages];
 
+  // Before waiting for the kernel in front (which makes this step's q, k and v), everything that
+  // does not depend on it is fetched: the step's description, which the host wrote before the
+  // step began, and the cached keys and values of earlier positions, which earlier steps wrote.
   pdl_trigger();
-  pdl_wait();
+  // One token per sequence: token t is sequence t of the step (how a one-token-each step is laid
+  // out), which spares a dependent load.
   const int c = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
-  const int s = token_seq[t];
+  const int s = t;
   __nv_bfloat16* o = out + ((size_t)t * n_heads + h) * hd;
   if (seq_slot[s] < 0) {  // padding: a defined output, nothing read
+    pdl_wait();
     if (c == 0)
       for (int d = threadIdx.x; d < hd; d += kThreads) o[d] = __float2bfloat16_rn(0.f);
     return;
@@ -64,17 +94,65 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   const int chunk_keys = pages_per_chunk * kPage;
   const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
   if (c < first_chunk || c > last_chunk) return;
-  const int begin = max(lo, c * chunk_keys), end = min(p + 1, (c + 1) * chunk_keys);
+  const bool own = k_store != nullptr && c == last_chunk;  // this block also takes the token's own key
+  // cached keys of this chunk: [begin, end); the token's own position is not among them when this
+  // launch stores it (it is taken from the step's activations instead)
+  const int begin = max(lo, c * chunk_keys);
+  const int end = min(k_store ? p : p + 1, (c + 1) * chunk_keys);
   const int kvh = h / (n_heads / kv_heads);
   const int width = (n_heads + 2 * kv_heads) * hd;
-  if (k_store && c == last_chunk) {
-    // The token's own key and value go into the cache here (no separate launch): the block that
-    // reads position p writes it first.  Blocks of other heads of the same group write the same
-    // bytes.
-    const int page = pages[(size_t)s * max_blocks + p / kPage];
+  const int* my_pages = pages + (size_t)s * max_blocks;
+  const bool cached_pages = pages_per_chunk <= kMaxChunkPages;
+  if (cached_pages)
+    for (int i = threadIdx.x; i < pages_per_chunk; i += kThreads) {
+      const int blk = c * pages_per_chunk + i;
+      s_pages[i] = blk < max_blocks ? my_pages[blk] : -1;
+    }
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sid = warp * kGroups + lane / LPK, sub = lane % LPK;
+  const bool dims = sub * 8 < hd;
+
+  uint4 kraw[kUnroll], vraw[kUnroll];
+  bool have[kUnroll];
+  auto fetch = [&](int j0) {
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int j = j0 + u * kStreams + sid;
+      int page = -1;
+      if (j < end) page = cached_pages ? s_pages[j / kPage - c * pages_per_chunk] : my_pages[j / kPage];
+      have[u] = page >= 0;
+      kraw[u] = make_uint4(0, 0, 0, 0);
+      vraw[u] = make_uint4(0, 0, 0, 0);
+      if (dims && have[u]) {
+        const size_t row = (((size_t)page * kv_heads + kvh) * kPage + (j % kPage)) * hd + sub * 8;
+        kraw[u] = *reinterpret_cast<const uint4*>(kc + row);
+        vraw[u] = *reinterpret_cast<const uint4*>(vc + row);
+      }
+    }
+  };
+  // A cache that this launch stores into holds, below p, only rows of earlier steps: they can be
+  // fetched while the kernels in front finish.  A cache that another layer stored into earlier in
+  // this same step (this launch only reads it) may not be touched before the wait: kernels that
+  // were launched this way can be several deep in their waits.
+  if (!k_store) pdl_wait();
+  fetch(begin);
+  if (k_store) pdl_wait();
+
+  float q[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) q[i] = 0.f;
+  if (dims) unpack8(*reinterpret_cast<const uint4*>(qkv + (size_t)t * width + (size_t)h * hd + sub * 8), q);
+  uint4 own_k = make_uint4(0, 0, 0, 0), own_v = make_uint4(0, 0, 0, 0);
+  if (own) {
+    // The token's own key and value: from the step's activations into the cache (no separate
+    // launch; blocks of other heads of the same group write the same bytes; nothing in this launch
+    // reads the row), and into stream 0 of this block.
+    const __nv_bfloat16* src = qkv + (size_t)t * width + (size_t)(n_heads + kvh) * hd;
+    const int page = my_pages[p / kPage];
     if (page >= 0) {
       const size_t dst = (((size_t)page * kv_heads + kvh) * kPage + (p % kPage)) * hd;
-      const __nv_bfloat16* src = qkv + (size_t)t * width + (size_t)(n_heads + kvh) * hd;
       const int vecs = hd / 8;
       for (int i = threadIdx.x; i < 2 * vecs; i += kThreads) {
         const bool is_v = i >= vecs;
@@ -83,52 +161,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
         *reinterpret_cast<uint4*>((is_v ? v_store : k_store) + dst + j) = val;
       }
     }
-    __syncthreads();
+    if (sid == 0 && dims) {
+      own_k = *reinterpret_cast<const uint4*>(src + sub * 8);
+      own_v = *reinterpret_cast<const uint4*>(src + kv_heads * hd + sub * 8);
+    }
   }
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sid = warp * kGroups + lane / LPK, sub = lane % LPK;
-  const bool dims = sub * 8 < hd;
-  const int g = kvh;
-  const int qkv_width = width;
-  const int* my_pages = pages + (size_t)s * max_blocks;
-
-  float q[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = 0.f;
-  if (dims) unpack8(*reinterpret_cast<const uint4*>(qkv + (size_t)t * qkv_width + (size_t)h * hd + sub * 8), q);
 
   float m = -INFINITY, l = 0.f, acc[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i] = 0.f;
 
-  // every lane of a warp makes the same number of trips (the shuffles below name all 32 lanes)
-  for (int j0 = begin; j0 < end; j0 += kStreams) {
-    const int j = j0 + sid;
-    const int page = j < end ? my_pages[j / kPage] : -1;
-    const size_t row = (((size_t)max(page, 0) * kv_heads + g) * kPage + (j % kPage)) * hd + sub * 8;
-    float k[8], v[8];
-    uint4 kraw = make_uint4(0, 0, 0, 0), vraw = make_uint4(0, 0, 0, 0);
-    if (dims && page >= 0) {
-      kraw = *reinterpret_cast<const uint4*>(kc + row);
-      vraw = *reinterpret_cast<const uint4*>(vc + row);
-    }
-    unpack8(kraw, k);
-    unpack8(vraw, v);
-    float dot = 0.f;
+  // Every lane of a warp makes the same number of trips (the shuffles name all 32 lanes).  A trip
+  // takes kUnroll keys per stream: their loads are issued together, then they are folded into the
+  // stream's running softmax one after the other.
+  for (int j0 = begin; j0 < end; j0 += kUnroll * kStreams) {
+    if (j0 != begin) fetch(j0);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) dot = fmaf(q[i], k[i], dot);
-#pragma unroll
-    for (int off = LPK / 2; off > 0; off >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
-    const float sc = page >= 0 ? dot * scale : -INFINITY;
-    const float m_new = fmaxf(m, sc);
-    const float corr = m_new == -INFINITY ? 0.f : __expf(m - m_new);
-    const float pj = m_new == -INFINITY ? 0.f : __expf(sc - m_new);
-    l = l * corr + pj;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = fmaf(pj, v[i], acc[i] * corr);
-    m = m_new;
+    for (int u = 0; u < kUnroll; ++u) fold_key<LPK>(kraw[u], vraw[u], have[u], q, scale, m, l, acc);
   }
+  if (own && warp == 0) fold_key<LPK>(own_k, own_v, sid == 0, q, scale, m, l, acc);  // all of warp 0: its shuffles are whole-warp
 
   // merge the block's streams
   if (sub == 0) {

@@ -101,7 +101,7 @@ class CudaOps:
         self._counters = None          # ... and its per-(token, head) counters, zero between calls
         self._retired = []             # outgrown scratch stays alive: captured graphs may still name it
         self.launches = 0
-        self.decode_ctas = 6000        # blocks the decode attention aims for (about four waves of 148 SMs x 10)
+        self.decode_ctas = 4800        # blocks the decode attention aims for (about four waves of 148 SMs x 8)
         # Run a layer norm inside the following product's kernel when it can be.  Off: measured on
         # GPT-2 XL's shapes a separate norm kernel, overlapped with the product's weight fetch by
         # programmatic dependent launch, is faster (23.8 against 30.8 microseconds a layer at 8 rows).
@@ -251,7 +251,9 @@ class CudaOps:
         pages = plan.pages[cache.group_index]
         if qkv.dtype == torch.bfloat16 and plan.all_single:
             blocks = min(plan.max_blocks, max(1, -(-plan.max_end // 64)))
-            per_chunk = max(1, min(blocks, plan.T * n_heads * blocks // self.decode_ctas))
+            # at least two pages a chunk (a block's fixed costs are then shared by 128 keys), more while
+            # the launch still has several waves of blocks
+            per_chunk = max(min(2, blocks), min(blocks, plan.T * n_heads * blocks // self.decode_ctas))
             n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
             partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
             self._call("ember_attention_decode", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
