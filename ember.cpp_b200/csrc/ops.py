@@ -86,6 +86,13 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = _c_int
+    lib.ember_attention_decode_partials.argtypes = [_c_int] * 5
+    lib.ember_attention_decode_partials.restype = _c_size
+    for name in ("ember_decode_program_op_size", "ember_decode_program_state_size"):
+        getattr(lib, name).argtypes = []
+        getattr(lib, name).restype = _c_int
+    lib.ember_decode_program_run.argtypes = [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void]
+    lib.ember_decode_program_run.restype = _c_int
     lib._path = path
     return lib
 

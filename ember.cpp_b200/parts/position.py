@@ -11,6 +11,8 @@ from .base import Position, WeightSpec, register_part
 
 
 class LearnedAbsolute(Position):
+    ops_only = True
+
     def __init__(self, prefix: str, width: int, n_positions: int, table: str = "weight", init_std: float = 0.02):
         super().__init__(prefix)
         self.width, self.n_positions = int(width), int(n_positions)
@@ -32,6 +34,8 @@ class LearnedAbsolute(Position):
 
 
 class NoPosition(Position):
+    ops_only = True
+
     def __init__(self, prefix: str = ""):
         super().__init__(prefix)
 

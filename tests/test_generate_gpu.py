@@ -95,6 +95,24 @@ def test_padding_changes_no_result(engines, plains, dtype):
             assert rel_error(alone[0], got) < TOL[dtype]
 
 
+@pytest.mark.parametrize("name", NAMES)
+def test_one_launch_decode_program_equals_the_graph(tiny_folders, plains, name):
+    """The persistent decode kernel (a recorded step run as one launch) against the replayed graph
+    and the plain implementation: unequal batches, padding, a sequence that leaves early."""
+    plain = plains[name]
+    seqs = [random_ids(450 + i, plain.vocab, n) for i, n in enumerate((plain.n_positions, 40, 70))]
+    out = []
+    for programs in (True, False):
+        eng = Engine.from_folder(tiny_folders[name], dtype="bfloat16", max_tokens=1024, decode_programs=programs)
+        assert eng.decode_programs == programs
+        out.append(run_batch(eng, seqs, (10, 1, 30))[0])
+        if programs:
+            assert eng._programs and not eng._graphs
+    for ids, a, b in zip(seqs, *out):
+        assert rel_error(a, plain.logits(ids)) < TOL["bfloat16"]
+        assert rel_error(a, b) < TOL["bfloat16"]
+
+
 def test_graph_replay_equals_launch_by_launch(tiny_folders, plains):
     plain = plains["tiny_a"]
     seqs = [random_ids(400 + i, plain.vocab, 50) for i in range(3)]
