@@ -450,6 +450,7 @@ decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* b
   float* attn = red + kWarps * 16 * 8 * MT;                                          // [2][kAttnScratchFloats]
   float* rows = attn + 2 * kAttnScratchFloats;                                       // [kWarps]
 
+  unsigned long long t_start = 0;
   Cursor staged = first_piece(ops, n_ops, 0);
   int staged_buf = 0;
   if (staged.op < n_ops) stage_piece(ops[staged.op], staged, wbuf);
@@ -457,6 +458,12 @@ decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* b
     const EmberOp& op = ops[i];
     if (trace && threadIdx.x == 0) {  // a debugging aid: the operation each block has reached (host-visible memory)
       trace[blockIdx.x] = i + 1;
+      if (blockIdx.x == 0 && i < 768) {  // and when block 0 began it, in nanoseconds since the kernel started
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (i == 0) t_start = now;
+        trace[256 + i] = (int)(now - t_start);
+      }
       __threadfence_system();
     }
     if (op.type == EMBER_OP_LINEAR) run_linear<MT>(ops, n_ops, i, staged, staged_buf, wbuf, buf_elems, red);
@@ -489,9 +496,9 @@ EMBER_API int ember_decode_program_state_size() { return (int)sizeof(GridBarrier
 // state; `error`: one int on the device, zero before the run, non-zero afterwards if a block gave
 // up waiting at a barrier (1) or an index of the step's description was out of range (2); the
 // results are then not valid.
-// `trace`: null, or one int per SM in memory the host can read (pinned and mapped): each block
+// `trace`: null, or 1,024 ints in memory the host can read (pinned and mapped): each block
 // writes there the number of the operation it has reached (1-based; -1 once it has left), which
-// is still readable after a fault.
+// is still readable after a fault; from entry 256 on, the time at which block 0 began each operation.
 EMBER_API int ember_decode_program_run(const void* ops, int n_ops, int max_rows, void* state, int* error, int* trace,
                                        cudaStream_t stream) {
   EMBER_CHECK(n_ops > 0 && max_rows > 0 && max_rows <= 16, "decode_program: %d operations for %d rows", n_ops, max_rows);
