@@ -12,6 +12,7 @@ bfloat16 operands take the tensor-core kernels.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -31,6 +32,7 @@ _SIGNATURES = {
     "ember_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_bf16": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_void, _c_size, _c_void],
+    "ember_linear_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_void],
     "ember_kv_store": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
@@ -50,6 +52,7 @@ class KernelError(RuntimeError):
 
 
 SMALL_M = 16          # rows up to which the weight-streaming product is used instead of the library's
+TC_MIN_M = 64         # rows above which the tcgen05 product is used (its tiles have 128 rows)
 
 
 class LazyNorm:
@@ -93,6 +96,8 @@ def load_library() -> ctypes.CDLL:
         getattr(lib, name).restype = _c_int
     lib.ember_decode_program_run.argtypes = [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void]
     lib.ember_decode_program_run.restype = _c_int
+    lib.ember_linear_tc_status.argtypes = []
+    lib.ember_linear_tc_status.restype = _c_int
     lib._path = path
     return lib
 
@@ -113,6 +118,13 @@ class CudaOps:
         # GPT-2 XL's shapes a separate norm kernel, overlapped with the product's weight fetch by
         # programmatic dependent launch, is faster (23.8 against 30.8 microseconds a layer at 8 rows).
         self.fuse_norm = False
+        # Products of more than SMALL_M rows go to cuBLASLt ("lt"), as ember.cpp's own go to cuBLAS, or
+        # with EMBER_GEMM=tc in the environment, above TC_MIN_M rows, to this library's tcgen05 kernel.
+        # Measured on GPT-2 XL's four products the library is ahead: at 2,048 rows 133 against 205
+        # microseconds a layer, at 16,384 rows the tcgen05 kernel reaches 87 % of it on the QKV product.
+        self.gemm = os.environ.get("EMBER_GEMM", "lt")
+        if self.gemm not in ("tc", "lt"):
+            raise KernelError(f"EMBER_GEMM={self.gemm!r}: 'tc' (this library's tcgen05 kernel) or 'lt' (cuBLASLt)")
 
     # ------------------------------------------------------------------ helpers
     def _call(self, name: str, *args, allow=()) -> int:
@@ -227,6 +239,8 @@ class CudaOps:
             return out
         if norm is not None:
             a = norm.materialize()
+        if self.gemm == "tc" and M > TC_MIN_M and K % 8 == 0:
+            return self.linear_tc(a, w, bias, act, residual, out)
         fused = _ACT[act] if act != "gelu_erf" else 0
         ws = self._lt_workspace()
         self._call("ember_linear_bf16", a.data_ptr(), w.data_ptr(), self._ptr(bias),
@@ -235,6 +249,21 @@ class CudaOps:
         if act == "gelu_erf":
             self._call("ember_act_inplace", out.data_ptr(), out.numel(), _ACT[act], _code(target))
         return out
+
+    def linear_tc(self, a, w, bias, act, residual, out, tile_n: int = 0):
+        """The tcgen05 product with its epilogue (bias, activation, float32 residual sum) into `out`."""
+        M, K = a.shape
+        self._call("ember_linear_tc", a.data_ptr(), w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(),
+                   M, w.shape[0], K, _ACT[act], _code(out.dtype), tile_n)
+        return out
+
+    def check(self) -> None:
+        """Raises if a kernel with bounded waits gave up since the last call.  The caller has
+        synchronized with the device (it has just read a step's results)."""
+        code = self.lib.ember_linear_tc_status()
+        if code:
+            role = {1: "the TMA producer", 2: "the product issuer", 3: "the epilogue", 4: "copies in flight"}.get(code, code)
+            raise KernelError(f"linear_tc: a wait ran out ({role}); the results of that launch are not valid")
 
     # ------------------------------------------------------------------ cache and attention
     def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):

@@ -113,6 +113,25 @@ def test_one_launch_decode_program_equals_the_graph(tiny_folders, plains, name):
         assert rel_error(a, b) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("name", NAMES)
+def test_prompts_through_the_tcgen05_products(tiny_folders, plains, name):
+    """Whole prompts with the library's own tcgen05 matrix products in place of cuBLASLt: batches of
+    more than 64 tokens (one tile of 128 rows cut off, and two blocks sharing a 256-row tile), both
+    GELU forms, the residual sums and the float32 head."""
+    plain = plains[name]
+    eng = Engine.from_folder(tiny_folders[name], dtype="bfloat16", max_tokens=1024)
+    eng.ops.gemm = "tc"
+    P = plain.n_positions
+    seqs = [random_ids(460 + i, plain.vocab, n) for i, n in enumerate((P, P - 7, 70))]
+    rows, _ = run_batch(eng, seqs, (P, P - 7, 66))
+    eng.ops.check()
+    for ids, got in zip(seqs, rows):
+        assert rel_error(got, plain.logits(ids)) < TOL["bfloat16"]
+    alone, _ = run_batch(eng, [seqs[0]], (P,))
+    eng.ops.check()
+    assert rel_error(alone[0], plain.logits(seqs[0])) < TOL["bfloat16"]
+
+
 def test_graph_replay_equals_launch_by_launch(tiny_folders, plains):
     plain = plains["tiny_a"]
     seqs = [random_ids(400 + i, plain.vocab, 50) for i in range(3)]

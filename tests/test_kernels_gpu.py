@@ -120,6 +120,39 @@ def test_linear_few_rows_streams_the_weights(ops, M, N, K, act, with_bias, with_
     assert (got.double() - want).abs().max().item() / scale < (2e-4 if out == "float32" else 2 ** -7)
 
 
+@pytest.mark.parametrize("M, N, K, tile_n", [(128, 64, 64, 0), (200, 1600, 1600, 0), (129, 1001, 72, 0), (65, 48, 4104, 16),
+                                             (300, 500, 200, 48), (1000, 777, 136, 256), (2048, 4800, 1600, 0),
+                                             (257, 6400, 320, 208)])
+@pytest.mark.parametrize("act, with_bias, with_res, out", [(None, True, False, "bfloat16"), ("gelu_tanh", True, False, "bfloat16"),
+                                                           ("gelu_erf", False, False, "bfloat16"), (None, True, True, "float32"),
+                                                           (None, False, False, "float32")])
+def test_linear_on_the_tcgen05_kernel(ops, M, N, K, tile_n, act, with_bias, with_res, out):
+    """The TMA-fed tcgen05 product with its epilogue: tiles cut off in M, N and K, every tile
+    width class (the narrowest, one that is no power of two, the widest), more tiles than SMs so
+    that blocks walk several tiles and both accumulators, and a width that is no multiple of 8."""
+    a, w = gen((M, K), 50, torch.bfloat16), gen((N, K), 51, torch.bfloat16, 0.1)
+    bias = gen((N,), 52) if with_bias else None
+    res = gen((M, N), 53) if with_res else None
+    want = linear_ref(a, w, bias, act, res)
+    got = res.clone() if with_res else torch.full((M, N), float("nan"), dtype=DT[out], device="cuda")
+    ops.linear_tc(a, w, bias, act, got if with_res else None, got, tile_n=tile_n)
+    torch.cuda.synchronize()
+    ops.check()
+    scale = want.abs().max().item() + 1e-6
+    assert (got.double() - want).abs().max().item() / scale < (2e-4 if out == "float32" else 2 ** -7)
+
+
+def test_linear_routes_large_products_to_the_tcgen05_kernel_when_asked(ops, monkeypatch):
+    a, w = gen((130, 64), 54, torch.bfloat16), gen((96, 64), 55, torch.bfloat16, 0.1)
+    seen = []
+    monkeypatch.setattr(ops, "linear_tc", lambda *args, **kw: seen.append(1) or args[5])
+    ops.linear(a, w, None)
+    assert seen == []
+    monkeypatch.setattr(ops, "gemm", "tc")
+    ops.linear(a, w, None)
+    assert seen == [1]
+
+
 @pytest.mark.parametrize("M, N, K", [(1, 4800, 1600), (7, 100, 96), (16, 1000, 64), (11, 320, 2056), (4, 64, 4104)])
 def test_linear_with_the_norm_in_its_prologue(ops, M, N, K):
     """The layer norm run inside the product's kernel gives what the separate kernel gives."""
