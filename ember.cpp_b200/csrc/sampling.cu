@@ -179,6 +179,107 @@ __device__ u64 radix_select(const Row& row, int V, bool by_mass, u64 need, unsig
   return prefix;
 }
 
+
+constexpr int kSmallK = 512;   // top_k up to which the candidates are finished as a short list
+constexpr int kListCap = 1024;  // entries of that list
+
+// The short way for a small top_k.  Radix passes by count run only until the candidates that can
+// still be among the top_k (those above the chosen bucket, fewer than top_k, and the bucket itself)
+// number at most kListCap; these are gathered into a list and finished there: each one's rank and
+// the mass above it by comparison with all others, the kept set (rank < top_k, and the mass above
+// it short of the top_p target: the same set as the two radix selections give), and the draw in
+// index order.  Integer masses make every sum independent of the list's order.  Returns false
+// (having written nothing) when the list would not fit, which takes a bucket of hundreds of
+// candidates with the same leading digits on every level.
+__device__ bool sample_small(const Row& row, int V, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
+                             unsigned* cnt, u64* list, u64* scratch, int* s_hit, u64* s_before, int* s_n) {
+  const int shifts[6] = {53, 42, 32, 21, 10, 0};
+  const int widths[6] = {11, 11, 10, 11, 11, 10};
+  u64 prefix = 0, need = (u64)top_k, above = 0;
+  bool fits = false;
+  for (int pass = 0; pass < 6 && !fits; ++pass) {
+    const int shift = shifts[pass];
+    if (pass >= 3 && ((u64)(V - 1) >> shift) == 0 && shift > 0) continue;
+    const u64 high_mask = pass == 0 ? 0ull : ~0ull << (shift + widths[pass]);
+    const unsigned digit_mask = (1u << widths[pass]) - 1;
+    for (int b = threadIdx.x; b < kBins; b += kThreads) cnt[b] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += kThreads) {
+      const u64 key = key_of(row.p(i), i);
+      if ((key & high_mask) == prefix) {
+        const int b = (int)((key >> shift) & digit_mask);
+        const unsigned peers = __match_any_sync(__activemask(), b);
+        if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[b], (unsigned)__popc(peers));
+      }
+    }
+    __syncthreads();
+    const Pick pick = find_bucket(cnt, nullptr, false, need, scratch, s_hit, s_before);
+    prefix |= (u64)pick.bin << shift;
+    if (pick.none) return false;  // fewer candidates than top_k: not this function's case
+    need -= pick.before;
+    above += pick.before;
+    fits = above + pick.count <= (u64)kListCap;
+  }
+  if (!fits) return false;
+  if (threadIdx.x == 0) *s_n = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += kThreads) {
+    const u64 key = key_of(row.p(i), i);
+    if (key >= prefix) list[atomicAdd(s_n, 1)] = key;
+  }
+  __syncthreads();
+  const int n = *s_n;
+  u64* kept_mass = list + kListCap;
+  constexpr int kPer = kListCap / kThreads;
+  u64 my_key[kPer], my_mass[kPer];
+#pragma unroll
+  for (int t = 0; t < kPer; ++t) {
+    const int e = threadIdx.x + t * kThreads;
+    my_key[t] = 0;
+    my_mass[t] = 0;
+    if (e < n) {
+      const u64 key = list[e];
+      int rank = 0;
+      u64 mass_above = 0;
+      for (int j = 0; j < n; ++j) {
+        const u64 other = list[j];
+        if (other > key) {
+          ++rank;
+          mass_above += mass_of(__uint_as_float((unsigned)(other >> 32)));
+        }
+      }
+      const bool keep = rank < top_k && (rank == 0 || !use_p || mass_above < need_p);
+      my_key[t] = key;
+      my_mass[t] = keep ? mass_of(__uint_as_float((unsigned)(key >> 32))) : 0;
+    }
+  }
+  u64 total = 0;
+#pragma unroll
+  for (int t = 0; t < kPer; ++t) {
+    const int e = threadIdx.x + t * kThreads;
+    if (e < n) kept_mass[e] = my_mass[t];
+    total += my_mass[t];
+  }
+  total = block_sum(total, scratch);  // its barriers also publish kept_mass
+  if (threadIdx.x == 0) *s_hit = fallback;  // if nothing is drawn (no mass at all), the maximum
+  __syncthreads();
+  const u64 target = (__umul64hi(total, u24) << 40) | ((total * u24) >> 24);  // floor(total * u24 / 2^24)
+#pragma unroll
+  for (int t = 0; t < kPer; ++t) {
+    const int e = threadIdx.x + t * kThreads;
+    if (e < n && my_mass[t]) {
+      const unsigned idx = (unsigned)my_key[t];
+      u64 before = 0;
+      for (int j = 0; j < n; ++j)
+        if ((unsigned)list[j] < idx) before += kept_mass[j];
+      if (before <= target && target < before + my_mass[t]) *s_hit = (int)idx;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) out[blockIdx.x] = *s_hit;
+  return true;
+}
+
 template <bool CACHED>
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float temperature, int top_k,
@@ -191,7 +292,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   __shared__ int s_idx[kThreads / 32];
   __shared__ u64 s_u64[kThreads / 32];
   __shared__ u64 s_before;
-  __shared__ int s_hit, s_result;
+  __shared__ int s_hit, s_result, s_n;
 
   const float* rowp = logits + (size_t)blockIdx.x * V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -199,11 +300,17 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   // first maximal index; NaN never wins
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += kThreads) {
-    const float l = rowp[i];
-    if (l > best || (l == best && i < best_i)) {
-      best = l;
-      best_i = i;
+  for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {  // eight loads in flight a thread
+    float l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) l[j] = i0 + j * kThreads < V ? __ldg(rowp + i0 + j * kThreads) : -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * kThreads;
+      if (l[j] > best || (l[j] == best && i < best_i)) {  // indices ascend, so the first maximum stays
+        best = l[j];
+        best_i = i;
+      }
     }
   }
 #pragma unroll
@@ -241,13 +348,28 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   if (top_k <= 0 || top_k > V) top_k = V;
 
   u64 z = 0;
-  for (int i = threadIdx.x; i < V; i += kThreads) {
-    const float p = row.p(i);
-    if (CACHED) s_p[i] = p;
-    z += mass_of(p);
+  for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {
+    float l[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) l[j] = i0 + j * kThreads < V ? __ldg(rowp + i0 + j * kThreads) : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = i0 + j * kThreads;
+      if (i < V) {
+        const float p = (l[j] == l[j]) ? expf((l[j] - row.mx) * row.inv_t) : 0.f;  // as Row::p
+        if (CACHED) s_p[i] = p;
+        z += mass_of(p);
+      }
+    }
   }
   z = block_sum(z, s_u64);  // its barriers also publish s_p
   if (CACHED) row.cached = s_p;
+
+  if (top_k < V && top_k <= kSmallK) {
+    const u64 u = splitmix_uniform24(seed, (u64)streams[blockIdx.x], (u64)counters[blockIdx.x]);
+    const u64 need_p = (u64)ceil((double)fmaxf(top_p, 0.f) * (double)z);
+    if (sample_small(row, V, top_k, top_p < 1.0f, need_p, u, best_i, out, s_cnt, s_mass, s_u64, &s_hit, &s_before, &s_n)) return;
+  }
 
   u64 thr = 0;
   if (top_k < V) thr = radix_select(row, V, false, (u64)top_k, s_cnt, s_mass, s_u64, &s_hit, &s_before);

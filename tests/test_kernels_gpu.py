@@ -381,6 +381,28 @@ def test_sample_equals_plain(ops, V):
         assert got == want, (T, k, p)
 
 
+def test_sample_small_top_k_takes_the_short_list_or_falls_back(ops):
+    """A small top_k is finished on a short candidate list; rows whose candidates do not fit the
+    list (thousands of equal logits at the edge of top_k) take the general selection.  Both give
+    the plain implementation's token, for every top_p, a top_k of 1, 512 (the last short one) and
+    513, and a top_p of 0 (the best candidate alone)."""
+    V, rows = 50257, 5
+    logits = gen((rows, V), 21, scale=3.0)
+    logits[1, 1000:9000] = 9.0           # 8,000 equal maxima: the list cannot hold the bucket
+    logits[2, 0:V - 1:2] = logits[2, 1:V:2]   # pairs of equal logits
+    logits[3, 7] = 40.0                  # one token holds all the mass
+    logits[4] = logits[4].round()        # many ties on every level
+    streams = torch.arange(rows, dtype=torch.int32).cuda()
+    counters = torch.arange(rows, dtype=torch.int32).cuda() + 2
+    host = logits.cpu().numpy()
+    for T, k, p in [(1.0, 40, 0.9), (0.1, 40, 0.9), (1.0, 1, 1.0), (1.0, 512, 0.95), (1.0, 513, 0.95), (0.7, 40, 0.0),
+                    (2.0, 100, 1.0), (1.0, 40, 0.3)]:
+        for seed in (1, 2):
+            got = ops.sample(logits, T, k, p, seed, streams, counters).tolist()
+            want = [plain_gpt2.sample(host[r], T, k, p, plain_gpt2.uniform01(seed, r, r + 2)) for r in range(rows)]
+            assert got == want, (T, k, p, seed)
+
+
 def test_sample_first_maximum_and_ties(ops):
     logits = torch.zeros(3, 300).cuda()
     logits[0, [17, 250]] = 5.0           # the first of two maxima
