@@ -27,6 +27,12 @@
 // weights stream while the producer of X is still finishing.  Nothing is written to global memory
 // before the wait.
 //
+// Tail norm: when the caller says that the sum this product adds into the residual stream is
+// normed next, the block that finishes last (a ticket from an atomic counter, which it sets back to
+// zero) norms all M rows of the stream and writes them in bfloat16: the values the separate norm
+// kernel would write, one launch and one trip through the launch queue earlier.  Nothing waits:
+// every block takes its ticket after its own stores and a fence, and only the last one goes on.
+//
 // Input modes: float32 rows with a layer norm (statistics in float32 per row, each value
 // normalised and rounded to bfloat16 as it enters an MMA: the values the separate norm kernel
 // writes), or bfloat16 rows read as they are.
@@ -64,12 +70,97 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 // four chunks each) fall into distinct banks.
 __host__ __device__ inline int tile_stride(int per_block) { return per_block * 32 + ((per_block & 1) ? 0 : 32); }
 
+// Layer norm of rows of float32, written in bfloat16, by the whole block: two warps a row, four
+// rows at a time.  The rows were written by other blocks of this launch: they are read from L2
+// (`__ldcg`), never from this SM's L1.  Same order of operations inside a warp as the separate norm
+// kernel (values in registers, mean, then the biased variance); the two warps' sums are added in
+// warp order.  Every thread of the block must call it.
+constexpr int kTailVecs = 8;  // float4 per lane: rows of up to 2 * 32 * 8 * 4 = 2048 values stay in registers
+__device__ __noinline__ void tail_norm(const float* x, const float* __restrict__ gamma, const float* __restrict__ beta, float eps,
+                                       __nv_bfloat16* out, int M, int K) {
+  __shared__ float s_part[kWarps];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nv = K >> 2;
+  if ((K & 3) == 0 && nv <= 64 * kTailVecs) {
+    for (int m0 = 0; m0 < M; m0 += kWarps / 2) {
+      const int m = m0 + (warp >> 1);
+      const int l64 = (warp & 1) * 32 + lane;
+      const bool row_ok = m < M;
+      const float4* r4 = reinterpret_cast<const float4*>(x + (size_t)(row_ok ? m : 0) * K);
+      float4 v[kTailVecs];
+      float s = 0.f;
+#pragma unroll
+      for (int j = 0; j < kTailVecs; ++j) {
+        const int i = l64 + 64 * j;
+        v[j] = (row_ok && i < nv) ? __ldcg(r4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+      }
+      s = warp_sum(s);
+      __syncthreads();  // s_part is free again
+      if (lane == 0) s_part[warp] = s;
+      __syncthreads();
+      const float mean = (s_part[warp & ~1] + s_part[warp | 1]) / (float)K;
+      float q = 0.f;
+#pragma unroll
+      for (int j = 0; j < kTailVecs; ++j) {
+        if (l64 + 64 * j < nv) {
+          const float a0 = v[j].x - mean, a1 = v[j].y - mean, a2 = v[j].z - mean, a3 = v[j].w - mean;
+          q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+        }
+      }
+      q = warp_sum(q);
+      __syncthreads();
+      if (lane == 0) s_part[warp] = q;
+      __syncthreads();
+      const float inv = 1.0f / sqrtf((s_part[warp & ~1] + s_part[warp | 1]) / (float)K + eps);
+      if (row_ok) {
+        __nv_bfloat16* o = out + (size_t)m * K;
+#pragma unroll
+        for (int j = 0; j < kTailVecs; ++j) {
+          const int i = l64 + 64 * j;
+          if (i < nv) {
+            const float4 gm = reinterpret_cast<const float4*>(gamma)[i], bt = reinterpret_cast<const float4*>(beta)[i];
+            uint2 w;
+            w.x = pack2((v[j].x - mean) * inv * gm.x + bt.x, (v[j].y - mean) * inv * gm.y + bt.y);
+            w.y = pack2((v[j].z - mean) * inv * gm.z + bt.z, (v[j].w - mean) * inv * gm.w + bt.w);
+            *reinterpret_cast<uint2*>(o + 4 * i) = w;
+          }
+        }
+      }
+    }
+    return;
+  }
+  for (int m = warp; m < M; m += kWarps) {  // long or odd rows: a warp a row, three reads
+    const float* r = x + (size_t)m * K;
+    float s = 0.f;
+    for (int i = lane; i < K; i += 32) s += __ldcg(r + i);
+    const float mean = warp_sum(s) / (float)K;
+    float q = 0.f;
+    for (int i = lane; i < K; i += 32) {
+      const float c = __ldcg(r + i) - mean;
+      q += c * c;
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(q) / (float)K + eps);
+    for (int i = lane; i < K; i += 32)
+      out[(size_t)m * K + i] = __float2bfloat16_rn((__ldcg(r + i) - mean) * inv * gamma[i] + beta[i]);
+  }
+}
+
+struct TailNorm {  // all null / zero: no tail norm
+  const float* gamma;
+  const float* beta;
+  float eps;
+  __nv_bfloat16* out;  // [M, N]
+  int* counter;        // zero between launches
+};
+
 // MT: batch tiles of 8 sequences (1 or 2).  LN: float32 input with a fused layer norm.
 template <int MT, bool LN>
 __global__ void __launch_bounds__(kWarps * 32, 3)
 linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gamma, const float* __restrict__ beta,
                      float eps, const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
-                     const float* residual, void* out, int M, int N, int K, int act, int out_f32, int k_split) {
+                     const float* residual, void* out, int M, int N, int K, int act, int out_f32, int k_split,
+                     const TailNorm tail) {
   constexpr int kTile = 16 * 8 * MT;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -244,11 +335,23 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
     else
       static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(v);
   }
+  if (tail.out) {  // block 0 of every cluster comes here: one ticket a tile
+    __shared__ int s_last;
+    __threadfence();  // this thread's store is visible to the whole device before the ticket is taken
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(tail.counter, 1) == (int)(gridDim.x / k_split) - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    tail_norm(static_cast<const float*>(out), tail.gamma, tail.beta, tail.eps, tail.out, M, N);
+    if (threadIdx.x == 0) *tail.counter = 0;
+  }
 }
 
 template <int MT, bool LN>
 int launch(const void* xin, const float* gamma, const float* beta, float eps, const void* W, const float* bias,
-           const float* residual, void* out, int M, int N, int K, int act, int out_dtype, cudaStream_t stream) {
+           const float* residual, void* out, int M, int N, int K, int act, int out_dtype, const TailNorm& tail,
+           cudaStream_t stream) {
   const int tiles = (N + 15) / 16;
   const int all_steps = (K + 31) / 32;
   // Split K over a cluster (1, 2 or 4 blocks) so that a block's share of the matrix fits the
@@ -285,7 +388,7 @@ int launch(const void* xin, const float* gamma, const float* beta, float eps, co
   cfg.numAttrs = 2;
   const int out_f32 = out_dtype == EMBER_F32;
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_decode_kernel<MT, LN>, xin, gamma, beta, eps,
-                                     (const __nv_bfloat16*)W, bias, residual, out, M, N, K, act, out_f32, k_split);
+                                     (const __nv_bfloat16*)W, bias, residual, out, M, N, K, act, out_f32, k_split, tail);
   if (e != cudaSuccess) return ember_fail("linear_decode: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -294,19 +397,29 @@ int launch(const void* xin, const float* gamma, const float* beta, float eps, co
 
 // xin: float32 [M,K] when gamma is given (layer norm fused), else bfloat16 [M,K].
 // residual: float32 [M,N] or null; it may be the output buffer.  out: float32 or bfloat16 [M,N].
+// tail_*: all null, or the layer norm to apply to the float32 output's rows once they are complete
+// (gain and bias float32 [N], result bfloat16 [M,N], a counter that is zero and is left zero).
 EMBER_API int ember_linear_decode(const void* xin, const float* gamma, const float* beta, float eps, const void* W,
                                   const float* bias, const float* residual, void* out, int M, int N, int K, int act,
-                                  int out_dtype, cudaStream_t stream) {
+                                  int out_dtype, const float* tail_gamma, const float* tail_beta, float tail_eps,
+                                  void* tail_out, int* tail_counter, cudaStream_t stream) {
   EMBER_CHECK(M > 0 && M <= 16 && N > 0 && K > 0, "linear_decode: M = %d (at most 16), N = %d, K = %d", M, N, K);
   EMBER_CHECK(K % 8 == 0, "linear_decode: K = %d is not a multiple of 8 (16-byte rows)", K);
   EMBER_CHECK(act >= 0 && act <= 2, "linear_decode: activation %d", act);
   EMBER_CHECK(out_dtype == EMBER_F32 || out_dtype == EMBER_BF16, "linear_decode: output type %d", out_dtype);
   EMBER_CHECK(!residual || out_dtype == EMBER_F32, "linear_decode: a residual sum needs a float32 output");
   EMBER_CHECK((gamma == nullptr) == (beta == nullptr), "linear_decode: give both norm parameters or neither");
+  TailNorm tail = {tail_gamma, tail_beta, tail_eps, static_cast<__nv_bfloat16*>(tail_out), tail_counter};
+  if (tail_out) {
+    EMBER_CHECK(tail_gamma && tail_beta && tail_counter, "linear_decode: a tail norm needs its gain, bias and counter");
+    EMBER_CHECK(out_dtype == EMBER_F32, "linear_decode: a tail norm reads a float32 output");
+  } else {
+    tail = TailNorm{nullptr, nullptr, 0.f, nullptr, nullptr};
+  }
   const bool ln = gamma != nullptr;
   if (M <= 8)
-    return ln ? launch<1, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, stream)
-              : launch<1, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, stream);
-  return ln ? launch<2, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, stream)
-            : launch<2, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, stream);
+    return ln ? launch<1, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream)
+              : launch<1, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream);
+  return ln ? launch<2, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream)
+            : launch<2, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream);
 }

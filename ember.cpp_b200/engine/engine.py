@@ -75,6 +75,7 @@ class StepContext:
     plan: StepPlan
     apps: list
     position: object
+    next_norm: object = None   # set by the model: the norm that reads the stream after the current block, if any
 
 
 class Engine:

@@ -81,6 +81,10 @@ class Norm(Part):
         may fuse the two); a norm may ignore it."""
         raise NotImplementedError
 
+    def announce(self, ctx, out_dtype) -> None:
+        """Tells the kernels that the next sum into the residual stream is normed by this part
+        next (so that they may run the norm in that sum's launch).  A hint; the default says nothing."""
+
 
 class Mixer(Part):
     role = "mixer"

@@ -76,8 +76,13 @@ class DecoderModel:
         logits [wanted rows, vocab] (None if no row is wanted)."""
         plan, ops = ctx.plan, ctx.ops
         x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table())
-        for app in ctx.apps:
+        for i, app in enumerate(ctx.apps):
+            if i + 1 < len(ctx.apps):
+                ctx.next_norm = self.blocks[ctx.apps[i + 1].layer].norm1
+            else:  # the final norm reads the stream itself only if no rows are picked out first
+                ctx.next_norm = self.final_norm if plan.n_want and plan.wants_every_row else None
             x = self.blocks[app.layer].forward(ctx, x, app)
+        ctx.next_norm = None
         if plan.n_want == 0:
             return None
         rows = x if plan.wants_every_row else ops.gather_rows(x, plan.want_rows, plan.n_want)

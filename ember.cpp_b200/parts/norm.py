@@ -33,5 +33,10 @@ class LayerNorm(Norm):
         its own kernel (the value is the same)."""
         return ctx.ops.layernorm(x, self.w, self.b, self.eps, out_dtype, lazy=lazy)
 
+    def announce(self, ctx, out_dtype) -> None:
+        expect = getattr(ctx.ops, "expect_norm", None)
+        if expect is not None:
+            expect(self.w, self.b, self.eps, out_dtype)
+
 
 register_part("norm", "layernorm", LayerNorm)

@@ -120,6 +120,49 @@ def test_linear_few_rows_streams_the_weights(ops, M, N, K, act, with_bias, with_
     assert (got.double() - want).abs().max().item() / scale < (2e-4 if out == "float32" else 2 ** -7)
 
 
+@pytest.mark.parametrize("M, N, K", [(1, 1600, 1600), (8, 1600, 6400), (9, 96, 64), (16, 2056, 72), (5, 100, 1600), (16, 1600, 1600)])
+def test_linear_norms_the_stream_in_its_tail(ops, M, N, K):
+    """A product that sums into the residual stream and was told which norm follows leaves that
+    norm's result ready: the block that finishes last computes it.  It equals the separate kernel's
+    result (to a rounding of bfloat16, the two add the row's sums in different orders), the stream
+    itself is what the product alone would give, and the counter is zero again for the next call."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    ops = CudaOps()
+    ops.tail_norm = True          # off by default: measured, it gains nothing over the separate kernel
+    a, w, bias = gen((M, K), 60, torch.bfloat16), gen((N, K), 61, torch.bfloat16, 0.1), gen((N,), 62)
+    res = gen((M, N), 63) * 3 + 1
+    gw, gb = gen((N,), 64) * 0.1 + 1, gen((N,), 65) * 0.1
+    for rep in range(3):
+        x = res.clone()
+        ops.expect_norm(gw, gb, 1e-5, torch.bfloat16)
+        out = ops.linear(a, w, bias, residual=x)
+        assert out.data_ptr() == x.data_ptr() and ops._normed is not None
+        launches = ops.launches
+        h = ops.layernorm(out, gw, gb, 1e-5, torch.bfloat16)
+        assert ops.launches == launches            # nothing was launched for the norm
+        assert int(ops._tail_counter.item()) == 0
+        want_x = linear_ref(a, w, bias, None, res)
+        assert (out.double() - want_x).abs().max().item() / want_x.abs().max().item() < 2e-4
+        apart = ops.layernorm(out, gw, gb, 1e-5, torch.bfloat16)
+        assert ops.launches == launches + 1        # the result is handed out once
+        ref = torch.nn.functional.layer_norm(out.double(), (N,), gw.double(), gb.double(), 1e-5)
+        assert (h.double() - ref).abs().max().item() < 2 ** -7 * ref.abs().max().item()
+        assert (h.float() - apart.float()).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
+    # other parameters than the announced ones, or a changed stream: the norm runs as usual
+    x = res.clone()
+    ops.expect_norm(gw, gb, 1e-5, torch.bfloat16)
+    out = ops.linear(a, w, bias, residual=x)
+    launches = ops.launches
+    ops.layernorm(out, gb, gw, 1e-5, torch.bfloat16)
+    assert ops.launches == launches + 1
+    ops.expect_norm(gw, gb, 1e-5, torch.bfloat16)
+    out = ops.linear(a, w, bias, residual=x)
+    out = ops.linear(a, w, bias, residual=out)     # a second sum without an announcement
+    launches = ops.launches
+    ops.layernorm(out, gw, gb, 1e-5, torch.bfloat16)
+    assert ops.launches == launches + 1
+
+
 @pytest.mark.parametrize("M, N, K, tile_n", [(128, 64, 64, 0), (200, 1600, 1600, 0), (129, 1001, 72, 0), (65, 48, 4104, 16),
                                              (300, 500, 200, 48), (1000, 777, 136, 256), (2048, 4800, 1600, 0),
                                              (257, 6400, 320, 208)])
