@@ -6,21 +6,27 @@
 // (graph_ir.cpp:4306-4373): the graph hides the host's launch cost, not the GPU's.  On this GPU a
 // kernel node costs about 3.4 microseconds however small it is, while a layer of GPT-2 XL streams
 // its 61 MB of weights in 9.4; a step launched kernel by kernel is bound by the boundaries between
-// kernels.  Here the boundaries are grid barriers (about a microsecond), and the weights of the
-// next linear layer are already on their way into shared memory while the grid waits at one.
+// kernels.  Here the boundaries are grid barriers (one release-add and acquire-loads of a counter
+// that is never reset), and the weights of the next linear layers are already on their way into
+// shared memory while the grid waits at one.
 //
 // One block per SM, 16 warps.  The program is an array of EmberOp in device memory, written once
 // when the step's shape is first seen; only the step's description (tokens, positions, pages)
 // changes between launches.
 //   linear     block b owns output features [N*b/G, N*(b+1)/G) in tiles of 16 rows; a tile is
-//              brought in by cp.async in pieces of at most 1,664 values of K (double buffered,
-//              the next piece always in flight, also across operations and barriers); the 16
-//              warps take interleaved 32-wide slices on mma.sync with the operands swapped (as
-//              linear_decode.cu), are summed in shared memory in warp order, then bias, GELU and
-//              the float32 residual sum.
+//              brought in by cp.async in pieces of at most 800 values of K through a ring of seven
+//              slots (179 KB), six pieces always in flight, also across operations and barriers:
+//              the weights of the next linear layers stream in while the grid runs the attention
+//              or waits.  The 16 warps take the 32-wide slices of K in turn on mma.sync with the
+//              operands swapped (as linear_decode.cu); a warp's slices are the same in every tile,
+//              so it keeps the activations it multiplies with in registers for the whole
+//              operation (read once from L2; normed on the way when a layer norm precedes the
+//              product: row statistics by two warps a row first).  Up to four tiles' sums stay in
+//              registers, are summed in shared memory in warp order, then bias, GELU and the
+//              float32 residual sum.  At most 8 rows, K up to 6,656 (2,048 with a norm).
 //   attention  a (token, head) pair per half block (8 warps), all its keys, online softmax per
 //              stream, merged in shared memory; the token's own key and value are stored first.
-//   layer norm a row per block.  embedding: a row per block.
+//   layer norm (one that no product follows) a row per block.  embedding: a row per block.
 // Activations written in one phase and read in the next go through L2 (ld.global.cg): L1 is not
 // coherent between SMs.
 //
@@ -57,7 +63,12 @@ struct alignas(16) EmberOp {
 namespace {
 
 constexpr int kThreads = 512, kWarps = 16;
-constexpr int kMaxPiece = 1664;                 // values of K in one staged piece of a tile
+constexpr int kMaxPiece = 800;                  // values of K in one staged piece of a tile
+constexpr int kSlots = 7;                       // pieces the ring holds
+constexpr int kRows = 8;                        // rows (sequences) a program can have
+constexpr int kGroup = 4;                       // tiles whose sums stay in registers before they are finished
+constexpr int kNormK = 2048;                    // the widest row a fused layer norm takes
+constexpr int kMaxJ = 13;                       // 32-wide slices of K a warp can own: K <= 13 * 16 * 32 = 6,656
 constexpr unsigned kSpinLimit = 1u << 22;       // polls of a barrier before a block gives up
 
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
@@ -81,39 +92,36 @@ __host__ __device__ inline int piece_len(int K) {
 __host__ __device__ inline int piece_stride(int len) { return len + (((len / 32) & 1) ? 0 : 32); }
 
 struct GridBarrier {
-  unsigned count;
-  unsigned generation;
+  unsigned long long count;  // arrivals, never reset: barrier number k of launch e is complete at (e * barriers + k) * blocks
+  unsigned long long epoch;  // launches completed
 };
 
-// All blocks of the grid meet here.  Returns false if the wait ran out (the error flag is set).
-__device__ bool grid_barrier(GridBarrier* bar, int* error) {
+// All blocks of the grid meet here.  `target`: the arrival count at which this barrier is complete.
+// One release-add and acquire-loads until the count is there: each poll is one trip to L2.  Returns
+// false if the wait ran out or another block reported an error (the error flag is set).
+__device__ bool grid_barrier(GridBarrier* bar, unsigned long long target, int* error) {
   __shared__ int s_ok;
   __syncthreads();
   if (threadIdx.x == 0) {
     int ok = 1;
-    __threadfence();
-    const unsigned gen = *(volatile unsigned*)&bar->generation;
-    if (atomicAdd(&bar->count, 1u) == gridDim.x - 1) {
-      bar->count = 0;
-      __threadfence();
-      atomicAdd(&bar->generation, 1u);
-    } else {
-      unsigned spins = 0;
-      while (*(volatile unsigned*)&bar->generation == gen) {
+    asm volatile("red.release.gpu.global.add.u64 [%0], 1;\n" ::"l"(&bar->count) : "memory");
+    unsigned spins = 0;
+    for (;;) {
+      unsigned long long seen;
+      asm volatile("ld.acquire.gpu.global.u64 %0, [%1];\n" : "=l"(seen) : "l"(&bar->count) : "memory");
+      if (seen >= target) break;
+      if ((++spins & 63u) == 0) {
         if (*(volatile int*)error) {  // another block already gave up or found a bad index
           ok = 0;
           break;
         }
-        if (++spins > kSpinLimit) {
+        if (spins > kSpinLimit) {
           atomicCAS(error, 0, 1);
           ok = 0;
           break;
         }
-        __nanosleep(32);
       }
     }
-    __threadfence();
-    if (*(volatile int*)error) ok = 0;
     s_ok = ok;
   }
   __syncthreads();
@@ -121,128 +129,261 @@ __device__ bool grid_barrier(GridBarrier* bar, int* error) {
 }
 
 // ---------------------------------------------------------------------------- linear: the staged pieces
-struct Cursor {  // a piece of a tile of a linear operation, in the order this block works through them
-  int op, tile, piece;
-};
-
 struct LinearShape {
   int lo, hi, tiles, pieces, len;  // this block's rows [lo, hi), its 16-row tiles, pieces of K per tile, piece length
 };
 
+// (32-bit arithmetic: the launcher refuses programs whose N * blocks does not fit)
 __device__ __forceinline__ LinearShape shape_of(const EmberOp& op) {
   LinearShape s;
-  s.lo = (int)((long long)op.N * blockIdx.x / gridDim.x);
-  s.hi = (int)((long long)op.N * (blockIdx.x + 1) / gridDim.x);
+  s.lo = (int)((unsigned)op.N * blockIdx.x / gridDim.x);
+  s.hi = (int)((unsigned)op.N * (blockIdx.x + 1) / gridDim.x);
   s.tiles = (s.hi - s.lo + 15) / 16;
   s.len = piece_len(op.K);
   s.pieces = (op.K + s.len - 1) / s.len;
   return s;
 }
 
+struct Cursor {  // a piece of a tile of a linear operation, in the order this block works through them
+  int op, tile, piece;
+  LinearShape shape;  // of `op` for this block (worked out once per operation: it takes divisions)
+};
+
 // the first piece of the first linear operation at or after `from` in which this block has rows
 __device__ Cursor first_piece(const EmberOp* ops, int n_ops, int from) {
-  for (int i = from; i < n_ops; ++i)
-    if (ops[i].type == EMBER_OP_LINEAR && shape_of(ops[i]).tiles > 0) return Cursor{i, 0, 0};
-  return Cursor{n_ops, 0, 0};
+  Cursor c;
+  c.tile = c.piece = 0;
+  for (c.op = from; c.op < n_ops; ++c.op)
+    if (ops[c.op].type == EMBER_OP_LINEAR) {
+      c.shape = shape_of(ops[c.op]);
+      if (c.shape.tiles > 0) return c;
+    }
+  c.op = n_ops;
+  c.shape = LinearShape{0, 0, 0, 0, 32};
+  return c;
 }
 
-__device__ Cursor next_piece(const EmberOp* ops, int n_ops, Cursor c) {
-  const LinearShape s = shape_of(ops[c.op]);
-  if (++c.piece < s.pieces) return c;
+__device__ __forceinline__ Cursor next_piece(const EmberOp* ops, int n_ops, Cursor c) {
+  if (++c.piece < c.shape.pieces) return c;
   c.piece = 0;
-  if (++c.tile < s.tiles) return c;
+  if (++c.tile < c.shape.tiles) return c;
   return first_piece(ops, n_ops, c.op + 1);
 }
 
-__device__ void stage_piece(const EmberOp& op, Cursor c, __nv_bfloat16* buf) {
-  const LinearShape s = shape_of(op);
+// A slot of the ring: [16][ldw] weights, ldw = piece_stride(piece length).
+constexpr int kSlotElems = 16 * kMaxPiece;
+
+// Asks for the weights of piece `c` and commits the copies as one group.  Every thread commits,
+// whether it had copies or not.
+__device__ void stage_piece(const EmberOp& op, const Cursor& c, __nv_bfloat16* slot) {
+  const LinearShape& s = c.shape;
   const int ldw = piece_stride(s.len);
   const int k0 = c.piece * s.len;
   const int chunks = s.len / 8;
   const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(op.w);
   for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
-    const int r = i / chunks, ch = i % chunks;
+    const int r = (unsigned)i / (unsigned)chunks, ch = i - r * chunks;
     const int row = s.lo + c.tile * 16 + r, k = k0 + ch * 8;
     const bool ok = row < s.hi && k < op.K;
-    cp_async_16(buf + r * ldw + ch * 8, W + (size_t)(ok ? row : s.lo) * op.K + (ok ? k : 0), ok);
+    cp_async_16(slot + r * ldw + ch * 8, W + (size_t)(ok ? row : s.lo) * op.K + (ok ? k : 0), ok);
   }
   asm volatile("cp.async.commit_group;\n" ::);
 }
 
-template <int MT>
-__device__ void run_linear(const EmberOp* ops, int n_ops, int i, Cursor& staged, int& staged_buf, __nv_bfloat16* wbuf,
-                           size_t buf_elems, float* red) {
-  constexpr int kTile = 16 * 8 * MT;
+__device__ __forceinline__ void wait_groups(int pending) {  // at most `pending` of the newest groups still in flight
+  switch (pending) {
+    case 0: asm volatile("cp.async.wait_group 0;\n" ::: "memory"); break;
+    case 1: asm volatile("cp.async.wait_group 1;\n" ::: "memory"); break;
+    case 2: asm volatile("cp.async.wait_group 2;\n" ::: "memory"); break;
+    case 3: asm volatile("cp.async.wait_group 3;\n" ::: "memory"); break;
+    case 4: asm volatile("cp.async.wait_group 4;\n" ::: "memory"); break;
+    case 5: asm volatile("cp.async.wait_group 5;\n" ::: "memory"); break;
+    default: asm volatile("cp.async.wait_group 6;\n" ::: "memory"); break;
+  }
+}
+
+// The ring of staged pieces, the same in every thread of the block.
+struct Ring {
+  Cursor tail;  // the oldest staged piece (the next to be used)
+  Cursor head;  // the next piece to stage
+  int count;    // staged and not yet used
+  int tail_slot;
+};
+
+__device__ __forceinline__ bool fused_norm(const EmberOp& op) { return op.reserved != 0; }
+
+// Stages the next piece if the ring has room.  Weights are constants of the model, so pieces of
+// operations that have not begun may be staged at any time.
+__device__ void stage_next(const EmberOp* ops, int n_ops, Ring& ring, __nv_bfloat16* wbuf) {
+  if (ring.count >= kSlots || ring.head.op >= n_ops) return;
+  __nv_bfloat16* slot = wbuf + (size_t)((ring.tail_slot + ring.count) % kSlots) * kSlotElems;
+  stage_piece(ops[ring.head.op], ring.head, slot);
+  if (ring.count == 0) ring.tail = ring.head;
+  ring.head = next_piece(ops, n_ops, ring.head);
+  ++ring.count;
+}
+
+// Mean and 1/sqrt(var + eps) of the operation's (at most kRows) float32 rows: two warps a row,
+// the row in registers, mean, then the biased variance; the two warps' sums are added in warp
+// order.  The rows were written by other SMs in the phase before: read from L2.
+// stats: [2 * kRows]; part: [kWarps].
+__device__ void row_stats(const EmberOp& op, float* stats, float* part) {
+  constexpr int kVecs = kNormK / 4 / 64;  // float4 a lane
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = warp >> 1, l64 = (warp & 1) * 32 + lane;
+  const int K = op.K, nv = K >> 2;
+  const bool row_ok = m < op.M;
+  const float4* r4 = reinterpret_cast<const float4*>(static_cast<const float*>(op.a) + (size_t)(row_ok ? m : 0) * K);
+  float4 v[kVecs];
+  float s = 0.f;
+#pragma unroll
+  for (int j = 0; j < kVecs; ++j) {
+    const int i = l64 + 64 * j;
+    v[j] = (row_ok && i < nv) ? __ldcg(r4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+  }
+  s = warp_sum(s);
+  if (lane == 0) part[warp] = s;
+  __syncthreads();
+  const float mean = (part[warp & ~1] + part[warp | 1]) / (float)K;
+  float q = 0.f;
+#pragma unroll
+  for (int j = 0; j < kVecs; ++j) {
+    if (l64 + 64 * j < nv) {
+      const float a0 = v[j].x - mean, a1 = v[j].y - mean, a2 = v[j].z - mean, a3 = v[j].w - mean;
+      q += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
+    }
+  }
+  q = warp_sum(q);
+  __syncthreads();
+  if (lane == 0) part[warp] = q;
+  __syncthreads();
+  if ((warp & 1) == 0 && lane == 0 && m < kRows) {
+    stats[2 * m] = mean;
+    stats[2 * m + 1] = 1.0f / sqrtf((part[warp] + part[warp + 1]) / (float)K + op.eps);
+  }
+  __syncthreads();
+}
+
+// The sums of up to kGroup tiles, warps -> block in warp order, then the epilogue.
+__device__ void finish_tiles(const EmberOp& op, const LinearShape& s, int first_tile, int n_tiles, float (&acc)[kGroup][4],
+                             float* red) {
+  constexpr int kTile = 16 * 8;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, c = lane & 3;
+#pragma unroll
+  for (int t = 0; t < kGroup; ++t) {
+    if (t < n_tiles) {
+      float* mine = red + (warp * kGroup + t) * kTile;
+      mine[g * 8 + c * 2] = acc[t][0];
+      mine[g * 8 + c * 2 + 1] = acc[t][1];
+      mine[(g + 8) * 8 + c * 2] = acc[t][2];
+      mine[(g + 8) * 8 + c * 2 + 1] = acc[t][3];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
+  }
+  __syncthreads();
+  const int t = threadIdx.x / kTile, e = threadIdx.x % kTile;  // 512 threads: one output of one of four tiles each
+  if (t < n_tiles) {
+    const int r = e % 16, m = e / 16;
+    const int n = s.lo + (first_tile + t) * 16 + r;
+    if (m < op.M && n < s.hi) {
+      float v = 0.f;
+      for (int w = 0; w < kWarps; ++w) v += red[(w * kGroup + t) * kTile + r * 8 + m];
+      if (op.bias) v += op.bias[n];
+      v = apply_act(v, op.act);
+      const size_t at = (size_t)m * op.N + n;
+      if (op.residual) v = __ldcg(op.residual + at) + v;
+      if (op.out_f32)
+        static_cast<float*>(op.out)[at] = v;
+      else
+        static_cast<__nv_bfloat16*>(op.out)[at] = __float2bfloat16_rn(v);
+    }
+  }
+  __syncthreads();  // `red` is free again
+}
+
+// A warp owns the 32-wide slices of K whose number is its own modulo 16, in every tile: the
+// activations it multiplies with never change during the operation, so it holds them in registers
+// (8 values of row lane/4 a slice: the B fragments of two MMAs), read once from L2, normed on the
+// way if the operation has a norm.
+__device__ void run_linear(const EmberOp* ops, int n_ops, int i, Ring& ring, __nv_bfloat16* wbuf, float* red, float* part,
+                           float* stats) {
   const EmberOp& op = ops[i];
-  const LinearShape s = shape_of(op);
+  // this block's share: the ring's tail is this operation's first piece if the block has rows in it
+  const LinearShape s = (ring.count > 0 && ring.tail.op == i) ? ring.tail.shape : shape_of(op);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
   const int ldw = piece_stride(s.len);
-  const __nv_bfloat16* x = static_cast<const __nv_bfloat16*>(op.a);
-  float acc[MT][4];
-  for (int tile = 0; tile < s.tiles; ++tile) {
+  const int spp = s.len / 32;  // slices a piece
+  const bool normed = fused_norm(op);
+  if (normed) row_stats(op, stats, part);
+  uint4 xr[kMaxJ];
 #pragma unroll
-    for (int t = 0; t < MT; ++t)
-#pragma unroll
-      for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
-    for (int piece = 0; piece < s.pieces; ++piece) {
-      // `staged` is this piece (the block stages pieces in exactly the order it uses them)
-      const int buf = staged_buf;
-      const Cursor nxt = next_piece(ops, n_ops, staged);
-      if (nxt.op < n_ops) {
-        stage_piece(ops[nxt.op], nxt, wbuf + (size_t)(buf ^ 1) * buf_elems);
-        asm volatile("cp.async.wait_group 1;\n" ::: "memory");
+  for (int j = 0; j < kMaxJ; ++j) {
+    const int piece = (j * kWarps + warp) / spp;  // slice number -> where it lies in K as the pieces cut it
+    const int k = piece * s.len + ((j * kWarps + warp) - piece * spp) * 32 + c * 8;
+    xr[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (piece < s.pieces && k < op.K && g < op.M) {
+      if (normed) {
+        const float* r = static_cast<const float*>(op.a) + (size_t)g * op.K + k;
+        const float4 v0 = __ldcg(reinterpret_cast<const float4*>(r)), v1 = __ldcg(reinterpret_cast<const float4*>(r) + 1);
+        const float4* gm = reinterpret_cast<const float4*>(static_cast<const float*>(op.w2) + k);
+        const float4* bt = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(op.reserved_ptr) + k);
+        const float4 g0 = gm[0], g1 = gm[1], b0 = bt[0], b1 = bt[1];
+        const float mean = stats[2 * g], inv = stats[2 * g + 1];
+        const __nv_bfloat162 p0 = __floats2bfloat162_rn((v0.x - mean) * inv * g0.x + b0.x, (v0.y - mean) * inv * g0.y + b0.y);
+        const __nv_bfloat162 p1 = __floats2bfloat162_rn((v0.z - mean) * inv * g0.z + b0.z, (v0.w - mean) * inv * g0.w + b0.w);
+        const __nv_bfloat162 p2 = __floats2bfloat162_rn((v1.x - mean) * inv * g1.x + b1.x, (v1.y - mean) * inv * g1.y + b1.y);
+        const __nv_bfloat162 p3 = __floats2bfloat162_rn((v1.z - mean) * inv * g1.z + b1.z, (v1.w - mean) * inv * g1.w + b1.w);
+        xr[j].x = *reinterpret_cast<const unsigned*>(&p0);
+        xr[j].y = *reinterpret_cast<const unsigned*>(&p1);
+        xr[j].z = *reinterpret_cast<const unsigned*>(&p2);
+        xr[j].w = *reinterpret_cast<const unsigned*>(&p3);
       } else {
-        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        xr[j] = ldcg16(static_cast<const __nv_bfloat16*>(op.a) + (size_t)g * op.K + k);
       }
-      staged = nxt;
-      staged_buf = buf ^ 1;
-      __syncthreads();
-      const __nv_bfloat16* wt = wbuf + (size_t)buf * buf_elems;
-      const int k0 = piece * s.len;
-      const int slices = s.len / 32;
-#pragma unroll 2
-      for (int sl = warp; sl < slices; sl += kWarps) {
-        const int kl = sl * 32 + c * 8, k = k0 + kl;
-        const uint4 a_lo = *reinterpret_cast<const uint4*>(wt + g * ldw + kl);
-        const uint4 a_hi = *reinterpret_cast<const uint4*>(wt + (g + 8) * ldw + kl);
+    }
+  }
+  float acc[kGroup][4];
 #pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          const int m = t * 8 + g;
-          const uint4 b = (k < op.K && m < op.M) ? ldcg16(x + (size_t)m * op.K + k) : make_uint4(0, 0, 0, 0);
-          mma_bf16(acc[t], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-          mma_bf16(acc[t], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
-        }
-      }
-      if (piece == s.pieces - 1) {
-        // warps -> block in warp order, then the epilogue
+  for (int t = 0; t < kGroup; ++t)
 #pragma unroll
-        for (int t = 0; t < MT; ++t) {
-          float* mine = red + warp * kTile + t * 8;
-          mine[g * (8 * MT) + c * 2] = acc[t][0];
-          mine[g * (8 * MT) + c * 2 + 1] = acc[t][1];
-          mine[(g + 8) * (8 * MT) + c * 2] = acc[t][2];
-          mine[(g + 8) * (8 * MT) + c * 2 + 1] = acc[t][3];
-        }
-        __syncthreads();
-        if (threadIdx.x < kTile) {
-          const int r = threadIdx.x % 16, m = threadIdx.x / 16;
-          const int n = s.lo + tile * 16 + r;
-          if (m < op.M && n < s.hi) {
-            float v = 0.f;
-            for (int w = 0; w < kWarps; ++w) v += red[w * kTile + r * (8 * MT) + m];
-            if (op.bias) v += op.bias[n];
-            v = apply_act(v, op.act);
-            const size_t at = (size_t)m * op.N + n;
-            if (op.residual) v = __ldcg(op.residual + at) + v;
-            if (op.out_f32)
-              static_cast<float*>(op.out)[at] = v;
-            else
-              static_cast<__nv_bfloat16*>(op.out)[at] = __float2bfloat16_rn(v);
+    for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
+  for (int tile = 0; tile < s.tiles; ++tile) {
+    const int tg = tile % kGroup;
+    for (int piece = 0; piece < s.pieces; ++piece) {
+      // the ring's tail is this piece: pieces are staged in exactly the order they are used
+      if (ring.count == 0) stage_next(ops, n_ops, ring, wbuf);
+      wait_groups(ring.count - 1);
+          __syncthreads();  // the piece is visible to all warps, and all have left the slot used before it
+          const __nv_bfloat16* wt = wbuf + (size_t)ring.tail_slot * kSlotElems;
+      ring.tail = next_piece(ops, n_ops, ring.tail);
+      ring.tail_slot = (ring.tail_slot + 1) % kSlots;
+      --ring.count;
+      // refill behind it (never the slot in use: at most kSlots - 1 are staged while one is used)
+      while (ring.count < kSlots - 1 && ring.head.op < n_ops) stage_next(ops, n_ops, ring, wbuf);
+      const int first = piece * spp;
+#pragma unroll
+      for (int j = 0; j < kMaxJ; ++j) {
+        const int sl = j * kWarps + warp - first;  // this warp's j-th slice, counted inside this piece
+        if (sl >= 0 && sl < spp) {
+          const int kl = sl * 32 + c * 8;
+          const uint4 a_lo = *reinterpret_cast<const uint4*>(wt + g * ldw + kl);
+          const uint4 a_hi = *reinterpret_cast<const uint4*>(wt + (g + 8) * ldw + kl);
+#pragma unroll
+          for (int t = 0; t < kGroup; ++t) {
+            if (t == tg) {
+              mma_bf16(acc[t], a_lo.x, a_hi.x, a_lo.y, a_hi.y, xr[j].x, xr[j].y);
+              mma_bf16(acc[t], a_lo.z, a_hi.z, a_lo.w, a_hi.w, xr[j].z, xr[j].w);
+            }
           }
         }
       }
-      __syncthreads();  // the buffer and `red` are free again
+    }
+    if (tg == kGroup - 1 || tile == s.tiles - 1) {
+          finish_tiles(op, s, tile - tg, tg + 1, acc, red);
     }
   }
 }
@@ -440,23 +581,33 @@ __device__ void run_attention(const EmberOp& op, float* scratch_all, int scratch
 
 constexpr int kAttnScratchFloats = 3 * 128 + 128 * 17 + 64;  // per half block; the largest of the five head-size cases
 
-template <int MT>
+constexpr size_t kRingBytes = (size_t)kSlots * kSlotElems * sizeof(__nv_bfloat16);
+constexpr size_t kRedFloats = (size_t)kWarps * kGroup * 16 * 8;  // also the attention's scratch
+constexpr size_t kProgramSmem = kRingBytes + kRedFloats * sizeof(float) + 4 * kWarps * sizeof(float);
+static_assert(kRedFloats >= 2 * (size_t)kAttnScratchFloats, "the attention's scratch shares the sums' buffer");
+static_assert(kProgramSmem <= 227 * 1024, "shared memory of the persistent kernel");
+
 __global__ void __launch_bounds__(kThreads, 1)
 decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* bar, int* error, int* trace) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
-  const size_t buf_elems = (size_t)16 * piece_stride(kMaxPiece);
-  __nv_bfloat16* wbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                 // [2][buf_elems]
-  float* red = reinterpret_cast<float*>(wbuf + 2 * buf_elems);                       // [kWarps][16*8*MT]
-  float* attn = red + kWarps * 16 * 8 * MT;                                          // [2][kAttnScratchFloats]
-  float* rows = attn + 2 * kAttnScratchFloats;                                       // [kWarps]
+  __nv_bfloat16* wbuf = reinterpret_cast<__nv_bfloat16*>(smem_raw);                      // the ring
+  float* red = reinterpret_cast<float*>(smem_raw + kRingBytes);                           // [kWarps][kGroup][128]
+  float* rows = red + kRedFloats;                                                         // [2 * kWarps]: sums of warps
+  float* stats = rows + 2 * kWarps;                                                       // [2 * kRows]: mean, 1/sd
 
   unsigned long long t_start = 0;
-  Cursor staged = first_piece(ops, n_ops, 0);
-  int staged_buf = 0;
-  if (staged.op < n_ops) stage_piece(ops[staged.op], staged, wbuf);
+  // arrivals before this launch: every block reads the epoch before its first arrival, and block 0
+  // advances it only after its last barrier, which no block passes before all have arrived at the first
+  const unsigned long long arrivals0 = *(volatile unsigned long long*)&bar->epoch * (unsigned long long)(n_ops - 1) * gridDim.x;
+  Ring ring;
+  ring.head = first_piece(ops, n_ops, 0);
+  ring.tail = ring.head;
+  ring.count = 0;
+  ring.tail_slot = 0;
+  while (ring.count < kSlots && ring.head.op < n_ops) stage_next(ops, n_ops, ring, wbuf);
   for (int i = 0; i < n_ops; ++i) {
     const EmberOp& op = ops[i];
-    if (trace && threadIdx.x == 0) {  // a debugging aid: the operation each block has reached (host-visible memory)
+    if (trace && threadIdx.x == 0) {  // a debugging aid: the operation each block has reached
       trace[blockIdx.x] = i + 1;
       if (blockIdx.x == 0 && i < 768) {  // and when block 0 began it, in nanoseconds since the kernel started
         unsigned long long now;
@@ -464,24 +615,22 @@ decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* b
         if (i == 0) t_start = now;
         trace[256 + i] = (int)(now - t_start);
       }
-      __threadfence_system();
     }
-    if (op.type == EMBER_OP_LINEAR) run_linear<MT>(ops, n_ops, i, staged, staged_buf, wbuf, buf_elems, red);
-    else if (op.type == EMBER_OP_ATTENTION) run_attention(op, attn, kAttnScratchFloats, error);
-    else if (op.type == EMBER_OP_LAYERNORM) run_layernorm(op, rows);
-    else if (op.type == EMBER_OP_EMBED) run_embed(op, error);
-    if (i + 1 < n_ops && !grid_barrier(bar, error)) break;
+    if (op.type == EMBER_OP_LINEAR) {
+      run_linear(ops, n_ops, i, ring, wbuf, red, rows, stats);
+      while (ring.count < kSlots && ring.head.op < n_ops) stage_next(ops, n_ops, ring, wbuf);  // the next products' weights
+    } else if (op.type == EMBER_OP_ATTENTION) {
+      run_attention(op, red, kAttnScratchFloats, error);
+    } else if (op.type == EMBER_OP_LAYERNORM) {
+      run_layernorm(op, rows);
+    } else if (op.type == EMBER_OP_EMBED) {
+      run_embed(op, error);
+    }
+    if (i + 1 < n_ops && !grid_barrier(bar, arrivals0 + (unsigned long long)(i + 1) * gridDim.x, error)) break;
   }
   asm volatile("cp.async.wait_all;\n" ::: "memory");  // nothing of this block is in flight when it leaves
-  if (trace && threadIdx.x == 0) {
-    trace[blockIdx.x] = -1;  // left the kernel
-    __threadfence_system();
-  }
-}
-
-size_t program_smem(int mt) {
-  return (size_t)2 * 16 * piece_stride(kMaxPiece) * sizeof(__nv_bfloat16) + (size_t)kWarps * 16 * 8 * mt * sizeof(float) +
-         (size_t)2 * kAttnScratchFloats * sizeof(float) + kWarps * sizeof(float);
+  if (blockIdx.x == 0 && threadIdx.x == 0) bar->epoch = bar->epoch + 1;
+  if (trace && threadIdx.x == 0) trace[blockIdx.x] = -1;  // left the kernel
 }
 
 }  // namespace
@@ -492,7 +641,7 @@ EMBER_API int ember_decode_program_op_size() { return (int)sizeof(EmberOp); }
 // ready for the next).
 EMBER_API int ember_decode_program_state_size() { return (int)sizeof(GridBarrier); }
 
-// Runs a program of `n_ops` operations (device array) for up to 16 rows.  `state`: the barrier's
+// Runs a program of `n_ops` operations (device array) for up to 8 rows.  `state`: the barrier's
 // state; `error`: one int on the device, zero before the run, non-zero afterwards if a block gave
 // up waiting at a barrier (1) or an index of the step's description was out of range (2); the
 // results are then not valid.
@@ -501,26 +650,25 @@ EMBER_API int ember_decode_program_state_size() { return (int)sizeof(GridBarrier
 // is still readable after a fault; from entry 256 on, the time at which block 0 began each operation.
 EMBER_API int ember_decode_program_run(const void* ops, int n_ops, int max_rows, void* state, int* error, int* trace,
                                        cudaStream_t stream) {
-  EMBER_CHECK(n_ops > 0 && max_rows > 0 && max_rows <= 16, "decode_program: %d operations for %d rows", n_ops, max_rows);
+  EMBER_CHECK(n_ops > 0 && max_rows > 0 && max_rows <= kRows, "decode_program: %d operations for %d rows (at most 8)", n_ops,
+              max_rows);
   static int sms = 0;
-  static bool configured[2] = {false, false};
   if (!sms) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return ember_fail("decode_program: %s", cudaGetErrorString(e));
   }
-  const int mt = max_rows <= 8 ? 1 : 2;
-  const size_t smem = program_smem(mt);
-  const void* fn = mt == 1 ? (const void*)decode_program_kernel<1> : (const void*)decode_program_kernel<2>;
-  if (!configured[mt - 1]) {
+  const size_t smem = kProgramSmem;
+  const void* fn = (const void*)decode_program_kernel;
+  static bool configured = false;
+  if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ember_fail("decode_program: %s", cudaGetErrorString(e));
     int per_sm = 0;
-    e = mt == 1 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_program_kernel<1>, kThreads, smem)
-                : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_program_kernel<2>, kThreads, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_program_kernel, kThreads, smem);
     if (e != cudaSuccess || per_sm < 1) return ember_fail("decode_program: the kernel does not fit an SM");
-    configured[mt - 1] = true;
+    configured = true;
   }
   GridBarrier* bar = static_cast<GridBarrier*>(state);
   void* args[] = {(void*)&ops, (void*)&n_ops, (void*)&bar, (void*)&error, (void*)&trace};

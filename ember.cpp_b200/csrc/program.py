@@ -16,7 +16,9 @@ import torch
 from .ops import _ACT, KernelError, LazyNorm, _code
 
 OP_EMBED, OP_LAYERNORM, OP_LINEAR, OP_ATTENTION = 0, 1, 2, 3
-MAX_ROWS = 16
+MAX_ROWS = 8
+MAX_K = 6656           # 13 slices of 32 values for each of the kernel's 16 warps
+NORM_WIDTH = 2048      # the widest row the kernel norms inside a product
 
 _i, _f, _p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -32,6 +34,17 @@ class EmberOp(ctypes.Structure):
 
 class NotRecordable(Exception):
     """The step asked for something the persistent kernel does not do."""
+
+
+class RecordedNorm:
+    """A layer norm whose only reader is the product that follows: it runs in that product's prologue."""
+
+    def __init__(self, ops, x, w, b, eps, out_dtype):
+        self.ops, self.x, self.w, self.b, self.eps, self.dtype = ops, x, w, b, float(eps), out_dtype
+        self.shape = x.shape
+
+    def materialize(self):
+        return self.ops.layernorm(self.x, self.w, self.b, self.eps, self.dtype)
 
 
 class RecordingOps:
@@ -69,6 +82,9 @@ class RecordingOps:
         rows, d = x.shape
         if x.dtype != torch.float32:
             raise NotRecordable("layer norm of a non-float32 stream")
+        if (lazy and out_dtype == torch.bfloat16 and d % 8 == 0 and d <= NORM_WIDTH and rows <= MAX_ROWS
+                and w.dtype == torch.float32 and b.dtype == torch.float32):
+            return RecordedNorm(self, x, w, b, eps, out_dtype)
         out = self._new((rows, d), out_dtype, x.device)
         self._add(type=OP_LAYERNORM, M=rows, K=d, eps=float(eps), out_f32=int(out_dtype == torch.float32), a=x, w=w, w2=b,
                   out=out)
@@ -79,14 +95,23 @@ class RecordingOps:
             a = a.materialize()
         if act not in _ACT:
             raise KernelError(f"linear: activation {act!r}")
+        norm = None
+        if isinstance(a, RecordedNorm):
+            if w.dtype == torch.bfloat16:
+                norm, a = a, a.x
+            else:
+                a = a.materialize()
         M, K = a.shape
         N = w.shape[0]
-        if w.dtype != torch.bfloat16 or a.dtype != torch.bfloat16 or w.shape[1] != K or K % 8 or M > MAX_ROWS:
-            raise NotRecordable("a linear layer that is not a few bfloat16 rows with K a multiple of 8")
+        if (w.dtype != torch.bfloat16 or (norm is None and a.dtype != torch.bfloat16) or w.shape[1] != K or K % 8
+                or M > MAX_ROWS or K > MAX_K or N >= 1 << 22):
+            raise NotRecordable("a linear layer that is not a few bfloat16 rows with K a multiple of 8 up to 6,656")
         target = torch.float32 if residual is not None else (out_dtype or torch.bfloat16)
         out = residual if residual is not None else self._new((M, N), target, a.device)
+        fused = {} if norm is None else dict(reserved=1, w2=norm.w, reserved_ptr=norm.b, eps=norm.eps)
         self._add(type=OP_LINEAR, M=M, N=N, K=K, act=_ACT[act], out_f32=int(target == torch.float32), a=a, w=w,
-                  bias=bias if bias is not None else None, residual=residual if residual is not None else None, out=out)
+                  bias=bias if bias is not None else None, residual=residual if residual is not None else None, out=out,
+                  **fused)
         return out
 
     def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False):

@@ -216,7 +216,7 @@ class Engine:
             bucket *= 2
         host, shape = self.prepare(entries, pad_to=bucket, want_all=True)
         g = None
-        if self.decode_programs and bucket <= 16:
+        if self.decode_programs and bucket <= 8:
             g = self._programs.get(bucket)
             if g is None:
                 try:
