@@ -74,7 +74,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
   __nv_bfloat16* sK = sQ + kRows * LD;      // [2][64][LD]
   __nv_bfloat16* sV = sK + 2 * kRows * LD;  // [2][64][LD]
 
-  const int tile = blockIdx.x, h = blockIdx.y, s = blockIdx.z;
+  // the last tiles of a sequence have the most keys before them: they are handed out first, so that the
+  // launch does not end on a few long blocks
+  const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, s = blockIdx.z;
   const int n_new = seq_new[s];
   if (tile * kRows >= n_new) return;
   const int rows = min(kRows, n_new - tile * kRows);

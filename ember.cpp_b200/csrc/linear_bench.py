@@ -6,7 +6,8 @@
 `lt` is cuBLASLt with its epilogue, `tc` this library's tcgen05 kernel.  Each timed region follows
 a write of 256 MiB (larger than L2), is bracketed by CUDA events, and the median is printed.  With
 --chain C the region is C launches in a row and the time is divided by C: the host's work for a
-launch then hides behind the launch before it, as it does inside a model's step.
+launch then hides behind the launch before it, as it does inside a model's step; with --graph the
+chain is captured once and replayed, as the engine's decode step is.
 """
 from __future__ import annotations
 
@@ -28,6 +29,7 @@ def main() -> None:
     ap.add_argument("--only", default=None, choices=["tc", "lt"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--chain", type=int, default=1)
+    ap.add_argument("--graph", action="store_true", help="capture the chain in a CUDA graph and time its replay")
     args = ap.parse_args()
     ops = CudaOps()
     M, N, K = args.M, args.N, args.K
@@ -50,13 +52,21 @@ def main() -> None:
             continue
         for _ in range(3):
             fn()
+        run = fn
+        if args.graph:        # the host's part of a launch is then outside the timed region altogether
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(args.chain):
+                    fn()
+            run = graph.replay
         times = []
         for _ in range(args.iters):
             flush.zero_()
             t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             t0.record()
-            for _ in range(args.chain):
-                fn()
+            for _ in range(1 if args.graph else args.chain):
+                run()
             t1.record()
             torch.cuda.synchronize()
             times.append(t0.elapsed_time(t1) / args.chain)

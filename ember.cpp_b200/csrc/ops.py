@@ -43,6 +43,8 @@ _SIGNATURES = {
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void],
     "ember_attention_prefill": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ember_attention_prefill_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_void],
 }
 
@@ -96,8 +98,9 @@ def load_library() -> ctypes.CDLL:
         getattr(lib, name).restype = _c_int
     lib.ember_decode_program_run.argtypes = [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void]
     lib.ember_decode_program_run.restype = _c_int
-    lib.ember_linear_tc_status.argtypes = []
-    lib.ember_linear_tc_status.restype = _c_int
+    for name in ("ember_linear_tc_status", "ember_attention_tc_status"):
+        getattr(lib, name).argtypes = []
+        getattr(lib, name).restype = _c_int
     lib._path = path
     return lib
 
@@ -131,6 +134,9 @@ class CudaOps:
         # Measured on GPT-2 XL's four products the library is ahead: at 2,048 rows 133 against 205
         # microseconds a layer, at 16,384 rows the tcgen05 kernel reaches 87 % of it on the QKV product.
         self.gemm = os.environ.get("EMBER_GEMM", "lt")
+        # Prefill attention with head size 64 runs on the tcgen05 kernel; EMBER_ATTENTION=mma keeps it
+        # on the mma.sync kernel (which takes every other head size anyway).
+        self.attention_tc = os.environ.get("EMBER_ATTENTION", "tc") != "mma"
         if self.gemm not in ("tc", "lt"):
             raise KernelError(f"EMBER_GEMM={self.gemm!r}: 'tc' (this library's tcgen05 kernel) or 'lt' (cuBLASLt)")
 
@@ -297,6 +303,10 @@ class CudaOps:
         if code:
             role = {1: "the TMA producer", 2: "the product issuer", 3: "the epilogue", 4: "copies in flight"}.get(code, code)
             raise KernelError(f"linear_tc: a wait ran out ({role}); the results of that launch are not valid")
+        code = self.lib.ember_attention_tc_status()
+        if code:
+            role = {11: "the TMA loader", 12: "the product issuer", 13: "the softmax warps"}.get(code, code)
+            raise KernelError(f"attention_prefill_tc: a wait ran out ({role}); the results of that launch are not valid")
 
     # ------------------------------------------------------------------ cache and attention
     def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):
@@ -332,6 +342,13 @@ class CudaOps:
             return out
         if store:
             self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim)
+        if qkv.dtype == torch.bfloat16 and scale > 0 and self.attention_tc:
+            rc = self._call("ember_attention_prefill_tc", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                            out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),
+                            plan.cu_new.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.n, plan.max_new, plan.T,
+                            cache.k.shape[0], n_heads, kv_heads, head_dim, float(scale), int(window), allow=(2,))
+            if rc == 0:
+                return out
         if qkv.dtype == torch.bfloat16 and scale > 0:
             rc = self._call("ember_attention_prefill", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),

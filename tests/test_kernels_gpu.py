@@ -341,6 +341,27 @@ def test_attention_window(ops, dtype, window):
     assert (got - want).abs().max().item() < ATOL[dtype]
 
 
+@pytest.mark.parametrize("heads, kv_heads", [(25, 25), (8, 2), (3, 1)])
+@pytest.mark.parametrize("window", [0, 1, 70, 200])
+def test_attention_on_the_tcgen05_kernel(ops, heads, kv_heads, window):
+    """Head size 64 in bfloat16 takes the TMA/tcgen05 prefill kernel: prompts that end inside a
+    128-row tile, on its edge and past it, tokens added on top of cached ones (tiles that start in
+    the middle of a page), grouped heads, windows that cut pages, scrambled page order, and the
+    mma.sync kernel as its twin."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    seqs = [(0, 300), (0, 128), (0, 1), (70, 129), (64, 64), (200, 57), (0, 127)]
+    assert ops.attention_tc
+    launches = ops.launches
+    got, want = run_attention(ops, seqs, heads, kv_heads, 64, "bfloat16", window=window, seed=7 + window, poison=1e30)
+    torch.cuda.synchronize()
+    ops.check()
+    assert (got - want).abs().max().item() < ATOL["bfloat16"]
+    twin = CudaOps()
+    twin.attention_tc = False
+    other, _ = run_attention(twin, seqs, heads, kv_heads, 64, "bfloat16", window=window, seed=7 + window, poison=1e30)
+    assert (got - other).abs().max().item() < ATOL["bfloat16"]
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
     """One early key is made to stand out (its score far above the rest): every later query must
