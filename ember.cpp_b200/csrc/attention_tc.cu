@@ -48,7 +48,7 @@ struct AttArgs {
   const int* seq_new;
   const int* cu_new;
   const int* pages;
-  int max_blocks, n_heads, kv_heads, window, n_pages;
+  int max_blocks, n_heads, kv_heads, window, n_pages, n_seqs, n_tiles;
   float scale_log2;
   int* status;
 };
@@ -80,8 +80,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   __shared__ unsigned long long bars[15];
   __shared__ unsigned s_tmem;
 
-  // the last tiles of a sequence have the most keys before them: they are handed out first
-  const int tile = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, s = blockIdx.z;
+  // Blocks are handed out in the order of their numbers.  The last tiles of a sequence have the
+  // most keys before them, so the numbering goes by tile first, last tiles first, and inside a
+  // tile over heads and sequences: the long blocks all start at once and the short ones fill in.
+  const int per_tile = p.n_heads * p.n_seqs;
+  const int tile = p.n_tiles - 1 - (int)blockIdx.x / per_tile;
+  const int h = ((int)blockIdx.x % per_tile) % p.n_heads, s = ((int)blockIdx.x % per_tile) / p.n_heads;
   const int n_new = p.seq_new[s];
   if (tile * kQRows >= n_new) return;
   const int rows = min(kQRows, n_new - tile * kQRows);
@@ -226,12 +230,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       // Most pages lie wholly before every row of the tile (and inside every row's window): only
       // the pages on the diagonal and at the window's edge are masked, by selection.
       const bool all_seen = key0 + kKeys - 1 <= p0 && (p.window <= 0 || key0 > p_last - p.window);
-      float m_blk = -INFINITY;
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains, not one of 64 links
       if (all_seen) {
 #pragma unroll
         for (int half = 0; half < 2; ++half)
 #pragma unroll
-          for (int c = 0; c < 32; ++c) m_blk = fmaxf(m_blk, __uint_as_float(sc[half][c]));
+          for (int c = 0; c < 32; ++c) m4[c & 3] = fmaxf(m4[c & 3], __uint_as_float(sc[half][c]));
       } else {
         const int hi = pos - key0;                                            // keys with index <= hi
         const int lo = p.window > 0 ? pos - p.window + 1 - key0 : -(1 << 30);  // and >= lo
@@ -242,9 +246,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             const int key = half * 32 + c;
             const float v = (key <= hi && key >= lo) ? __uint_as_float(sc[half][c]) : -INFINITY;
             sc[half][c] = __float_as_uint(v);
-            m_blk = fmaxf(m_blk, v);
+            m4[c & 3] = fmaxf(m4[c & 3], v);
           }
       }
+      const float m_blk = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       const bool grow = m_blk > m_used && (m_used == -INFINITY || (m_blk - m_used) * p.scale_log2 > kRescale);
       float corr = 1.0f;
       if (grow) {
@@ -279,7 +284,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (!ok) break;
       }
       unsigned char* p_row = p_rows + b * kPBytes;
-      float row_sum = 0.f;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int half = 0; half < 2; ++half)
 #pragma unroll
@@ -289,14 +294,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
           for (int j = 0; j < 4; ++j) {
             const float e0 = ex2(__uint_as_float(sc[half][c8 * 8 + 2 * j]) * p.scale_log2 - base_e);
             const float e1 = ex2(__uint_as_float(sc[half][c8 * 8 + 2 * j + 1]) * p.scale_log2 - base_e);
-            row_sum += e0 + e1;
+            sum4[j] += e0 + e1;
             const __nv_bfloat162 v2 = __floats2bfloat162_rn(e0, e1);
             w[j] = *reinterpret_cast<const unsigned*>(&v2);
           }
           const int chunk = half * 4 + c8;
           *reinterpret_cast<uint4*>(p_row + ((chunk ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-      l_run += row_sum;
+      l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       fence_async_smem();  // P is read by the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(p_full + 8 * b);
@@ -385,9 +390,12 @@ EMBER_API int ember_attention_prefill_tc(const void* qkv, const void* kc, const 
   a.out = static_cast<__nv_bfloat16*>(out);
   a.seq_slot = seq_slot, a.seq_start = seq_start, a.seq_new = seq_new, a.cu_new = cu_new, a.pages = pages;
   a.max_blocks = max_blocks, a.n_heads = n_heads, a.kv_heads = kv_heads, a.window = window, a.n_pages = n_pages;
+  a.n_seqs = n_seqs, a.n_tiles = (max_new + kQRows - 1) / kQRows;
   a.scale_log2 = scale * 1.4426950408889634f;
   a.status = st.device;
-  dim3 grid((max_new + kQRows - 1) / kQRows, n_heads, n_seqs);
+  const long long blocks = (long long)a.n_tiles * n_heads * n_seqs;
+  EMBER_CHECK(blocks < (1ll << 31), "attention_prefill_tc: %lld blocks exceed one launch", blocks);
+  dim3 grid((unsigned)blocks);
   attention_tc_kernel<<<grid, kThreads, kSmem, stream>>>(map_q, map_k, map_v, a);
   EMBER_LAUNCH_OK("attention_prefill_tc");
   return 0;
