@@ -6,7 +6,8 @@ weights (batch 8 by default, 128-token prompts decoded towards the 1,024-token c
 
 Prints ONE JSON line on stdout (everything else goes to stderr).  A "step" is one decode step of
 the whole batch.  `value` times K steps of the engine's own loop (step function + device sampler,
-ids read back every step) with CUDA events; `e2e` is the same count of tokens through the Python
+every step's ids read back to the host; the loop, like the library's generation loop, queues a step
+with the ids of the step before still on the device and reads them afterwards) with CUDA events; `e2e` is the same count of tokens through the Python
 entry point (`Session.generate_batch`, host ids in, host ids out) by wall clock between its first
 and last new token.  ember.cpp publishes no GPT-2 speed, so `vs_baseline` is null.
 """
@@ -190,7 +191,10 @@ def main() -> int:
         logits = engine.step([(s, p, [prompt_len - 1]) for s, p in zip(slots, prompts)])
         streams = torch.arange(B, dtype=torch.int32, device="cuda")
         counters = torch.zeros(B, dtype=torch.int32, device="cuda")
-        toks = sampler.sample(logits, params, streams, counters).tolist()
+        ids = sampler.sample(logits, params, streams, counters)
+        on_the_way = sampler.fetch(ids)
+        rows = list(range(B))
+        generated = []
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         cache_bytes = 0
         launches0 = 0
@@ -202,9 +206,15 @@ def main() -> int:
                 start.record()
             if i >= warm:
                 cache_bytes += sum(engine.length(s) + 1 for s in slots) * kv_bytes_per_pos
-            logits = engine.step([(s, [t], [0]) for s, t in zip(slots, toks)], borrow=True)
+            # as Generator does: the step takes its tokens from the sampler's output on the device and is
+            # queued before the host reads those ids
+            logits = engine.step([(s, [0], [0]) for s in slots], borrow=True, device_tokens=(ids, rows))
             counters += 1
-            toks = sampler.sample(logits, params, streams, counters).tolist()
+            following = sampler.sample(logits, params, streams, counters)
+            fetched = sampler.fetch(following)
+            generated.append(on_the_way.tolist())
+            ids, on_the_way = following, fetched
+        generated.append(on_the_way.tolist())
         stop.record()
         torch.cuda.synchronize()
         windows.append((w0, time.time()))

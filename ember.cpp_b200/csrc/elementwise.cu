@@ -140,6 +140,28 @@ EMBER_API int ember_layernorm(const float* x, const float* w, const float* b, vo
   return 0;
 }
 
+// ---------------------------------------------------------------------------- tokens sampled on the device
+// A step whose tokens are the ids an earlier step's sampler drew takes them where they are:
+// tokens[i] = ids[src[i]] where src[i] >= 0 (else the host's token stays).  The host can then
+// queue the step before it has read those ids itself.
+__global__ void take_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src, const int* __restrict__ ids, int n,
+                                   int n_ids, int vocab) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int r = src[i];
+  if (r < 0 || r >= n_ids) return;
+  const int t = ids[r];
+  tokens[i] = (t >= 0 && t < vocab) ? t : 0;  // a sampler's id is always in range; nothing else may reach the table
+}
+
+EMBER_API int ember_take_tokens(int* tokens, const int* src, const int* ids, int n, int n_ids, int vocab,
+                                cudaStream_t stream) {
+  EMBER_CHECK(n > 0 && n_ids > 0 && vocab > 0, "take_tokens: %d tokens from %d ids, vocabulary %d", n, n_ids, vocab);
+  take_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(tokens, src, ids, n, n_ids, vocab);
+  EMBER_LAUNCH_OK("take_tokens");
+  return 0;
+}
+
 // ---------------------------------------------------------------------------- row gather
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, float* __restrict__ out,
                                    int d) {

@@ -28,6 +28,7 @@ _SIGNATURES = {
     "ember_embed": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
     "ember_layernorm": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
+    "ember_take_tokens": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
     "ember_act_inplace": [_c_void, _c_size, _c_int, _c_int, _c_void],
     "ember_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_bf16": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -218,6 +219,14 @@ class CudaOps:
         self._call("ember_layernorm", self._dense(x, "layernorm input").data_ptr(), w.data_ptr(), b.data_ptr(),
                    out.data_ptr(), rows, d, float(eps), _code(out_dtype))
         return out
+
+    def take_tokens(self, tokens, token_src, ids, vocab_size: int) -> None:
+        """tokens[i] = ids[token_src[i]] where token_src[i] >= 0: a step's tokens taken from an earlier
+        step's sampled ids on the device."""
+        if ids.dtype != torch.int32 or not ids.is_cuda or not ids.is_contiguous():
+            raise KernelError("take_tokens: sampled ids are a contiguous int32 CUDA tensor")
+        self._call("ember_take_tokens", tokens.data_ptr(), token_src.data_ptr(), ids.data_ptr(), tokens.shape[0],
+                   ids.numel(), int(vocab_size))
 
     def gather_rows(self, x, rows, n_rows):
         out = torch.empty((n_rows, x.shape[1]), dtype=torch.float32, device=x.device)

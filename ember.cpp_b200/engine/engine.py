@@ -156,16 +156,24 @@ class Engine:
                 if not 0 <= int(w) < len(tokens):
                     raise StepError(f"slot {slot}: wanted place {w} is not among its {len(tokens)} new tokens")
 
-    def prepare(self, entries, pad_to: int = 0, want_all: bool = False):
+    def prepare(self, entries, pad_to: int = 0, want_all: bool = False, device_tokens=None):
         """Checks a step, takes its pages and builds its description; launches nothing."""
         self.check_step(entries)
+        rows = None
+        if device_tokens is not None:
+            ids, rows = device_tokens
+            rows = [int(r) for r in rows]
+            if len(rows) != len(entries) or any(len(t) != 1 for _, t, _ in entries):
+                raise StepError("tokens taken from the device: one row for each sequence, one token a sequence")
+            if ids.dtype != torch.int32 or ids.dim() != 1 or any(not 0 <= r < ids.shape[0] for r in rows):
+                raise StepError("tokens taken from the device: rows of a one-dimensional int32 tensor of sampled ids")
         shape = [(slot, len(tokens)) for slot, tokens, _ in entries]
         try:
             self.cache.reserve(shape)
         except CacheError as e:
             raise StepError(str(e)) from None
         tables = [g.table for g in self.cache.groups]
-        return build_step(entries, self.cache.lengths, tables, self.cache.max_blocks, pad_to, want_all), shape
+        return build_step(entries, self.cache.lengths, tables, self.cache.max_blocks, pad_to, want_all, rows), shape
 
     def _stage(self, staging: "_Staging", host, device_buffer) -> None:
         """Host description -> pinned memory -> device, without racing an earlier copy."""
@@ -181,15 +189,21 @@ class Engine:
         self._stage(self._staging, host, self._device_buffer)
         return StepPlan(host, self._device_buffer)
 
-    def step(self, entries, borrow: bool = False) -> torch.Tensor | None:
+    def step(self, entries, borrow: bool = False, device_tokens=None) -> torch.Tensor | None:
         """entries: (slot, tokens, want) per sequence; `want` lists the places among this step's
         tokens whose logits are returned.  Returns float32 [sum of wants, vocab] on the device,
         in the order of the entries and of `want` (None if nothing is wanted).  With `borrow` the
-        result may be a view of a buffer that the next step overwrites."""
+        result may be a view of a buffer that the next step overwrites.
+        device_tokens = (ids, rows): every sequence brings one token, and the token of entry i is
+        ids[rows[i]], an id that an earlier step's sampler left on the device (the entry's own
+        token value is a placeholder).  The step can then be queued before the host has read
+        those ids."""
         if self.cuda_graphs and all(len(t) == 1 for _, t, _ in entries):
-            return self._graph_step(entries, borrow)
-        host, shape = self.prepare(entries)
+            return self._graph_step(entries, borrow, device_tokens)
+        host, shape = self.prepare(entries, device_tokens=device_tokens)
         plan = self.upload(host)
+        if device_tokens is not None:
+            self.ops.take_tokens(plan.tokens, plan.token_src, device_tokens[0], self.vocab_size)
         logits = self.run(plan)
         self._account(host, shape)
         return logits
@@ -204,7 +218,7 @@ class Engine:
         return self.model.forward(ctx)
 
     # ------------------------------------------------------------------ one token each, as a replayed graph
-    def _graph_step(self, entries, borrow: bool):
+    def _graph_step(self, entries, borrow: bool, device_tokens=None):
         """A step in which every sequence brings one token runs as a CUDA graph captured once per
         batch-size bucket (ember.cpp captures its one-token step once and replays it with
         [token, pos, kv_row] in device memory, graph_ir.cpp:4306-4373).  The batch is padded to the
@@ -214,7 +228,8 @@ class Engine:
         bucket = 1
         while bucket < n_real:
             bucket *= 2
-        host, shape = self.prepare(entries, pad_to=bucket, want_all=True)
+        host, shape = self.prepare(entries, pad_to=bucket, want_all=True, device_tokens=device_tokens)
+        ids = None if device_tokens is None else device_tokens[0]
         g = None
         if self.decode_programs and bucket <= 8:
             g = self._programs.get(bucket)
@@ -228,7 +243,7 @@ class Engine:
             g = self._graphs.get(bucket)
             if g is None:
                 g = self._graphs[bucket] = _DecodeGraph(self, host)
-        g.replay(self, host)
+        g.replay(self, host, ids)
         self._account(host, shape)
         rows = [i for i, (_, _, want) in enumerate(entries) for _ in want]
         if not rows:
@@ -281,12 +296,14 @@ class _DecodeProgramStep:
         self.program = DecodeProgram(engine.ops.lib, recording, host.n, dev)
         self.ran = False
 
-    def replay(self, engine: Engine, host) -> None:
+    def replay(self, engine: Engine, host, ids=None) -> None:
         if host.packed.shape[0] != self.size:
             raise StepError("the step's description changed size under a recorded program")
         if self.ran:
             self.program.check()      # the step before: by now it is over, so this does not wait for long
         engine._stage(self.staging, host, self.buffer)
+        if ids is not None:
+            engine.ops.take_tokens(self.plan.tokens, self.plan.token_src, ids, engine.vocab_size)
         self.program.run()
         self.ran = True
         engine.ops.launches += 1
@@ -314,10 +331,12 @@ class _DecodeGraph:
             self.logits = engine.run(self.plan)
         self.launches = engine.ops.launches - before
 
-    def replay(self, engine: Engine, host) -> None:
+    def replay(self, engine: Engine, host, ids=None) -> None:
         if host.packed.shape[0] != self.size:
             raise StepError("the step's description changed size under a captured graph")
         engine._stage(self.staging, host, self.buffer)
+        if ids is not None:           # outside the graph: the ids' address changes from step to step
+            engine.ops.take_tokens(self.plan.tokens, self.plan.token_src, ids, engine.vocab_size)
         if self.graph is None:
             self.logits = engine.run(self.plan)
         else:

@@ -85,9 +85,10 @@ def plan_batches(prompt_lengths: Sequence[int], max_new_tokens: int, max_batch_s
 
 
 class Generator:
-    def __init__(self, engine, sampler: Sampler | None = None):
+    def __init__(self, engine, sampler: Sampler | None = None, run_ahead: bool = True):
         self.engine = engine
         self.sampler = sampler or Sampler(engine.ops)
+        self.run_ahead = bool(run_ahead) and hasattr(engine.ops, "take_tokens")
         self.stats = {"batches": 0, "prefill_steps": 0, "decode_steps": 0, "prompt_tokens": 0, "new_tokens": 0}
 
     def generate(self, prompts: Sequence[Sequence[int]], params: GenerationParams = GenerationParams(),
@@ -109,36 +110,62 @@ class Generator:
         return results  # type: ignore[return-value]
 
     def _run_batch(self, batch, prompts, params, stop_ids, max_pos, results, on_token, first_stream) -> None:
+        """One batch from its prompts to its last token.
+
+        The loop runs one step ahead of what the host has read: a step's tokens stay on the device
+        and the next step takes them from there (`Engine.step(device_tokens=...)`), so the host
+        queues step t+1, then reads step t's ids (by then long computed) and decides who ended.
+        Whether a sequence ends by its count of new tokens or by the context is known without the
+        token; a stop id is not, so a sequence that drew one has been stepped once more for
+        nothing: that row is dropped, and its slot is closed like any other."""
         eng = self.engine
         self.stats["batches"] += 1
         slots = {i: eng.open() for i in batch}
         generated: dict[int, list[int]] = {i: [] for i in batch}
+
+        def launch(active, entries, device_tokens):
+            logits = eng.step(entries, borrow=device_tokens is not None, device_tokens=device_tokens)
+            ids = self.sampler.sample(logits, params.sampling, [first_stream + i for i in active],
+                                      [len(generated[i]) + (device_tokens is not None) for i in active])
+            # (requests, their ids on the device and on the way to the host, positions in the cache after the step)
+            return active, ids, self.sampler.fetch(ids), [eng.length(slots[i]) for i in active]
+
         try:
             active = list(batch)
-            entries = [(slots[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in active]
             self.stats["prefill_steps"] += 1
             self.stats["prompt_tokens"] += sum(len(prompts[i]) for i in active)
-            while active:
-                logits = eng.step(entries)
-                tokens = self.sampler.sample(logits, params.sampling, [first_stream + i for i in active],
-                                             [len(generated[i]) for i in active]).tolist()
-                still = []
-                for i, tok in zip(active, tokens):
+            pending = launch(active, [(slots[i], list(prompts[i]), [len(prompts[i]) - 1]) for i in active], None)
+            while pending is not None:
+                active, ids, on_the_way, cached = pending
+                following = None
+                if self.run_ahead:
+                    # who goes on whatever token was drawn: not those at their count or at the context's end
+                    ahead = [(row, i) for row, i in enumerate(active)
+                             if results[i] is None and len(generated[i]) + 1 < params.max_new_tokens
+                             and not (max_pos is not None and cached[row] + 1 > max_pos)]
+                    if ahead:
+                        self.stats["decode_steps"] += 1
+                        following = launch([i for _, i in ahead], [(slots[i], [0], [0]) for _, i in ahead],
+                                           (ids, [row for row, _ in ahead]))
+                tokens = on_the_way.tolist()   # waits for the step that drew them; the next one is queued already
+                for row, (i, tok) in enumerate(zip(active, tokens)):
+                    if results[i] is not None:
+                        continue           # it ended a step ago on a stop id: this row was computed for nothing
                     generated[i].append(tok)
                     self.stats["new_tokens"] += 1
                     if on_token is not None:
                         on_token(i, tok)
-                    why = finish_reason(tok, len(generated[i]), eng.length(slots[i]), stop_ids, params.max_new_tokens,
-                                        max_pos)
-                    if why is None:
-                        still.append(i)
-                    else:
+                    why = finish_reason(tok, len(generated[i]), cached[row], stop_ids, params.max_new_tokens, max_pos)
+                    if why is not None:
                         results[i] = Generation(generated[i], why)
                         eng.close(slots.pop(i))   # the slot and its pages are free for the next batch at once
-                active = still
-                entries = [(slots[i], [generated[i][-1]], [0]) for i in active]
-                if active:
-                    self.stats["decode_steps"] += 1
+                if following is None and not self.run_ahead:
+                    still = [i for i in active if results[i] is None]
+                    if still:
+                        self.stats["decode_steps"] += 1
+                        pending = launch(still, [(slots[i], [generated[i][-1]], [0]) for i in still], None)
+                        continue
+                pending = following
         finally:
             for slot in slots.values():
                 eng.close(slot)

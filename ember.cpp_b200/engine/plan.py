@@ -8,6 +8,7 @@ ember.cpp's batch path gathers, per step, the active sequences' (token, position
 once:
 
   tokens[T] positions[T] token_seq[T]            one entry per token, sequences back to back
+  token_src[T]                                   -1, or the row of an earlier step's sampled ids that is this token
   seq_slot[n] seq_start[n] seq_new[n] cu_new[n+1] one entry per sequence (slot -1: padding)
   want_rows[R]                                   rows of the token list whose logits are wanted
   pages[g][n, max_blocks]                        per cache group, each sequence's page numbers
@@ -43,6 +44,7 @@ class StepLayout:
         self.tokens = take(self.T)
         self.positions = take(self.T)
         self.token_seq = take(self.T)
+        self.token_src = take(self.T)
         self.seq_slot = take(self.n)
         self.seq_start = take(self.n)
         self.seq_new = take(self.n)
@@ -67,12 +69,15 @@ class HostStep:
     wants_every_row: bool = False # the wanted rows are all rows, in order
 
 
-def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, want_all: bool = False) -> HostStep:
+def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, want_all: bool = False,
+               token_rows=None) -> HostStep:
     """entries: (slot, tokens, want) per sequence, `want` being indices into that sequence's new
     tokens.  lengths: slot -> positions held before the step.  page_tables: per group, a function
     (slots, width) -> int32 [n, width].  pad_to: pad a one-token-each batch with dummy sequences
     up to this many (0: no padding).  want_all: every token's row is wanted, padding included, and
-    the entries' own `want` is left to the caller (the shape a replayed graph needs)."""
+    the entries' own `want` is left to the caller (the shape a replayed graph needs).  token_rows:
+    per entry the row of a device array of sampled ids that holds its (single) token, which the
+    device puts in place of the entry's own token value."""
     n_real = len(entries)
     single = all(len(t) == 1 for _, t, _ in entries)
     n = max(n_real, pad_to) if (single and pad_to) else n_real
@@ -80,6 +85,9 @@ def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, 
     R = T if want_all else sum(len(w) for _, _, w in entries)
     lay = StepLayout(T, n, R, max_blocks, len(page_tables))
     buf = np.zeros(lay.size, dtype=np.int32)
+    buf[lay.token_src:lay.token_src + T] = -1
+    if token_rows is not None and (len(token_rows) != n_real or not single):
+        raise ValueError("tokens taken from the device: one row for each entry, one token an entry")
     slots = []
     t0 = 0
     r0 = 0
@@ -96,6 +104,8 @@ def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, 
         buf[lay.tokens + t0: lay.tokens + t0 + k] = toks
         buf[lay.positions + t0: lay.positions + t0 + k] = np.arange(start, start + k)
         buf[lay.token_seq + t0: lay.token_seq + t0 + k] = i
+        if token_rows is not None and i < n_real:
+            buf[lay.token_src + t0] = token_rows[i]
         buf[lay.seq_slot + i] = slot
         buf[lay.seq_start + i] = start
         buf[lay.seq_new + i] = k
@@ -135,6 +145,7 @@ class StepPlan:
         self.tokens = view(lay.tokens, lay.T)
         self.positions = view(lay.positions, lay.T)
         self.token_seq = view(lay.token_seq, lay.T)
+        self.token_src = view(lay.token_src, lay.T)
         self.seq_slot = view(lay.seq_slot, lay.n)
         self.seq_start = view(lay.seq_start, lay.n)
         self.seq_new = view(lay.seq_new, lay.n)

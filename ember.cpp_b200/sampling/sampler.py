@@ -49,18 +49,83 @@ def uniform01(seed: int, stream: int, counter: int) -> float:
     return (z >> 40) / float(1 << 24)
 
 
+class IdsOnTheWay:
+    """Sampled ids on their way to the host: the copy runs on a stream of its own as soon as the
+    sampler has finished, beside whatever was queued on the main stream after it, so that reading
+    the ids of one step does not wait for the step that was queued behind it."""
+
+    def __init__(self, ids: torch.Tensor, stream, pinned):
+        self.ids = ids                      # kept alive until the copy has run
+        self.event = None
+        self.host = None
+        if ids.is_cuda:
+            drawn = torch.cuda.Event()
+            drawn.record()                  # on the stream the sampler ran on
+            self.host = pinned[:ids.shape[0]]
+            with torch.cuda.stream(stream):
+                stream.wait_event(drawn)
+                self.host.copy_(ids, non_blocking=True)
+                self.event = torch.cuda.Event()
+                self.event.record(stream)
+
+    def tolist(self) -> list[int]:
+        if self.event is None:
+            return self.ids.tolist()
+        self.event.synchronize()
+        return self.host.tolist()
+
+
 class Sampler:
     """Draws one token per row of logits on the device."""
 
     def __init__(self, ops):
         self.ops = ops
+        self._stream = None
+        self._pinned = []                   # four buffers in turn: a step's ids are read while later steps' are copied
+        self._turn = 0
+        self._hpinned = []                  # pinned staging for the per-row stream and counter numbers
+        self._hturn = 0
+
+    def fetch(self, ids: torch.Tensor) -> IdsOnTheWay:
+        """Starts copying sampled ids to the host without stopping the stream they were drawn on."""
+        if not ids.is_cuda:
+            return IdsOnTheWay(ids, None, None)
+        if self._stream is None:
+            self._stream = torch.cuda.Stream(device=ids.device)
+        n = ids.shape[0]
+        self._turn = (self._turn + 1) % 4
+        while len(self._pinned) < 4:
+            self._pinned.append(torch.empty(max(n, 64), dtype=torch.int32, pin_memory=True))
+        if self._pinned[self._turn].numel() < n:
+            self._pinned[self._turn] = torch.empty(n, dtype=torch.int32, pin_memory=True)
+        return IdsOnTheWay(ids, self._stream, self._pinned[self._turn])
 
     def sample(self, logits: torch.Tensor, params: SamplingParams, streams, counters) -> torch.Tensor:
         """logits: float32 [rows, vocab] on the device.  streams, counters: one int per row (lists
         or int32 tensors).  Returns int32 [rows] on the device."""
-        dev = logits.device
-        if not torch.is_tensor(streams):
-            streams = torch.tensor(list(streams), dtype=torch.int32, device=dev)
-        if not torch.is_tensor(counters):
-            counters = torch.tensor(list(counters), dtype=torch.int32, device=dev)
+        if not torch.is_tensor(streams) or not torch.is_tensor(counters):
+            streams, counters = self._to_device(list(streams), list(counters), logits.device)
         return self.ops.sample(logits, params.temperature, params.top_k, params.top_p, params.seed, streams, counters)
+
+    def _to_device(self, streams: list[int], counters: list[int], dev):
+        """Two lists of ints -> two int32 device tensors with one copy from pinned memory.  (A copy
+        from ordinary host memory would first wait for everything queued on the stream, which is
+        the step this sampler call is meant to be queued behind.)"""
+        n = len(streams)
+        both = torch.tensor(streams + counters, dtype=torch.int32)
+        if dev.type != "cuda":
+            return both[:n], both[n:]
+        self._hturn = (self._hturn + 1) % 8
+        while len(self._hpinned) < 8:
+            self._hpinned.append([torch.empty(256, dtype=torch.int32, pin_memory=True), None])
+        slot = self._hpinned[self._hturn]
+        if slot[1] is not None:
+            slot[1].synchronize()          # the copy that last read this buffer (eight calls ago) is over
+        if slot[0].numel() < 2 * n:
+            slot[0] = torch.empty(2 * n, dtype=torch.int32, pin_memory=True)
+        slot[0][:2 * n] = both
+        out = torch.empty(2 * n, dtype=torch.int32, device=dev)
+        out.copy_(slot[0][:2 * n], non_blocking=True)
+        slot[1] = torch.cuda.Event()
+        slot[1].record()
+        return out[:n], out[n:]

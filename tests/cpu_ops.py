@@ -81,6 +81,10 @@ class CpuOps:
                 out[t, h * head_dim:(h + 1) * head_dim] = pr @ v[:, h // rep, :]
         return out.to(out_dtype)
 
+    def take_tokens(self, tokens, token_src, ids, vocab_size):
+        take = token_src >= 0
+        tokens[take] = ids[token_src[take].long()].to(tokens.dtype)
+
     def gather_rows(self, x, rows, n_rows):
         return x[rows[:n_rows].long()]
 

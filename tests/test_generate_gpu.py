@@ -167,6 +167,29 @@ def test_greedy_generation_through_the_entry_point(tiny_folders, plains, name):
     assert session.engine.cache.slots.held == 0 and s16.engine.cache.slots.held == 0
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_running_a_step_ahead_changes_no_token_on_the_gpu(tiny_folders, plains, dtype):
+    """The generation loop queues a step with the ids of the step before still on the device
+    (`take_tokens`, then the replayed graph).  Against the loop that reads every id first: the
+    same tokens and reasons, with stop ids, unequal counts and batches one after another."""
+    plain = plains["tiny_a"]
+    prompts = [random_ids(800 + i, plain.vocab, n) for i, n in enumerate((4, 33, 64, 1, 90, 7, plain.n_positions - 1))]
+    out = []
+    for ahead in (True, False):
+        session = E.Session(tiny_folders["tiny_a"], max_batch_size=3, dtype=dtype, max_tokens=1024, seed=3)
+        session.generator.run_ahead = ahead
+        free = session.generate_detailed(prompts, steps=9, temperature=0.9, top_k=30, top_p=0.95, stop_token_ids=[])
+        stops = [free[1].tokens[3], free[4].tokens[0]]
+        session.set_seed(3)
+        got = session.generate_detailed(prompts, steps=9, temperature=0.9, top_k=30, top_p=0.95, stop_token_ids=stops)
+        out.append([(g.tokens, g.finish_reason) for g in free + got])
+        assert got[1].finish_reason == "stop" and got[4].finish_reason == "stop" and got[6].finish_reason == "context"
+        session.engine.ops.check()
+        session.engine.cache.check()
+        assert session.engine.cache.slots.held == 0
+    assert out[0] == out[1]
+
+
 def test_temperature_generation_equals_plain(tiny_folders, plains):
     plain = plains["tiny_b"]
     prompts = [random_ids(600 + i, plain.vocab, n) for i, n in enumerate((1, 9, 40, 63))]

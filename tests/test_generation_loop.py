@@ -50,6 +50,7 @@ def test_step_description_layout():
     assert b[lay.want_rows:lay.want_rows + 3].tolist() == [0, 2, 3]
     assert b[lay.pages[0]:lay.pages[0] + 4].tolist() == [0, 1, 2, 3]
     assert all(off % 4 == 0 for off in (lay.tokens, lay.positions, lay.seq_slot, lay.want_rows, lay.pages[0]))
+    assert b[lay.token_src:lay.token_src + 4].tolist() == [-1, -1, -1, -1]      # every token is the host's own
     # a padded one-token batch: dummy sequences of slot -1, every row wanted
     h = build_step([(5, [4], [])], lengths, tables, 2, pad_to=4, want_all=True)
     assert (h.T, h.n, h.n_want, h.all_single) == (4, 4, 4, True)
@@ -57,6 +58,11 @@ def test_step_description_layout():
     assert h.max_end == 71
     with pytest.raises(ValueError, match="wanted place"):
         build_step([(3, [1], [1])], lengths, tables, 2)
+    # tokens that an earlier step's sampler left on the device: the row of each, padding has none
+    h = build_step([(5, [0], []), (3, [0], [])], lengths, tables, 2, pad_to=4, want_all=True, token_rows=[2, 0])
+    assert h.packed[h.layout.token_src:h.layout.token_src + 4].tolist() == [2, 0, -1, -1]
+    with pytest.raises(ValueError, match="one token an entry"):
+        build_step([(3, [1, 2], [])], lengths, tables, 2, token_rows=[0])
 
 
 # ------------------------------------------------------------------------------ engine on the stand-in
@@ -139,6 +145,60 @@ def test_stop_token_ends_a_sequence_early(tiny_folders, plains):
         n = len(g.tokens)
         assert g.tokens == f.tokens[:n]   # what the others generate does not depend on who left
     assert session.engine.cache.slots.held == 0
+
+
+def test_running_a_step_ahead_changes_no_token(tiny_folders, plains):
+    """The loop queues step t+1 with the ids of step t still on the device and reads them
+    afterwards.  Against the loop that reads every id before it goes on: the same tokens, reasons
+    and callback order, with stop ids (whose sequences are stepped once for nothing), counts that
+    run out at different steps and a prompt that ends at the context's end; no slot is left."""
+    plain = plains["tiny_b"]
+    prompts = [random_ids(30 + i, plain.vocab, n) for i, n in enumerate((3, 20, plain.n_positions - 2, 8, 1))]
+    out = []
+    for ahead in (True, False):
+        session = E.Session(tiny_folders["tiny_b"], max_batch_size=4, dtype="float32", ops=CpuOps(), device="cpu",
+                            max_tokens=512)
+        session.generator.run_ahead = ahead
+        free = session.generate_detailed(prompts, steps=7, temperature=1.0, top_k=0, top_p=1.0, stop_token_ids=[])
+        stops = [free[0].tokens[1], free[3].tokens[4]]
+        session.set_seed(0)
+        seen = []
+        session.set_token_callback(lambda i, tok: seen.append((i, tok)))
+        got = session.generate_detailed(prompts, steps=7, temperature=1.0, top_k=0, top_p=1.0, stop_token_ids=stops)
+        out.append(([(g.tokens, g.finish_reason) for g in free], [(g.tokens, g.finish_reason) for g in got], seen))
+        assert got[0].finish_reason == "stop" and got[2].finish_reason == "context" and len(got[2].tokens) == 3
+        session.engine.cache.check()
+        assert session.engine.cache.slots.held == 0
+    assert out[0] == out[1]
+    for i, p in enumerate(prompts):
+        want, why = plain_gpt2.generate(plain, p, 7, 1.0, 0, 1.0, seed=0, stream=i, stop_ids=tuple(stops))
+        assert out[0][1][i] == (want, why)
+
+
+def test_tokens_taken_from_the_device_equal_tokens_from_the_host(cpu_engine, plains):
+    eng, plain = cpu_engine["tiny_a"], plains["tiny_a"]
+    a, b = random_ids(40, plain.vocab, 9), random_ids(41, plain.vocab, 4)
+    import torch
+    rows = []
+    for device in (False, True):
+        s0, s1 = eng.open(), eng.open()
+        eng.step([(s0, a[:-1], []), (s1, b[:-1], [])])
+        ids = torch.tensor([7, b[-1], 3, a[-1]], dtype=torch.int32)       # as a sampler would have left them
+        if device:
+            out = eng.step([(s0, [0], [0]), (s1, [0], [0])], device_tokens=(ids, [3, 1]))
+        else:
+            out = eng.step([(s0, [a[-1]], [0]), (s1, [b[-1]], [0])])
+        rows.append(out.clone())
+        eng.close(s0)
+        eng.close(s1)
+    assert torch.equal(rows[0], rows[1])
+    s0 = eng.open()
+    with pytest.raises(StepError, match="taken from the device"):
+        eng.step([(s0, [1, 2], [])], device_tokens=(torch.zeros(2, dtype=torch.int32), [0]))
+    with pytest.raises(StepError, match="taken from the device"):
+        eng.step([(s0, [1], [])], device_tokens=(torch.zeros(2, dtype=torch.int32), [2]))
+    assert eng.length(s0) == 0
+    eng.close(s0)
 
 
 def test_session_refuses_what_is_not_built(tiny_folders):

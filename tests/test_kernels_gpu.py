@@ -64,6 +64,16 @@ def test_layernorm_statistics_are_per_row(ops):
         assert torch.equal(ops.layernorm(x[r:r + 1].contiguous(), w, b, 1e-5, torch.float32)[0], whole[r])
 
 
+def test_take_tokens(ops):
+    tokens = torch.tensor([5, 6, 7, 8, 9], dtype=torch.int32).cuda()
+    src = torch.tensor([2, -1, 0, 9, -1], dtype=torch.int32).cuda()      # row 9 does not exist: left alone
+    ids = torch.tensor([40, 41, 42, 1000], dtype=torch.int32).cuda()
+    ops.take_tokens(tokens, src, ids, 100)
+    assert tokens.tolist() == [42, 6, 40, 8, 9]
+    ops.take_tokens(tokens, torch.tensor([3, -1, -1, -1, -1], dtype=torch.int32).cuda(), ids, 100)
+    assert tokens.tolist()[0] == 0                                       # an id outside the vocabulary never reaches the table
+
+
 def test_gather_rows(ops):
     x = gen((11, 72), 8)
     rows = torch.tensor([10, 0, 3, 3], dtype=torch.int32).cuda()
