@@ -346,16 +346,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
 }  // namespace
 
-// 0, or the code of the role whose wait ran out in a launch since the last call (11 loader, 12
-// products, 13 softmax); the word is cleared.  Meaningful after the stream has been synchronized.
-EMBER_API int ember_attention_tc_status() {
-  tc::Status& st = tc::status();
-  if (!st.host) return 0;
-  const int s = *reinterpret_cast<volatile int*>(st.host);
-  if (s) *reinterpret_cast<volatile int*>(st.host) = 0;
-  return s;
-}
-
 // Arguments as ember_attention_prefill, with the number of rows of qkv (`n_tokens`) and of pages in
 // the cache (`n_pages`) that the tensor maps need.  Returns 0 on success, 1 on an error, 2 if the
 // kernel does not take this head size or these pointers (the caller then takes the mma.sync kernel).

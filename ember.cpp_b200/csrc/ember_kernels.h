@@ -46,11 +46,11 @@ int ember_attention_decode_static(const void* qkv, const void* kc, const void* v
  * epilogue.  A, W bfloat16 row-major and 16-byte aligned, K a multiple of 8; bias float32 [N] or
  * null; residual float32 [M,N] or null (out_dtype is then 0, float32, and out may be the residual's
  * buffer); act 0 none, 1 tanh GELU, 2 erf GELU; out_dtype 0 float32, 1 bfloat16; tile_n 0 (the
- * kernel chooses) or a multiple of 16 up to 256.  ember_linear_tc_status() returns, after the
- * stream was synchronized, 0 or the code of a wait that ran out in a launch since the last call. */
+ * kernel chooses) or a multiple of 16 up to 256.  ember_tc_status() returns, after the stream was
+ * synchronized, 0 or the code of a wait that ran out in a launch of a tcgen05 kernel since the last call. */
 int ember_linear_tc(const void* A, const void* W, const float* bias, const float* residual, void* out, int M, int N, int K,
                     int act, int out_dtype, int tile_n, cudaStream_t stream);
-int ember_linear_tc_status(void);
+int ember_tc_status(void);
 
 #ifdef __cplusplus
 }

@@ -28,13 +28,11 @@
 // Every wait on an mbarrier has a time limit.  A role whose wait runs out records a code in the
 // status word (host-visible memory) and leaves; the block then waits, again with a limit, for its
 // copies in flight, meets its partner, frees its tensor memory and returns.  The results of such a
-// launch are not valid, and `ember_linear_tc_status` says so.
-#include <cuda.h>
-
+// launch are not valid, and `ember_tc_status` says so.
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace {
 
@@ -49,16 +47,9 @@ constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kMaxStages = 16;
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kTurnBytes = kEpiWarps * 32 * 33 * 4;  // a 32 x 32 block (rows padded to 33) for each epilogue warp
-constexpr unsigned long long kWaitNs = 2000000000ull;  // a wait gives up after two seconds
 
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+using namespace tc;  // mbarriers with time-limited waits, descriptors, fences, tensor-memory loads (tc_common.cuh)
 
-__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
 // the same barrier in the first block of the cluster (this block, when it is the first)
 __device__ __forceinline__ unsigned leader_addr(unsigned bar) {
   unsigned r;
@@ -68,39 +59,12 @@ __device__ __forceinline__ unsigned leader_addr(unsigned bar) {
 __device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_bar) : "memory");
 }
-__device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
-  unsigned ok;
-  asm volatile(
-      "{\n.reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Waits for the phase of the given parity to complete.  False when the time ran out.
-__device__ bool mbar_wait_one(unsigned bar, unsigned parity) {
-  if (mbar_try(bar, parity)) return true;
-  unsigned long long t0, t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
-  for (;;) {
-    for (int i = 0; i < 256; ++i)
-      if (mbar_try(bar, parity)) return true;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    if (t - t0 > kWaitNs) return false;
-  }
-}
-
-// The same for a whole warp: one lane polls, all lanes get the answer (and, through the warp
-// barrier, see what the completed phase made visible).
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) { return mbar_wait_one(bar, parity); }
 
 // One box of a tensor map into this block's shared memory.  With two blocks the completion is
 // counted on the first block's barrier (`bar` is a cluster address then): that block issues the
 // products for both.  No multicast: every block fetches what it uses.
 template <int CTAS>
-__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+__device__ __forceinline__ void load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
   if constexpr (CTAS == 2)
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(
@@ -114,17 +78,6 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
         : "memory");
 }
 
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled by 128
-// bytes: start address / 16; leading offset 1 (not used by this layout); 1,024 bytes between
-// groups of eight rows; descriptor version 1; layout type 2 (128-byte swizzle).
-__device__ __forceinline__ unsigned long long smem_desc(unsigned addr) {
-  return (unsigned long long)((addr & 0x3FFFF) >> 4) | (1ull << 16) | ((unsigned long long)(1024 >> 4) << 32) | (1ull << 46) |
-         (2ull << 61);
-}
-// Instruction descriptor: float32 accumulator, bfloat16 A and B, both K-major, M = m, N = bn.
-__device__ __forceinline__ unsigned instr_desc(int m, int bn) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(bn >> 3) << 17) | ((unsigned)(m >> 4) << 24);
-}
 template <int CTAS>
 __device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
                                      unsigned accumulate) {
@@ -154,25 +107,9 @@ __device__ __forceinline__ void umma_commit(unsigned bar) {
   else
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
-
-// 32 consecutive accumulator columns of this thread's row (issue only; tmem_wait before use)
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, "
-      "[%32];\n"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
-        "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
-        "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 
 // The tanh GELU as v / (1 + exp(-2u)), u = sqrt(2/pi) (v + 0.044715 v^3): the same function as
 // 0.5 v (1 + tanh u), one exponential and one division in place of a tanh.
@@ -252,10 +189,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
   }
-  tc_fence_before();
+  fence_before();
   __syncthreads();
   if constexpr (CTAS == 2) cluster_sync();  // the partner's barriers exist before anything arrives on them
-  tc_fence_after();
+  fence_after();
   const unsigned tmem = s_tmem;
   // Everything above touched this block's own resources only and may run while the kernel before
   // this one still does; its results are read from here on.
@@ -281,8 +218,8 @@ __global__ void __launch_bounds__(kThreads, 1)
           if constexpr (CTAS == 2) bar = leader_addr(bar);
 #pragma unroll
           for (int j = 0; j < KSUB; ++j) {  // a box past the end of K reads as zeros
-            tma_load_2d<CTAS>(dst + j * a_bytes, &map_a, (kb * KSUB + j) * BK, m0, bar);
-            tma_load_2d<CTAS>(dst + KSUB * a_bytes + j * b_bytes, &map_w, (kb * KSUB + j) * BK, n0, bar);
+            load_2d<CTAS>(dst + j * a_bytes, &map_a, (kb * KSUB + j) * BK, m0, bar);
+            load_2d<CTAS>(dst + KSUB * a_bytes + j * b_bytes, &map_w, (kb * KSUB + j) * BK, n0, bar);
           }
         }
         __syncwarp();
@@ -301,25 +238,25 @@ __global__ void __launch_bounds__(kThreads, 1)
   } else if (warp == 1) {
     // ------------------------------------------------------------------ products (first block only)
     if (rank == 0) {
-      const unsigned idesc = instr_desc(BM * CTAS, p.bn);
+      const unsigned idesc = instr_desc_bf16(BM * CTAS, p.bn, false);
       int it = 0, t = 0;
       bool ok = true;
       for (int tile = group; tile < n_tiles && ok; tile += groups, ++t) {
         const int as = t & 1;
         ok = mbar_wait(acc_empty0 + 8 * as, ((t >> 1) & 1) ^ 1);
         if (!ok) break;
-        tc_fence_after();
+        fence_after();
         const unsigned acc = tmem + as * kAccStride;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % p.stages;
           ok = mbar_wait(full0 + 8 * s, (it / p.stages) & 1);
           if (!ok) break;
-          tc_fence_after();
+          fence_after();
           if (lane == 0) {
             const unsigned a_addr = base + s * stage_bytes;
 #pragma unroll
             for (int j = 0; j < KSUB; ++j) {
-              const unsigned long long da = smem_desc(a_addr + j * a_bytes), db = smem_desc(a_addr + KSUB * a_bytes + j * b_bytes);
+              const unsigned long long da = smem_desc_sw128(a_addr + j * a_bytes), db = smem_desc_sw128(a_addr + KSUB * a_bytes + j * b_bytes);
 #pragma unroll
               for (int k = 0; k < BK / 16; ++k) umma<CTAS>(acc, da + 2 * k, db + 2 * k, idesc, (kb | j | k) != 0);  // 32 bytes a step
             }
@@ -363,7 +300,7 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (c0 < p.bn) fetch_residual(c0);
       ok = mbar_wait(acc_full0 + 8 * as, (t >> 1) & 1);
       if (!ok) break;
-      tc_fence_after();
+      fence_after();
       const unsigned taddr = tmem + ((unsigned)(quarter * 32) << 16) + as * kAccStride;
       for (; c0 < p.bn; c0 += 64) {
         unsigned acc[32];
@@ -433,7 +370,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (c0 + 64 < p.bn) fetch_residual(c0 + 64);
         __syncwarp();
       }
-      tc_fence_before();
+      fence_before();
       __syncwarp();
       if (lane == 0) {
         if constexpr (CTAS == 2)
@@ -445,11 +382,11 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (!ok && lane == 0) atomicCAS(p.status, TC_OK, TC_EPILOGUE);
   }
 
-  tc_fence_before();
+  fence_before();
   __syncthreads();
   if constexpr (CTAS == 2) cluster_sync();  // neither block ends, or frees tensor memory, while the other still uses it
   if (warp == 1) {
-    tc_fence_after();
+    fence_after();
     if constexpr (CTAS == 2)
       asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(kTmemCols) : "memory");
     else
@@ -458,14 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 // ---------------------------------------------------------------------------------------- host
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 std::mutex g_mutex;
-EncodeTiled g_encode = nullptr;
-int* g_status_host = nullptr;  // pinned and mapped: the kernel writes it, the host reads it without a copy
-int* g_status_dev = nullptr;
 int g_sms = 0;
 
 struct MapKey {
@@ -481,28 +411,20 @@ struct MapHash {
     return (h ^ (size_t)k.box_rows) * 1099511628211ull;
   }
 };
-std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;  // weights come back with every call: their maps are kept
 
 int tc_setup() {
-  if (g_encode) return 0;
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult q;
-  cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
-  if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
-    return ember_fail("linear_tc: the driver has no cuTensorMapEncodeTiled (%s)", cudaGetErrorString(e));
-  e = cudaHostAlloc(reinterpret_cast<void**>(&g_status_host), sizeof(int), cudaHostAllocMapped);
-  if (e != cudaSuccess) return ember_fail("linear_tc: status word: %s", cudaGetErrorString(e));
-  *g_status_host = 0;
-  e = cudaHostGetDevicePointer(reinterpret_cast<void**>(&g_status_dev), g_status_host, 0);
-  if (e != cudaSuccess) return ember_fail("linear_tc: status word: %s", cudaGetErrorString(e));
-  int dev = 0;
+  if (g_sms) return 0;
+  if (!tc::encoder()) return ember_fail("linear_tc: the driver has no cuTensorMapEncodeTiled");
+  if (!tc::status().device) return ember_fail("linear_tc: no host-visible status word");
+  int dev = 0, sms = 0;
   cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev);
-  e = cudaFuncSetAttribute(linear_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024);
   if (e == cudaSuccess)
     e = cudaFuncSetAttribute(linear_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024);
   if (e != cudaSuccess) return ember_fail("linear_tc: shared memory: %s", cudaGetErrorString(e));
-  g_encode = reinterpret_cast<EncodeTiled>(fn);
+  g_sms = sms;
   return 0;
 }
 
@@ -515,15 +437,9 @@ int tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* o
     *out = it->second;
     return 0;
   }
-  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  const cuuint32_t elem[2] = {1, 1};
   CUtensorMap m;
-  const CUresult r = g_encode(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return ember_fail("linear_tc: cuTensorMapEncodeTiled failed with %d for [%d, %d]", (int)r, rows, cols);
+  if (!tc::encode_bf16_sw128(&m, ptr, (size_t)rows, (size_t)cols, (size_t)cols * 2, box_rows))
+    return ember_fail("linear_tc: the driver refused a tensor map for [%d, %d]", rows, cols);
   if (g_maps.size() > 4096) g_maps.clear();
   g_maps.emplace(key, m);
   *out = m;
@@ -546,13 +462,15 @@ int pick_bn(int M, int N, int groups, int ctas) {
 
 }  // namespace
 
-// 0 when every launch so far ran to its end; else the code of the role whose wait ran out
-// (1 producer, 2 products, 3 epilogue, 4 copies that never landed), and the word is cleared.
-// Meaningful after the stream has been synchronized.
-EMBER_API int ember_linear_tc_status() {
-  if (!g_status_host) return 0;
-  const int s = *reinterpret_cast<volatile int*>(g_status_host);
-  if (s) *reinterpret_cast<volatile int*>(g_status_host) = 0;
+// 0 when every launch of the tcgen05 kernels so far ran to its end; else the code of the role
+// whose wait ran out (linear_tc: 1 producer, 2 products, 3 epilogue, 4 copies that never landed;
+// attention_prefill_tc: 11 loader, 12 products, 13 softmax), and the word is cleared.  Meaningful
+// after the stream has been synchronized.
+EMBER_API int ember_tc_status() {
+  tc::Status& st = tc::status();
+  if (!st.host) return 0;
+  const int s = *reinterpret_cast<volatile int*>(st.host);
+  if (s) *reinterpret_cast<volatile int*>(st.host) = 0;
   return s;
 }
 
@@ -584,7 +502,7 @@ EMBER_API int ember_linear_tc(const void* A, const void* W, const float* bias, c
   TcArgs p;
   p.bias = bias, p.residual = residual, p.out = out;
   p.M = M, p.N = N, p.K = K, p.bn = bn, p.act = act, p.out_f32 = out_dtype == EMBER_F32;
-  p.status = g_status_dev;
+  p.status = tc::status().device;
   const int stage_bytes = KSUB * (BM + bn / ctas) * BK * 2;
   const int smem = kSmemLimit - 1024;
   p.stages = (smem - 1024 - kTurnBytes) / stage_bytes;

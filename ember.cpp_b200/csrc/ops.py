@@ -99,9 +99,8 @@ def load_library() -> ctypes.CDLL:
         getattr(lib, name).restype = _c_int
     lib.ember_decode_program_run.argtypes = [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void]
     lib.ember_decode_program_run.restype = _c_int
-    for name in ("ember_linear_tc_status", "ember_attention_tc_status"):
-        getattr(lib, name).argtypes = []
-        getattr(lib, name).restype = _c_int
+    lib.ember_tc_status.argtypes = []
+    lib.ember_tc_status.restype = _c_int
     lib._path = path
     return lib
 
@@ -308,14 +307,12 @@ class CudaOps:
     def check(self) -> None:
         """Raises if a kernel with bounded waits gave up since the last call.  The caller has
         synchronized with the device (it has just read a step's results)."""
-        code = self.lib.ember_linear_tc_status()
+        code = self.lib.ember_tc_status()
         if code:
-            role = {1: "the TMA producer", 2: "the product issuer", 3: "the epilogue", 4: "copies in flight"}.get(code, code)
-            raise KernelError(f"linear_tc: a wait ran out ({role}); the results of that launch are not valid")
-        code = self.lib.ember_attention_tc_status()
-        if code:
-            role = {11: "the TMA loader", 12: "the product issuer", 13: "the softmax warps"}.get(code, code)
-            raise KernelError(f"attention_prefill_tc: a wait ran out ({role}); the results of that launch are not valid")
+            kernel = "linear_tc" if code < 10 else "attention_prefill_tc"
+            role = {1: "the TMA producer", 2: "the product issuer", 3: "the epilogue", 4: "copies in flight",
+                    11: "the TMA loader", 12: "the product issuer", 13: "the softmax warps"}.get(code, code)
+            raise KernelError(f"{kernel}: a wait ran out ({role}); the results of that launch are not valid")
 
     # ------------------------------------------------------------------ cache and attention
     def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):
