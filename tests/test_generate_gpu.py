@@ -132,6 +132,43 @@ def test_prompts_through_the_tcgen05_products(tiny_folders, plains, name):
     assert rel_error(alone[0], plain.logits(seqs[0])) < TOL["bfloat16"]
 
 
+@pytest.mark.parametrize("gemm", ["lt", "tc"])
+def test_wide_model_bfloat16_against_float32(gemm):
+    """GPT-2 XL's layer sizes (width 1600, 25 heads of 64, inner 6400, vocabulary 50,257; two
+    layers): the bfloat16 path (tcgen05 prefill attention, cuBLASLt or the tcgen05 products, the
+    weight-streaming decode products, split decode attention in a replayed graph) against the
+    32-bit path on the same weights: two prompts of unequal length over several pages, then
+    decode steps, every wanted row within the bfloat16 tolerance and the same best token where the
+    32-bit logits decide clearly."""
+    from ember_cpp_b200.config import get_architecture
+    from ember_cpp_b200.parts import DecoderModel
+    from ember_cpp_b200.weights import random_tensors
+    cfg = E.GPT2Config.from_dict(dict(vocab_size=50257, n_positions=1024, n_embd=1600, n_layer=2, n_head=25,
+                                      n_inner=6400, activation_function="gelu_new", layer_norm_epsilon=1e-5))
+    spec = get_architecture(cfg.architecture).build_spec(cfg)
+    tensors = random_tensors(DecoderModel(spec).weight_specs(), 5, torch.bfloat16, "cuda")
+    engines = {d: Engine.from_spec(spec, tensors, dtype=d, max_tokens=2048) for d in DTYPES}
+    engines["bfloat16"].ops.gemm = gemm
+    seqs = [random_ids(900 + i, 50257, n) for i, n in enumerate((710, 135))]
+    rows = {}
+    for d, eng in engines.items():
+        slots = [eng.open() for _ in seqs]
+        out = [eng.step([(s, q[:-6], [len(q) - 9, len(q) - 7]) for s, q in zip(slots, seqs)]).float().cpu().numpy()]
+        for k in range(6, 0, -1):
+            out.append(eng.step([(s, [q[-k]], [0]) for s, q in zip(slots, seqs)]).float().cpu().numpy())
+        rows[d] = np.concatenate(out)
+        eng.ops.check()
+        for s in slots:
+            eng.close(s)
+    ref, got = rows["float32"], rows["bfloat16"]
+    assert ref.shape == got.shape == (4 + 12, 50257)
+    assert rel_error(got, ref) < TOL["bfloat16"]
+    for r, g in zip(ref, got):
+        best = np.sort(r)[-2:]
+        if best[1] - best[0] > 4 * TOL["bfloat16"] * (r.max() - r.min()):
+            assert int(g.argmax()) == int(r.argmax())
+
+
 def test_graph_replay_equals_launch_by_launch(tiny_folders, plains):
     plain = plains["tiny_a"]
     seqs = [random_ids(400 + i, plain.vocab, 50) for i in range(3)]
