@@ -62,9 +62,13 @@ const char* lt_status(cublasStatus_t s) {
     if (s_ != CUBLAS_STATUS_SUCCESS) return ember_fail("linear_bf16: %s: %s", #call, lt_status(s_)); \
   } while (0)
 
-// Builds the descriptors for one shape and asks the library for an algorithm.  Returns 0 and
-// fills `plan`, or 2 when the library offers none for this combination.
-int make_plan(const PlanKey& key, bool bias_bf16, size_t workspace_bytes, Plan* plan) {
+constexpr int kCandidates = 8;
+
+// Builds the descriptors for one shape and asks the library for algorithms (its heuristic's
+// order).  Returns 0 and fills `plan` with the first, or 2 when the library offers none for this
+// combination; the others go to `more`.
+int make_plan(const PlanKey& key, bool bias_bf16, size_t workspace_bytes, Plan* plan, cublasLtMatmulAlgo_t* more,
+              int* n_more) {
   const cudaDataType_t out_type = key.out_dtype == EMBER_F32 ? CUDA_R_32F : CUDA_R_16BF;
   LT_TRY(cublasLtMatmulDescCreate(&plan->op, CUBLAS_COMPUTE_32F, CUDA_R_32F));
   const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
@@ -86,10 +90,10 @@ int make_plan(const PlanKey& key, bool bias_bf16, size_t workspace_bytes, Plan* 
   LT_TRY(cublasLtMatmulPreferenceCreate(&pref));
   LT_TRY(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &workspace_bytes,
                                               sizeof(workspace_bytes)));
-  cublasLtMatmulHeuristicResult_t result;
+  cublasLtMatmulHeuristicResult_t result[kCandidates];
   int found = 0;
-  cublasStatus_t s = cublasLtMatmulAlgoGetHeuristic(g_handle, plan->op, plan->a, plan->b, plan->c, plan->c, pref, 1,
-                                                    &result, &found);
+  cublasStatus_t s = cublasLtMatmulAlgoGetHeuristic(g_handle, plan->op, plan->a, plan->b, plan->c, plan->c, pref,
+                                                    kCandidates, result, &found);
   cublasLtMatmulPreferenceDestroy(pref);
   if (s != CUBLAS_STATUS_SUCCESS || found == 0) {
     cublasLtMatmulDescDestroy(plan->op);
@@ -99,9 +103,46 @@ int make_plan(const PlanKey& key, bool bias_bf16, size_t workspace_bytes, Plan* 
     *plan = Plan();
     return 2;
   }
-  plan->algo = result.algo;
+  plan->algo = result[0].algo;
   plan->bias_is_bf16 = bias_bf16;
+  *n_more = 0;
+  for (int i = 1; i < found; ++i)
+    if (result[i].state == CUBLAS_STATUS_SUCCESS) more[(*n_more)++] = result[i].algo;
   return 0;
+}
+
+// Times the candidates on the call's own operands, writing to `scratch` (as large as the output),
+// and keeps the fastest in `plan`.  The heuristic's first choice is not always the best for a
+// given shape; this runs once per shape, synchronizes the stream, and is skipped without scratch.
+void tune_plan(Plan* plan, const cublasLtMatmulAlgo_t* more, int n_more, const void* A, const void* W, const void* C,
+               float beta, void* scratch, void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  cudaEvent_t t0, t1;
+  if (cudaEventCreate(&t0) != cudaSuccess) return;
+  if (cudaEventCreate(&t1) != cudaSuccess) {
+    cudaEventDestroy(t0);
+    return;
+  }
+  const float one = 1.0f;
+  float best_ms = 0.f;
+  cublasLtMatmulAlgo_t best = plan->algo;
+  for (int i = -1; i < n_more; ++i) {
+    const cublasLtMatmulAlgo_t& algo = i < 0 ? plan->algo : more[i];
+    bool ok = true;
+    float ms = 0.f;
+    for (int rep = 0; rep < 4 && ok; ++rep) {  // the first run is not timed
+      if (rep == 1) cudaEventRecord(t0, stream);
+      ok = cublasLtMatmul(g_handle, plan->op, &one, W, plan->a, A, plan->b, &beta, C ? C : scratch, plan->c, scratch,
+                          plan->c, &algo, workspace, workspace_bytes, stream) == CUBLAS_STATUS_SUCCESS;
+    }
+    if (!ok || cudaEventRecord(t1, stream) != cudaSuccess || cudaEventSynchronize(t1) != cudaSuccess ||
+        cudaEventElapsedTime(&ms, t0, t1) != cudaSuccess)
+      continue;
+    if (i < 0 || ms < best_ms) best_ms = ms, best = algo;
+    if (i < 0) best_ms = ms;
+  }
+  plan->algo = best;
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
 }
 
 }  // namespace
@@ -110,9 +151,11 @@ int make_plan(const PlanKey& key, bool bias_bf16, size_t workspace_bytes, Plan* 
 // where the library takes it with this output type, else the bfloat16 one.
 // residual: float32 [M,N] added to the product (out is float32 then, and may be the same buffer).
 // act: none or the tanh GELU (the erf form is not a library epilogue; the caller applies it).
+// tune_scratch: null, or a buffer as large as the output: the first call for a shape then times
+// the library's candidate algorithms there (synchronizing the stream) and keeps the fastest.
 EMBER_API int ember_linear_bf16(const void* A, const void* W, const float* bias_f32, const void* bias_bf16,
                                 const float* residual, void* out, int M, int N, int K, int act, int out_dtype,
-                                void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+                                void* workspace, size_t workspace_bytes, void* tune_scratch, cudaStream_t stream) {
   EMBER_CHECK(M > 0 && N > 0 && K > 0, "linear_bf16: M = %d, N = %d, K = %d", M, N, K);
   EMBER_CHECK(act == EMBER_ACT_NONE || act == EMBER_ACT_GELU_TANH, "linear_bf16: activation %d is no library epilogue",
               act);
@@ -128,10 +171,20 @@ EMBER_API int ember_linear_bf16(const void* A, const void* W, const float* bias_
     auto it = g_plans.find(key);
     if (it == g_plans.end()) {
       Plan fresh;
-      int rc = make_plan(key, /*bias_bf16=*/false, workspace_bytes, &fresh);
-      if (rc == 2 && key.bias) rc = make_plan(key, /*bias_bf16=*/true, workspace_bytes, &fresh);
+      cublasLtMatmulAlgo_t more[kCandidates];
+      int n_more = 0;
+      int rc = make_plan(key, /*bias_bf16=*/false, workspace_bytes, &fresh, more, &n_more);
+      if (rc == 2 && key.bias) rc = make_plan(key, /*bias_bf16=*/true, workspace_bytes, &fresh, more, &n_more);
       if (rc == 2) return ember_fail("linear_bf16: the library has no algorithm for M=%d N=%d K=%d", M, N, K);
       if (rc != 0) return rc;
+      if (tune_scratch && n_more > 0) {
+        if (key.bias) {
+          const void* bias = fresh.bias_is_bf16 ? bias_bf16 : (const void*)bias_f32;
+          LT_TRY(cublasLtMatmulDescSetAttribute(fresh.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias)));
+        }
+        tune_plan(&fresh, more, n_more, A, W, residual, residual ? 1.0f : 0.0f, tune_scratch, workspace, workspace_bytes,
+                  stream);
+      }
       it = g_plans.emplace(key, fresh).first;
     }
     plan = it->second;

@@ -32,7 +32,7 @@ _SIGNATURES = {
     "ember_act_inplace": [_c_void, _c_size, _c_int, _c_int, _c_void],
     "ember_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_bf16": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
-                          _c_void, _c_size, _c_void],
+                          _c_void, _c_size, _c_void, _c_void],
     "ember_linear_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void],
@@ -134,6 +134,8 @@ class CudaOps:
         # Measured on GPT-2 XL's four products the library is ahead: at 2,048 rows 133 against 205
         # microseconds a layer, at 16,384 rows the tcgen05 kernel reaches 87 % of it on the QKV product.
         self.gemm = os.environ.get("EMBER_GEMM", "lt")
+        self.lt_tune = os.environ.get("EMBER_LT_TUNE", "1") != "0"
+        self._lt_tuned = set()
         # Prefill attention with head size 64 runs on the tcgen05 kernel; EMBER_ATTENTION=mma keeps it
         # on the mma.sync kernel (which takes every other head size anyway).
         self.attention_tc = os.environ.get("EMBER_ATTENTION", "tc") != "mma"
@@ -290,9 +292,15 @@ class CudaOps:
             return self.linear_tc(a, w, bias, act, residual, out)
         fused = _ACT[act] if act != "gelu_erf" else 0
         ws = self._lt_workspace()
+        # the first product of a shape times the library's candidates into a scratch output (outside any capture)
+        shape = (M, N, K, fused, bias is not None, residual is not None, target)
+        scratch = None
+        if self.lt_tune and shape not in self._lt_tuned and not torch.cuda.is_current_stream_capturing():
+            self._lt_tuned.add(shape)
+            scratch = torch.empty_like(out)
         self._call("ember_linear_bf16", a.data_ptr(), w.data_ptr(), self._ptr(bias),
                    None if bias is None else self._bias_bf16(bias).data_ptr(), self._ptr(residual), out.data_ptr(),
-                   M, N, K, fused, _code(target), ws.data_ptr(), ws.numel())
+                   M, N, K, fused, _code(target), ws.data_ptr(), ws.numel(), self._ptr(scratch))
         if act == "gelu_erf":
             self._call("ember_act_inplace", out.data_ptr(), out.numel(), _ACT[act], _code(target))
         return out
