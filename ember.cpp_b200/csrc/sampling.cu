@@ -45,7 +45,10 @@ struct Row {
 };
 
 __device__ __forceinline__ u64 key_of(float p, int i) { return ((u64)__float_as_uint(p) << 32) | (unsigned)i; }
-__device__ __forceinline__ u64 mass_of(float p) { return (u64)((double)p * kMassScale); }
+// floor(p * 2^40) for 0 <= p <= 1.  The product by a power of two is exact in float32 and the
+// conversion truncates, so this is the integer the float64 form would give, without float64
+// arithmetic (which this GPU has very little of).
+__device__ __forceinline__ u64 mass_of(float p) { return __float2ull_rz(p * (float)kMassScale); }
 
 // Sum over the block; every thread gets the total.  scratch: kThreads / 32 entries.
 __device__ u64 block_sum(u64 v, u64* scratch) {
