@@ -13,7 +13,8 @@ from conftest import TOL, random_ids, rel_error, run_batch
 from ember_cpp_b200.cache import SequenceCache
 from ember_cpp_b200.engine import Engine, Runtime, StepContext, StepPlan, build_step
 from ember_cpp_b200.engine.engine import AppHandle
-from ember_cpp_b200.parts import (Application, DecoderModel, LayerSpec, Mixer, ModelSpec, PartSpec, StateNeed, build_block,
+from ember_cpp_b200.parts import (Application, DecoderModel, FeedForward, LayerSpec, Mixer, ModelSpec, PartSpec, Position,
+                                  StateNeed, build_block,
                                   build_part, register_part)
 from ember_cpp_b200.weights import random_tensors
 
@@ -177,7 +178,63 @@ class ToyDecay(Mixer):
         return residual + out
 
 
-def toy_spec(width, vocab, n_pos, mixers, schedule, eps=1e-5):
+class ToyRouted(FeedForward):
+    """A feed-forward with routing: router logits in float32, the best expert of each token,
+    weighted by its softmax probability; each expert a small GELU MLP.  Every expert runs on every
+    token and the unchosen ones are zeroed (a toy: it shows the interface, not a fast kernel), so
+    nothing goes to the host and the step still replays as a graph."""
+
+    def __init__(self, prefix, width, inner, experts):
+        super().__init__(prefix)
+        self.width, self.inner, self.experts = width, inner, experts
+
+    def weight_specs(self):
+        from ember_cpp_b200.parts import WeightSpec
+        specs = [WeightSpec(self.prefix + "router.weight", (self.experts, self.width), std=0.5)]
+        for e in range(self.experts):
+            specs += [WeightSpec(f"{self.prefix}e{e}.up.weight", (self.inner, self.width), std=0.08),
+                      WeightSpec(f"{self.prefix}e{e}.down.weight", (self.width, self.inner), std=0.08)]
+        return specs
+
+    def load(self, get, runtime):
+        self.router = get(self.prefix + "router.weight").to(runtime.device, torch.float32)
+        self.up = [runtime.matrix(get(f"{self.prefix}e{e}.up.weight")) for e in range(self.experts)]
+        self.down = [runtime.matrix(get(f"{self.prefix}e{e}.down.weight")) for e in range(self.experts)]
+
+    def forward(self, ctx, h, residual):
+        logits = h.float() @ self.router.t()                       # router logits in 32-bit
+        prob = torch.softmax(logits, dim=-1)
+        best = logits.argmax(dim=-1)
+        out = residual
+        for e in range(self.experts):
+            u = ctx.ops.linear(h, self.up[e], None, act="gelu_tanh", out_dtype=ctx.dtype)
+            y = ctx.ops.linear(u, self.down[e], None, out_dtype=torch.float32)
+            gate = torch.where(best == e, prob[:, e], torch.zeros_like(prob[:, e]))
+            out = out + gate[:, None] * y
+        return out
+
+
+class ToyRotary(Position):
+    """Another position encoding: nothing is added to the embedding; the attention mixer's q and k
+    are rotated in place, pair (2i, 2i+1) of every head by position * base^(-2i/head size), the
+    angles in float32."""
+
+    def __init__(self, prefix, base):
+        super().__init__(prefix)
+        self.base = base
+
+    def apply_qk(self, ctx, qkv, n_heads, kv_heads, head_dim):
+        pos = ctx.plan.positions[:qkv.shape[0]].float()
+        inv = self.base ** (-torch.arange(0, head_dim, 2, device=qkv.device, dtype=torch.float32) / head_dim)
+        ang = pos[:, None] * inv[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        rot = qkv[:, :(n_heads + kv_heads) * head_dim].view(qkv.shape[0], n_heads + kv_heads, head_dim // 2, 2).float()
+        a, b = rot[..., 0], rot[..., 1]
+        turned = torch.stack((a * cos - b * sin, a * sin + b * cos), dim=-1).to(qkv.dtype)
+        qkv[:, :(n_heads + kv_heads) * head_dim] = turned.view(qkv.shape[0], -1)
+
+
+def toy_spec(width, vocab, n_pos, mixers, schedule, eps=1e-5, rotary=None, experts=0):
     """mixers: per layer ("attn", heads, kv_heads, hd, window) or ("decay", decay)."""
     layers = []
     for i, m in enumerate(mixers):
@@ -190,21 +247,39 @@ def toy_spec(width, vocab, n_pos, mixers, schedule, eps=1e-5):
                                                                "init_std": 0.08, "out_init_std": 0.08})
         else:
             mixer = PartSpec("toy_decay", p + "decay.", {"width": width, "decay": m[1]})
+        if experts and i % 2 == 1:                 # every other layer routes: different feed-forwards in one model
+            ffn = PartSpec("toy_routed", p + "moe.", {"width": width, "inner": width + 8, "experts": experts})
+        else:
+            ffn = PartSpec("dense", p + "ffn.", {"width": width, "inner": 2 * width + 8, "activation": "gelu_tanh",
+                                                 "up": "up", "down": "down", "stored": "out_in", "init_std": 0.08,
+                                                 "down_init_std": 0.08})
         layers.append(LayerSpec("pre_norm", PartSpec("layernorm", p + "n1.", {"width": width, "eps": eps}), mixer,
-                                PartSpec("layernorm", p + "n2.", {"width": width, "eps": eps}),
-                                PartSpec("dense", p + "ffn.", {"width": width, "inner": 2 * width + 8,
-                                                               "activation": "gelu_tanh", "up": "up", "down": "down",
-                                                               "stored": "out_in", "init_std": 0.08, "down_init_std": 0.08})))
+                                PartSpec("layernorm", p + "n2.", {"width": width, "eps": eps}), ffn))
+    position = (PartSpec("toy_rotary", "", {"base": rotary}) if rotary
+                else PartSpec("learned_absolute", "pos.", {"width": width, "n_positions": n_pos}))
     return ModelSpec(width=width, vocab_size=vocab, token_table="embed.weight",
-                     position=PartSpec("learned_absolute", "pos.", {"width": width, "n_positions": n_pos}),
+                     position=position,
                      layers=tuple(layers), schedule=tuple(Application(*a) for a in schedule),
                      final_norm=PartSpec("layernorm", "norm.", {"width": width, "eps": eps}), head="head.weight",
                      table_init_std=0.3)
 
 
+def plain_rotate(x, heads, hd, base):
+    """Rows of [T, heads * hd]: pair (2i, 2i+1) of every head turned by position * base^(-2i/hd)."""
+    T = x.shape[0]
+    ang = np.arange(T)[:, None] * base ** (-np.arange(0, hd, 2) / hd)[None, :]
+    v = x.reshape(T, heads, hd // 2, 2)
+    a, b = v[..., 0], v[..., 1]
+    c, s = np.cos(ang)[:, None, :], np.sin(ang)[:, None, :]
+    return np.stack((a * c - b * s, a * s + b * c), axis=-1).reshape(T, heads * hd)
+
+
 def toy_plain(spec, mixers, w, ids):
     """The toy model on a whole sequence, from the plain implementation's functions."""
-    x = plain_gpt2.position_embedding(plain_gpt2.token_embedding(w["embed.weight"], ids), w["pos.weight"])
+    rotary = spec.position.params.get("base") if spec.position.kind == "toy_rotary" else None
+    x = plain_gpt2.token_embedding(w["embed.weight"], ids)
+    if rotary is None:
+        x = plain_gpt2.position_embedding(x, w["pos.weight"])
     kv = {}
     for a, app in enumerate(spec.schedule):
         i, m, p = app.layer, mixers[app.layer], f"layers.{app.layer}."
@@ -214,6 +289,8 @@ def toy_plain(spec, mixers, w, ids):
             _, heads, kvh, hd, window = m
             qkv = plain_gpt2.linear(h, w[p + "attn.qkv.weight"], w[p + "attn.qkv.bias"])
             q, k, v = plain_gpt2.split_qkv(qkv, heads, kvh, hd)
+            if rotary is not None:
+                q, k = plain_rotate(q, heads, hd, rotary), plain_rotate(k, kvh, hd, rotary)
             kv[a] = (k, v)
             if app.cache_of is not None:
                 k, v = kv[app.cache_of]
@@ -228,6 +305,16 @@ def toy_plain(spec, mixers, w, ids):
                 out[t] = s
             x = x + out
         h = plain_gpt2.layer_norm(x, w[p + "n2.weight"], w[p + "n2.bias"], eps)
+        if spec.layers[i].ffn.kind == "toy_routed":
+            logits = h @ w[p + "moe.router.weight"].T
+            prob = np.exp(logits - logits.max(-1, keepdims=True))
+            prob /= prob.sum(-1, keepdims=True)
+            best = logits.argmax(-1)
+            for t in range(len(ids)):
+                e = int(best[t])
+                u = plain_gpt2.gelu(h[t:t + 1] @ w[f"{p}moe.e{e}.up.weight"].T, "tanh")
+                x[t] = x[t] + prob[t, e] * (u @ w[f"{p}moe.e{e}.down.weight"].T)[0]
+            continue
         x = x + plain_gpt2.mlp(h, w[p + "ffn.up.weight"], w[p + "ffn.up.bias"], w[p + "ffn.down.weight"],
                                w[p + "ffn.down.bias"], "tanh")
     h = plain_gpt2.layer_norm(x, w["norm.weight"], w["norm.bias"], spec.final_norm.params["eps"])
@@ -245,15 +332,22 @@ TOYS = {
     # a mixer with state of its own between attention layers, and run twice
     "state_of_its_own": (dict(width=48, vocab=150, n_pos=160), [("attn", 3, 3, 16, 0), ("decay", 0.8), ("attn", 3, 1, 16, 10)],
                          [(0,), (1,), (2,), (1,)]),
+    # another position encoding (q and k rotated, no table: the context is bounded by the cache alone) and
+    # a feed-forward with routing in every other layer
+    "rotary_routed": (dict(width=64, vocab=180, n_pos=160, rotary=100.0, experts=3),
+                      [("attn", 4, 2, 16, 0), ("attn", 2, 2, 32, 40), ("attn", 4, 4, 16, 0)], [(0,), (1,), (2,)]),
 }
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("toy", list(TOYS))
 def test_toy_models_step_like_whole_sequences(ops, dtype, toy):
-    register_part("mixer", "toy_decay", ToyDecay)            # a part of the test's own
+    register_part("mixer", "toy_decay", ToyDecay)            # parts of the test's own
+    register_part("ffn", "toy_routed", ToyRouted)
+    register_part("position", "toy_rotary", ToyRotary)
     sizes, mixers, schedule = TOYS[toy]
-    spec = toy_spec(sizes["width"], sizes["vocab"], sizes["n_pos"], mixers, schedule)
+    spec = toy_spec(sizes["width"], sizes["vocab"], sizes["n_pos"], mixers, schedule, rotary=sizes.get("rotary"),
+                    experts=sizes.get("experts", 0))
     tensors = random_tensors(DecoderModel(spec).weight_specs(), 3, torch.bfloat16)
     w = {k: f64(v) for k, v in tensors.items()}
     eng = Engine.from_spec(spec, tensors, dtype=dtype, max_tokens=1024, ops=ops)
@@ -265,8 +359,17 @@ def test_toy_models_step_like_whole_sequences(ops, dtype, toy):
     if toy == "state_of_its_own":
         assert eng.apps[1].state is not None and eng.apps[3].state is not None
         assert eng.apps[1].state.data_ptr() != eng.apps[3].state.data_ptr()
+    if toy == "rotary_routed":
+        assert eng.model.max_positions() is None and len(eng.cache.groups) == 3
+        assert [type(b.ffn).__name__ for b in eng.model.blocks] == ["DenseFeedForward", "ToyRouted", "DenseFeedForward"]
     tol = 1e-5 if dtype == "float32" else 2e-2
     seqs = [random_ids(i, sizes["vocab"], n) for i, n in enumerate((150, 33, 70))]
+    if toy == "rotary_routed":
+        # The best expert of a token is a discontinuous function of the activations: where two router logits
+        # nearly tie, bfloat16 may choose the other expert and no tolerance covers that.  These sequences
+        # were picked (from the plain implementation) so that every token's best two router logits are at
+        # least 6 % of the logits' spread apart.
+        seqs = [random_ids(seed, sizes["vocab"], n) for seed, n in ((271, 150), (26, 33), (110, 70))]
     for batch in ((40, 1, 70), (100, 20, 5)):                 # the second batch reuses slots and state rows
         rows, _ = run_batch(eng, seqs, batch)
         for ids, got in zip(seqs, rows):
