@@ -15,8 +15,8 @@
 //
 // Work is cut so that a few-megabyte matrix still occupies the whole chip: a tile is 16 weight
 // rows; a thread-block cluster of 1, 2 or 4 blocks shares a tile and splits K between its blocks.
-// A block asks for its whole share of the matrix at once (cp.async into shared memory, about 50 KB,
-// three or four blocks to an SM), so the matrix is in flight from the first instruction and the
+// A block asks for its whole share of the matrix at once (bulk copies into shared memory, a row of
+// the tile each, about 50 KB, three blocks to an SM), so the matrix is in flight from the first instruction and the
 // kernel runs at the speed of HBM, not of its own round trips.  Inside a block 8 warps take
 // interleaved slices; warps are summed in shared memory in warp order, the cluster's blocks in
 // block order through distributed shared memory into block 0, which applies the epilogue: no
@@ -53,12 +53,6 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
 
 constexpr int kWarps = 8;
 constexpr int kRowVecs = 16;  // float4 per lane of a row held in registers (K <= 2048)
-
-__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
-  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
-  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
-}
 
 __device__ __forceinline__ unsigned pack2(float a, float b) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
@@ -180,16 +174,35 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   float* stats = gather + k_split * kTile;
 
   // The block's whole share of the matrix is asked for before anything else: it does not depend
-  // on the kernel before this one, whose completion is awaited only after that.
-  {
-    const int chunks = (step_hi - step_lo) * 4;  // 16-byte chunks per row
-    for (int i = threadIdx.x; i < 16 * chunks; i += kWarps * 32) {
-      const int r = i / chunks, ch = i % chunks;
-      const int k = k_lo + ch * 8;
-      const int row = min(row0 + r, N - 1);  // rows past N repeat the last row and are dropped at the end
-      cp_async_16(wt + r * ldw + ch * 8, W + (size_t)row * K + min(k, K - 8), k < K);
+  // on the kernel before this one, whose completion is awaited only after that.  Sixteen bulk
+  // copies, a row of the tile each, issued by sixteen lanes and counted on one mbarrier: no
+  // per-16-byte address arithmetic, and the whole share is in flight a few cycles after the block
+  // starts.  (Rows past N repeat the last row and are dropped at the end; values of K past the
+  // matrix's width are zeroed by hand: a bulk copy cannot.)
+  __shared__ unsigned long long s_bar;
+  const unsigned bar = (unsigned)__cvta_generic_to_shared(&s_bar);
+  const int k_hi = min(K, step_hi * 32);                      // one past the last value of K this block holds
+  const unsigned row_bytes = (unsigned)max(0, k_hi - k_lo) * 2;  // a multiple of 16: K is a multiple of 8
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"(bar));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
+  if (warp == 0) {
+    if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(16u * row_bytes) : "memory");
+    __syncwarp();
+    if (lane < 16 && row_bytes) {
+      const int row = min(row0 + lane, N - 1);
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(wt + lane * ldw);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                   "l"(W + (size_t)row * K + k_lo), "r"(row_bytes), "r"(bar)
+                   : "memory");
     }
-    asm volatile("cp.async.commit_group;\n" ::);
+  }
+  {
+    const int tail = (step_hi - step_lo) * 32 - (k_hi - k_lo);  // values past K in the block's last slice
+    for (int i = threadIdx.x; i < 16 * tail; i += kWarps * 32)
+      wt[(i / tail) * ldw + (k_hi - k_lo) + i % tail] = __float2bfloat16_rn(0.f);
   }
   if (LN) {
     // the norm's gain and bias are constants too: bring their lines into L1 now
@@ -262,7 +275,17 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
       }
     }
   }
-  asm volatile("cp.async.wait_all;\n" ::: "memory");
+  {  // the weights have landed (a wait with a limit: a copy that never completes must not hang the GPU)
+    unsigned done = 0;
+    for (unsigned spin = 0; !done && spin < (1u << 24); ++spin)
+      asm volatile(
+          "{\n.reg .pred p;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n"
+          "selp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(done)
+          : "r"(bar)
+          : "memory");
+  }
   __syncthreads();
 
   float acc[MT][4];
