@@ -275,7 +275,8 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
       }
     }
   }
-  {  // the weights have landed (a wait with a limit: a copy that never completes must not hang the GPU)
+  // the weights have landed (a wait with a limit: a copy that never completes must not hang the GPU)
+  auto wait_for_weights = [&]() {
     unsigned done = 0;
     for (unsigned spin = 0; !done && spin < (1u << 24); ++spin)
       asm volatile(
@@ -285,8 +286,8 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
           : "=r"(done)
           : "r"(bar)
           : "memory");
-  }
-  __syncthreads();
+    __syncthreads();
+  };
 
   float acc[MT][4];
 #pragma unroll
@@ -294,33 +295,62 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
 #pragma unroll
     for (int j = 0; j < 4; ++j) acc[t][j] = 0.f;
 
-#pragma unroll 2
-  for (int s = step_lo + warp; s < step_hi; s += kWarps) {
-    const int k = s * 32 + c * 8;
-    const bool ok = k < K;
-    const uint4 a_lo = *reinterpret_cast<const uint4*>(wt + g * ldw + (k - k_lo));
-    const uint4 a_hi = *reinterpret_cast<const uint4*>(wt + (g + 8) * ldw + (k - k_lo));
+  constexpr int kMaxSlices = 7;
+  if (MT == 1 && !LN && per_block <= kMaxSlices * kWarps) {
+    // All of this warp's activations (8 values of row g for each of its slices) are asked for at
+    // once, before the weights are waited for: one trip to L2 on the step's chain of dependent
+    // waits instead of one for every two slices.  (Up to 56 slices a block, 7 a warp: every K up to
+    // 6,912; wider matrices take the loop below.)
+    uint4 xr[kMaxSlices];
 #pragma unroll
-    for (int t = 0; t < MT; ++t) {
-      const int m = t * 8 + g;
-      uint4 b = make_uint4(0, 0, 0, 0);
-      if (ok && m < M) {
-        if (LN) {
-          const float* r = static_cast<const float*>(xin) + (size_t)m * K + k;
-          const float4 v0 = *reinterpret_cast<const float4*>(r), v1 = *reinterpret_cast<const float4*>(r + 4);
-          const float4 g0 = *reinterpret_cast<const float4*>(gamma + k), g1 = *reinterpret_cast<const float4*>(gamma + k + 4);
-          const float4 b0 = *reinterpret_cast<const float4*>(beta + k), b1 = *reinterpret_cast<const float4*>(beta + k + 4);
-          const float mean = stats[2 * m], inv = stats[2 * m + 1];
-          b.x = pack2((v0.x - mean) * inv * g0.x + b0.x, (v0.y - mean) * inv * g0.y + b0.y);
-          b.y = pack2((v0.z - mean) * inv * g0.z + b0.z, (v0.w - mean) * inv * g0.w + b0.w);
-          b.z = pack2((v1.x - mean) * inv * g1.x + b1.x, (v1.y - mean) * inv * g1.y + b1.y);
-          b.w = pack2((v1.z - mean) * inv * g1.z + b1.z, (v1.w - mean) * inv * g1.w + b1.w);
-        } else {
-          b = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)m * K + k);
-        }
+    for (int j = 0; j < kMaxSlices; ++j) {
+      const int k = (step_lo + warp + j * kWarps) * 32 + c * 8;
+      xr[j] = make_uint4(0, 0, 0, 0);
+      if (step_lo + warp + j * kWarps < step_hi && k < K && g < M)
+        xr[j] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)g * K + k);
+    }
+    wait_for_weights();
+#pragma unroll
+    for (int j = 0; j < kMaxSlices; ++j) {
+      const int sl = step_lo + warp + j * kWarps;
+      if (sl < step_hi) {
+        const int kl = sl * 32 + c * 8 - k_lo;
+        const uint4 a_lo = *reinterpret_cast<const uint4*>(wt + g * ldw + kl);
+        const uint4 a_hi = *reinterpret_cast<const uint4*>(wt + (g + 8) * ldw + kl);
+        mma_bf16(acc[0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, xr[j].x, xr[j].y);
+        mma_bf16(acc[0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, xr[j].z, xr[j].w);
       }
-      mma_bf16(acc[t], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
-      mma_bf16(acc[t], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+    }
+  } else {
+    wait_for_weights();
+  #pragma unroll 2
+    for (int s = step_lo + warp; s < step_hi; s += kWarps) {
+      const int k = s * 32 + c * 8;
+      const bool ok = k < K;
+      const uint4 a_lo = *reinterpret_cast<const uint4*>(wt + g * ldw + (k - k_lo));
+      const uint4 a_hi = *reinterpret_cast<const uint4*>(wt + (g + 8) * ldw + (k - k_lo));
+  #pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        const int m = t * 8 + g;
+        uint4 b = make_uint4(0, 0, 0, 0);
+        if (ok && m < M) {
+          if (LN) {
+            const float* r = static_cast<const float*>(xin) + (size_t)m * K + k;
+            const float4 v0 = *reinterpret_cast<const float4*>(r), v1 = *reinterpret_cast<const float4*>(r + 4);
+            const float4 g0 = *reinterpret_cast<const float4*>(gamma + k), g1 = *reinterpret_cast<const float4*>(gamma + k + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(beta + k), b1 = *reinterpret_cast<const float4*>(beta + k + 4);
+            const float mean = stats[2 * m], inv = stats[2 * m + 1];
+            b.x = pack2((v0.x - mean) * inv * g0.x + b0.x, (v0.y - mean) * inv * g0.y + b0.y);
+            b.y = pack2((v0.z - mean) * inv * g0.z + b0.z, (v0.w - mean) * inv * g0.w + b0.w);
+            b.z = pack2((v1.x - mean) * inv * g1.x + b1.x, (v1.y - mean) * inv * g1.y + b1.y);
+            b.w = pack2((v1.z - mean) * inv * g1.z + b1.z, (v1.w - mean) * inv * g1.w + b1.w);
+          } else {
+            b = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)m * K + k);
+          }
+        }
+        mma_bf16(acc[t], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+        mma_bf16(acc[t], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+      }
     }
   }
 
