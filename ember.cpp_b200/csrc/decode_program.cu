@@ -77,11 +77,6 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
-  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
-  const int bytes = valid ? 16 : 0;
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
-}
 __device__ __forceinline__ uint4 ldcg16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
 
 // how K is cut into pieces: the fewest pieces of at most kMaxPiece, each a multiple of 32
@@ -173,33 +168,50 @@ __device__ __forceinline__ Cursor next_piece(const EmberOp* ops, int n_ops, Curs
 // A slot of the ring: [16][ldw] weights, ldw = piece_stride(piece length).
 constexpr int kSlotElems = 16 * kMaxPiece;
 
-// Asks for the weights of piece `c` and commits the copies as one group.  Every thread commits,
-// whether it had copies or not.
-__device__ void stage_piece(const EmberOp& op, const Cursor& c, __nv_bfloat16* slot) {
+// Asks for the weights of piece `c`: a bulk copy for every row of the tile that the block owns, issued
+// by the lanes of warp 0 and counted on the slot's mbarrier (no per-16-byte address arithmetic: the
+// staging loop of 16-byte cp.async took more issue slots than the products).  Rows past the block's
+// share are not fetched (their sums are dropped at the end); what a piece holds past K is zeroed
+// by hand up to the next multiple of 32, so that the products meet no stale bits there.
+__device__ void stage_piece(const EmberOp& op, const Cursor& c, __nv_bfloat16* slot, unsigned bar) {
   const LinearShape& s = c.shape;
   const int ldw = piece_stride(s.len);
   const int k0 = c.piece * s.len;
-  const int chunks = s.len / 8;
-  const __nv_bfloat16* W = static_cast<const __nv_bfloat16*>(op.w);
-  for (int i = threadIdx.x; i < 16 * chunks; i += kThreads) {
-    const int r = (unsigned)i / (unsigned)chunks, ch = i - r * chunks;
-    const int row = s.lo + c.tile * 16 + r, k = k0 + ch * 8;
-    const bool ok = row < s.hi && k < op.K;
-    cp_async_16(slot + r * ldw + ch * 8, W + (size_t)(ok ? row : s.lo) * op.K + (ok ? k : 0), ok);
+  const int valid = max(0, min(s.len, op.K - k0));            // values of K this piece really holds
+  const int rows = max(0, min(16, s.hi - (s.lo + c.tile * 16)));
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    if (lane == 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"((unsigned)(rows * valid * 2))
+                   : "memory");
+    __syncwarp();
+    if (lane < rows && valid > 0) {
+      const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(op.w) + (size_t)(s.lo + c.tile * 16 + lane) * op.K + k0;
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(slot + lane * ldw);
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                   "l"(src), "r"((unsigned)(valid * 2)), "r"(bar)
+                   : "memory");
+    }
   }
-  asm volatile("cp.async.commit_group;\n" ::);
+  const int tail = min(s.len, (valid + 31) / 32 * 32) - valid;
+  for (int i = threadIdx.x; i < 16 * tail; i += kThreads) slot[(i / tail) * ldw + valid + i % tail] = __float2bfloat16_rn(0.f);
 }
 
-__device__ __forceinline__ void wait_groups(int pending) {  // at most `pending` of the newest groups still in flight
-  switch (pending) {
-    case 0: asm volatile("cp.async.wait_group 0;\n" ::: "memory"); break;
-    case 1: asm volatile("cp.async.wait_group 1;\n" ::: "memory"); break;
-    case 2: asm volatile("cp.async.wait_group 2;\n" ::: "memory"); break;
-    case 3: asm volatile("cp.async.wait_group 3;\n" ::: "memory"); break;
-    case 4: asm volatile("cp.async.wait_group 4;\n" ::: "memory"); break;
-    case 5: asm volatile("cp.async.wait_group 5;\n" ::: "memory"); break;
-    default: asm volatile("cp.async.wait_group 6;\n" ::: "memory"); break;
+// Waits until the copies into a slot have landed.  False (and the error flag set) when the wait ran out.
+__device__ bool slot_wait(unsigned bar, unsigned parity, int* error) {
+  for (unsigned spin = 0; spin < kSpinLimit; ++spin) {
+    unsigned done;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
   }
+  atomicCAS(error, 0, 3);
+  return false;
 }
 
 // The ring of staged pieces, the same in every thread of the block.
@@ -208,6 +220,8 @@ struct Ring {
   Cursor head;  // the next piece to stage
   int count;    // staged and not yet used
   int tail_slot;
+  unsigned parity;  // bit s: the phase of slot s's mbarrier that its next use waits for
+  unsigned bars;    // shared-memory address of the slots' mbarriers
 };
 
 __device__ __forceinline__ bool fused_norm(const EmberOp& op) { return op.reserved != 0; }
@@ -217,7 +231,7 @@ __device__ __forceinline__ bool fused_norm(const EmberOp& op) { return op.reserv
 __device__ void stage_next(const EmberOp* ops, int n_ops, Ring& ring, __nv_bfloat16* wbuf) {
   if (ring.count >= kSlots || ring.head.op >= n_ops) return;
   __nv_bfloat16* slot = wbuf + (size_t)((ring.tail_slot + ring.count) % kSlots) * kSlotElems;
-  stage_piece(ops[ring.head.op], ring.head, slot);
+  stage_piece(ops[ring.head.op], ring.head, slot, ring.bars + 8 * ((ring.tail_slot + ring.count) % kSlots));
   if (ring.count == 0) ring.tail = ring.head;
   ring.head = next_piece(ops, n_ops, ring.head);
   ++ring.count;
@@ -308,9 +322,17 @@ __device__ void finish_tiles(const EmberOp& op, const LinearShape& s, int first_
 // activations it multiplies with never change during the operation, so it holds them in registers
 // (8 values of row lane/4 a slice: the B fragments of two MMAs), read once from L2, normed on the
 // way if the operation has a norm.
+__device__ __forceinline__ void dbg_mark(int*& p) {
+  if (p && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    *p++ = (int)(now & 0x7fffffff);
+  }
+}
 __device__ void run_linear(const EmberOp* ops, int n_ops, int i, Ring& ring, __nv_bfloat16* wbuf, float* red, float* part,
-                           float* stats) {
+                           float* stats, int* error, int* dbg) {
   const EmberOp& op = ops[i];
+  dbg_mark(dbg);
   // this block's share: the ring's tail is this operation's first piece if the block has rows in it
   const LinearShape s = (ring.count > 0 && ring.tail.op == i) ? ring.tail.shape : shape_of(op);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -356,9 +378,13 @@ __device__ void run_linear(const EmberOp* ops, int n_ops, int i, Ring& ring, __n
     for (int piece = 0; piece < s.pieces; ++piece) {
       // the ring's tail is this piece: pieces are staged in exactly the order they are used
       if (ring.count == 0) stage_next(ops, n_ops, ring, wbuf);
-      wait_groups(ring.count - 1);
-          __syncthreads();  // the piece is visible to all warps, and all have left the slot used before it
-          const __nv_bfloat16* wt = wbuf + (size_t)ring.tail_slot * kSlotElems;
+      dbg_mark(dbg);
+      slot_wait(ring.bars + 8 * ring.tail_slot, (ring.parity >> ring.tail_slot) & 1u, error);
+      dbg_mark(dbg);
+      ring.parity ^= 1u << ring.tail_slot;
+      __syncthreads();
+      dbg_mark(dbg);  // all warps have left the slot used before this one (it may be refilled now)
+      const __nv_bfloat16* wt = wbuf + (size_t)ring.tail_slot * kSlotElems;
       ring.tail = next_piece(ops, n_ops, ring.tail);
       ring.tail_slot = (ring.tail_slot + 1) % kSlots;
       --ring.count;
@@ -599,7 +625,16 @@ decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* b
   // arrivals before this launch: every block reads the epoch before its first arrival, and block 0
   // advances it only after its last barrier, which no block passes before all have arrived at the first
   const unsigned long long arrivals0 = *(volatile unsigned long long*)&bar->epoch * (unsigned long long)(n_ops - 1) * gridDim.x;
+  __shared__ unsigned long long slot_bars[kSlots];
+  if (threadIdx.x == 0) {
+    for (int b = 0; b < kSlots; ++b)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"((unsigned)__cvta_generic_to_shared(&slot_bars[b])));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
+  __syncthreads();
   Ring ring;
+  ring.parity = 0;
+  ring.bars = (unsigned)__cvta_generic_to_shared(slot_bars);
   ring.head = first_piece(ops, n_ops, 0);
   ring.tail = ring.head;
   ring.count = 0;
@@ -617,7 +652,7 @@ decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* b
       }
     }
     if (op.type == EMBER_OP_LINEAR) {
-      run_linear(ops, n_ops, i, ring, wbuf, red, rows, stats);
+      run_linear(ops, n_ops, i, ring, wbuf, red, rows, stats, error, (trace && (i == 6 || i == 10)) ? trace + 512 + (i == 10 ? 64 : 0) : nullptr);
       while (ring.count < kSlots && ring.head.op < n_ops) stage_next(ops, n_ops, ring, wbuf);  // the next products' weights
     } else if (op.type == EMBER_OP_ATTENTION) {
       run_attention(op, red, kAttnScratchFloats, error);
@@ -628,7 +663,11 @@ decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* b
     }
     if (i + 1 < n_ops && !grid_barrier(bar, arrivals0 + (unsigned long long)(i + 1) * gridDim.x, error)) break;
   }
-  asm volatile("cp.async.wait_all;\n" ::: "memory");  // nothing of this block is in flight when it leaves
+  // nothing of this block is in flight when it leaves: pieces staged and never used (after an error) are waited for
+  for (int j = 0; j < ring.count; ++j) {
+    const int sl = (ring.tail_slot + j) % kSlots;
+    slot_wait(ring.bars + 8 * sl, (ring.parity >> sl) & 1u, error);
+  }
   if (blockIdx.x == 0 && threadIdx.x == 0) bar->epoch = bar->epoch + 1;
   if (trace && threadIdx.x == 0) trace[blockIdx.x] = -1;  // left the kernel
 }

@@ -159,6 +159,7 @@ class DecodeProgram:
         if code != 0:
             self.state.zero_()
             self.error.zero_()
-            what = ("a block gave up waiting at a grid barrier" if code == 1 else
-                    "a token id, position or page number of the step's description was out of range")
+            what = {1: "a block gave up waiting at a grid barrier",
+                    2: "a token id, position or page number of the step's description was out of range",
+                    3: "a block gave up waiting for a weight copy"}.get(code, f"error {code}")
             raise KernelError(f"decode_program: {what}; the step's results are not valid")
