@@ -14,8 +14,9 @@
 // when the step's shape is first seen; only the step's description (tokens, positions, pages)
 // changes between launches.
 //   linear     block b owns output features [N*b/G, N*(b+1)/G) in tiles of 16 rows; a tile is
-//              brought in by cp.async in pieces of at most 800 values of K through a ring of seven
-//              slots (179 KB), six pieces always in flight, also across operations and barriers:
+//              brought in by bulk copies (a row of the tile each, counted on the slot's mbarrier) in
+//              pieces of at most 800 values of K through a ring of seven slots (179 KB), six pieces
+//              always in flight, also across operations and barriers:
 //              the weights of the next linear layers stream in while the grid runs the attention
 //              or waits.  The 16 warps take the 32-wide slices of K in turn on mma.sync with the
 //              operands swapped (as linear_decode.cu); a warp's slices are the same in every tile,
@@ -322,17 +323,9 @@ __device__ void finish_tiles(const EmberOp& op, const LinearShape& s, int first_
 // activations it multiplies with never change during the operation, so it holds them in registers
 // (8 values of row lane/4 a slice: the B fragments of two MMAs), read once from L2, normed on the
 // way if the operation has a norm.
-__device__ __forceinline__ void dbg_mark(int*& p) {
-  if (p && blockIdx.x == 0 && threadIdx.x == 0) {
-    unsigned long long now;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
-    *p++ = (int)(now & 0x7fffffff);
-  }
-}
 __device__ void run_linear(const EmberOp* ops, int n_ops, int i, Ring& ring, __nv_bfloat16* wbuf, float* red, float* part,
-                           float* stats, int* error, int* dbg) {
+                           float* stats, int* error) {
   const EmberOp& op = ops[i];
-  dbg_mark(dbg);
   // this block's share: the ring's tail is this operation's first piece if the block has rows in it
   const LinearShape s = (ring.count > 0 && ring.tail.op == i) ? ring.tail.shape : shape_of(op);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -378,12 +371,9 @@ __device__ void run_linear(const EmberOp* ops, int n_ops, int i, Ring& ring, __n
     for (int piece = 0; piece < s.pieces; ++piece) {
       // the ring's tail is this piece: pieces are staged in exactly the order they are used
       if (ring.count == 0) stage_next(ops, n_ops, ring, wbuf);
-      dbg_mark(dbg);
       slot_wait(ring.bars + 8 * ring.tail_slot, (ring.parity >> ring.tail_slot) & 1u, error);
-      dbg_mark(dbg);
       ring.parity ^= 1u << ring.tail_slot;
-      __syncthreads();
-      dbg_mark(dbg);  // all warps have left the slot used before this one (it may be refilled now)
+      __syncthreads();  // all warps have left the slot used before this one (it may be refilled now)
       const __nv_bfloat16* wt = wbuf + (size_t)ring.tail_slot * kSlotElems;
       ring.tail = next_piece(ops, n_ops, ring.tail);
       ring.tail_slot = (ring.tail_slot + 1) % kSlots;
@@ -652,7 +642,7 @@ decode_program_kernel(const EmberOp* __restrict__ ops, int n_ops, GridBarrier* b
       }
     }
     if (op.type == EMBER_OP_LINEAR) {
-      run_linear(ops, n_ops, i, ring, wbuf, red, rows, stats, error, (trace && (i == 6 || i == 10)) ? trace + 512 + (i == 10 ? 64 : 0) : nullptr);
+      run_linear(ops, n_ops, i, ring, wbuf, red, rows, stats, error);
       while (ring.count < kSlots && ring.head.op < n_ops) stage_next(ops, n_ops, ring, wbuf);  // the next products' weights
     } else if (op.type == EMBER_OP_ATTENTION) {
       run_attention(op, red, kAttnScratchFloats, error);
