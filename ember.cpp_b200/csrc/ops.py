@@ -297,7 +297,9 @@ class CudaOps:
         # the first product of a shape times the library's candidates into a scratch output (outside any capture)
         shape = (M, N, K, fused, bias is not None, residual is not None, target)
         scratch = None
-        if self.lt_tune and shape not in self._lt_tuned and not torch.cuda.is_current_stream_capturing():
+        # (large products only, and a bounded number of shapes: timing costs a few milliseconds a shape)
+        if (self.lt_tune and M >= 64 and shape not in self._lt_tuned and len(self._lt_tuned) < 512
+                and not torch.cuda.is_current_stream_capturing()):
             self._lt_tuned.add(shape)
             scratch = torch.empty_like(out)
         self._call("ember_linear_bf16", a.data_ptr(), w.data_ptr(), self._ptr(bias),
