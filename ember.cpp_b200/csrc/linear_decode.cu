@@ -51,6 +51,8 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+__device__ int g_gave_up = 0;  // set when a block's wait for its weight copies ran out
+
 constexpr int kWarps = 8;
 constexpr int kRowVecs = 16;  // float4 per lane of a row held in registers (K <= 2048)
 
@@ -286,6 +288,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
           : "=r"(done)
           : "r"(bar)
           : "memory");
+    if (!done) g_gave_up = 1;  // the results of this launch are not valid; the host asks with ember_linear_decode_status
     __syncthreads();
   };
 
@@ -447,6 +450,18 @@ int launch(const void* xin, const float* gamma, const float* beta, float eps, co
 }
 
 }  // namespace
+
+// 0, or 1 if a block of some launch since the last call gave up waiting for its weight copies (its
+// results are not valid); the flag is cleared.  Synchronizes with the device.
+EMBER_API int ember_linear_decode_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gave_up, sizeof(int)) != cudaSuccess) return 0;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gave_up, &zero, sizeof(int));
+  }
+  return v;
+}
 
 // xin: float32 [M,K] when gamma is given (layer norm fused), else bfloat16 [M,K].
 // residual: float32 [M,N] or null; it may be the output buffer.  out: float32 or bfloat16 [M,N].

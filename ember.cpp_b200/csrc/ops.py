@@ -99,8 +99,9 @@ def load_library() -> ctypes.CDLL:
         getattr(lib, name).restype = _c_int
     lib.ember_decode_program_run.argtypes = [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void]
     lib.ember_decode_program_run.restype = _c_int
-    lib.ember_tc_status.argtypes = []
-    lib.ember_tc_status.restype = _c_int
+    for name in ("ember_tc_status", "ember_linear_decode_status"):
+        getattr(lib, name).argtypes = []
+        getattr(lib, name).restype = _c_int
     lib._path = path
     return lib
 
@@ -319,6 +320,8 @@ class CudaOps:
     def check(self) -> None:
         """Raises if a kernel with bounded waits gave up since the last call.  The caller has
         synchronized with the device (it has just read a step's results)."""
+        if self.lib.ember_linear_decode_status():
+            raise KernelError("linear_decode: a block gave up waiting for its weight copies; the results of that launch are not valid")
         code = self.lib.ember_tc_status()
         if code:
             kernel = "linear_tc" if code < 10 else "attention_prefill_tc"

@@ -166,6 +166,9 @@ class Generator:
                         pending = launch(still, [(slots[i], [generated[i][-1]], [0]) for i in still], None)
                         continue
                 pending = following
+            check = getattr(eng.ops, "check", None)
+            if check is not None:
+                check()        # a kernel whose bounded wait ran out has said so (every id has been read: the device is idle)
         finally:
             for slot in slots.values():
                 eng.close(slot)
