@@ -68,13 +68,27 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float 
   d2[1] = __floats2bfloat162_rn(c, d);
 }
 
-template <typename OutT>
+// EARLY: the gain and the bias (constants of the model; in a decode step each layer's come from
+// DRAM) are fetched into registers before the kernel in front is waited for, so that they are
+// not a second trip to memory after the row's statistics.  Costs registers: for a few rows only.
+template <typename OutT, bool EARLY>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                                  OutT* __restrict__ out, int rows, int d, float eps) {
   pdl_trigger();
-  pdl_wait();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
+  float4 gm_early[EARLY ? kRowVecs : 1], bt_early[EARLY ? kRowVecs : 1];
+  if (EARLY && (d & 3) == 0 && d <= 128 * kRowVecs) {
+#pragma unroll
+    for (int j = 0; j < kRowVecs; ++j) {
+      const int i = lane + 32 * j;
+      if (i < (d >> 2)) {
+        gm_early[j] = reinterpret_cast<const float4*>(w)[i];
+        bt_early[j] = reinterpret_cast<const float4*>(b)[i];
+      }
+    }
+  }
+  pdl_wait();
   if (row >= rows) return;
   const float* r = x + (size_t)row * d;
   OutT* o = out + (size_t)row * d;
@@ -103,7 +117,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     for (int j = 0; j < kRowVecs; ++j) {
       const int i = lane + 32 * j;
       if (i < nv) {
-        const float4 gm = reinterpret_cast<const float4*>(w)[i], bt = reinterpret_cast<const float4*>(b)[i];
+        const float4 gm = EARLY ? gm_early[j] : reinterpret_cast<const float4*>(w)[i];
+        const float4 bt = EARLY ? bt_early[j] : reinterpret_cast<const float4*>(b)[i];
         store4<OutT>(o + 4 * i, (v[j].x - mean) * inv * gm.x + bt.x, (v[j].y - mean) * inv * gm.y + bt.y,
                      (v[j].z - mean) * inv * gm.z + bt.z, (v[j].w - mean) * inv * gm.w + bt.w);
       }
@@ -129,11 +144,17 @@ EMBER_API int ember_layernorm(const float* x, const float* w, const float* b, vo
   const int warps = rows < 64 ? 1 : 4;  // a few rows: a block each, so that they run on different SMs
   const int grid = (rows + warps - 1) / warps;
   cudaError_t e;
+  const bool early = rows < 64;
   if (out_dtype == EMBER_F32)
-    e = launch_pdl(layernorm_kernel<float>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b, (float*)out, rows, d, eps);
+    e = early ? launch_pdl(layernorm_kernel<float, true>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b, (float*)out, rows,
+                           d, eps)
+              : launch_pdl(layernorm_kernel<float, false>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b, (float*)out, rows,
+                           d, eps);
   else if (out_dtype == EMBER_BF16)
-    e = launch_pdl(layernorm_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b,
-                   (__nv_bfloat16*)out, rows, d, eps);
+    e = early ? launch_pdl(layernorm_kernel<__nv_bfloat16, true>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b,
+                           (__nv_bfloat16*)out, rows, d, eps)
+              : launch_pdl(layernorm_kernel<__nv_bfloat16, false>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b,
+                           (__nv_bfloat16*)out, rows, d, eps);
   else
     return ember_fail("layernorm: element type %d", out_dtype);
   if (e != cudaSuccess) return ember_fail("layernorm: %s", cudaGetErrorString(e));
