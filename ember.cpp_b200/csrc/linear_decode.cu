@@ -215,13 +215,15 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
     }
   }
   pdl_trigger();
-  pdl_wait();
-
-  // the element of the output tile that this thread finishes (block 0 of the cluster only)
+  // the element of the output tile that this thread finishes (block 0 of the cluster only); its
+  // bias is a constant of the model and is fetched before the wait (in a decode step it comes from
+  // DRAM: after the wait it would be the longest of the loads the epilogue waits for)
   const int e_r = threadIdx.x % 16, e_m = threadIdx.x / 16;
   const int e_n = row0 + e_r;
   const bool e_ok = rank == 0 && threadIdx.x < kTile && e_m < M && e_n < N;
   const float e_bias = (e_ok && bias) ? bias[e_n] : 0.f;
+  pdl_wait();
+
   const float e_res = (e_ok && residual) ? residual[(size_t)e_m * N + e_n] : 0.f;
 
   if (LN) {
