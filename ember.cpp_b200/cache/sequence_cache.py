@@ -104,6 +104,10 @@ class CacheView:
     def __init__(self, group_index: int, group: CacheGroup, local: int):
         self.group_index = group_index
         self.k, self.v = group.k[local], group.v[local]
+        # the storage of the application that runs next from this group (the first one after the last):
+        # a kernel may warm it while it reads this one
+        n = len(group.k)
+        self.following = (group.k[(local + 1) % n], group.v[(local + 1) % n]) if n > 1 else None
         self.kv_heads, self.head_dim = group.need.kv_heads, group.need.head_dim
         self.window = group.need.window if group.need.kind == "window" else 0
 

@@ -25,6 +25,7 @@ namespace {
 constexpr int kThreads = 128;
 constexpr int kUnroll = 4;          // keys a stream has in flight
 constexpr int kMaxChunkPages = 64;  // page numbers of a chunk kept in shared memory
+constexpr int kMergeAtOnce = 8;     // chunks whose partial results the merging block fetches in one batch
 
 template <int LPK>  // lanes per key; each lane owns 8 consecutive dims
 __global__ void __launch_bounds__(kThreads, 8)
@@ -34,7 +35,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
                         const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks, int n_heads,
                         int kv_heads, int hd, float scale, int window, int pages_per_chunk, int n_chunks,
-                        __nv_bfloat16* __restrict__ k_store, __nv_bfloat16* __restrict__ v_store) {
+                        __nv_bfloat16* __restrict__ k_store, __nv_bfloat16* __restrict__ v_store,
+                        const __nv_bfloat16* __restrict__ ahead_k, const __nv_bfloat16* __restrict__ ahead_v) {
   constexpr int kGroups = 32 / LPK;           // key streams per warp
   constexpr int kStreams = 4 * kGroups;       // per block
   __shared__ float s_m[kStreams], s_l[kStreams];
@@ -63,6 +65,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   const int chunk_keys = pages_per_chunk * kPage;
   const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
   if (c < first_chunk || c > last_chunk) return;
+  EMBER_MARK_START(kAttentionDecode);
   const bool own = k_store != nullptr && c == last_chunk;  // this block also takes the token's own key
   // cached keys of this chunk: [begin, end); the token's own position is not among them when this
   // launch stores it (it is taken from the step's activations instead)
@@ -107,11 +110,30 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   // were launched this way can be several deep in their waits.
   if (!k_store) pdl_wait();
   fetch(begin);
+  if (ahead_k && h % (n_heads / kv_heads) == 0) {
+    // The cache of the layer that attends next holds the same rows in the same pages.  Asking them
+    // into L2 now, a layer early, turns that layer's trips to DRAM into trips to L2.  One bulk
+    // prefetch per page and tensor: a page's rows for one head are contiguous.
+    const int first_blk = c * pages_per_chunk;
+    for (int i = threadIdx.x; i < 2 * pages_per_chunk; i += kThreads) {
+      const int blk = first_blk + (i >> 1);
+      const int r0 = max(begin, blk * kPage) - blk * kPage, r1 = min(end, (blk + 1) * kPage) - blk * kPage;
+      if (r1 > r0 && blk < max_blocks) {
+        const int page = my_pages[blk];
+        if (page >= 0) {
+          const __nv_bfloat16* at = ((i & 1) ? ahead_v : ahead_k) + (((size_t)page * kv_heads + kvh) * kPage + r0) * hd;
+          const unsigned bytes = (unsigned)(r1 - r0) * hd * 2;
+          asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(at), "r"(bytes) : "memory");
+        }
+      }
+    }
+  }
   if (k_store) pdl_wait();
+  EMBER_MARK(kAttentionDecode, kDependency);
 
-  float q[8];
+  float2 q[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) q[i] = 0.f;
+  for (int i = 0; i < 4; ++i) q[i] = make_float2(0.f, 0.f);
   if (dims) unpack8(*reinterpret_cast<const uint4*>(qkv + (size_t)t * width + (size_t)h * hd + sub * 8), q);
   uint4 own_k = make_uint4(0, 0, 0, 0), own_v = make_uint4(0, 0, 0, 0);
   if (own) {
@@ -136,20 +158,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     }
   }
 
-  float m = -INFINITY, l = 0.f, acc[8];
+  float m = -INFINITY, l = 0.f;
+  float2 acc[4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int i = 0; i < 4; ++i) acc[i] = make_float2(0.f, 0.f);
 
   // Every lane of a warp makes the same number of trips (the shuffles name all 32 lanes).  A trip
   // takes kUnroll keys per stream: their loads are issued together, then they are folded into the
   // stream's running softmax one after the other.
   for (int j0 = begin; j0 < end; j0 += kUnroll * kStreams) {
     if (j0 != begin) fetch(j0);
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) fold_key<LPK>(kraw[u], vraw[u], have[u], q, scale, m, l, acc);
+    fold_keys<LPK, kUnroll>(kraw, vraw, have, q, scale, m, l, acc);
   }
-  if (own && warp == 0) fold_key<LPK>(own_k, own_v, sid == 0, q, scale, m, l, acc);  // all of warp 0: its shuffles are whole-warp
+  if (own && warp == 0) {  // all of warp 0: its shuffles are whole-warp
+    const uint4 ok[1] = {own_k}, ov[1] = {own_v};
+    const bool oh[1] = {sid == 0};
+    fold_keys<LPK, 1>(ok, ov, oh, q, scale, m, l, acc);
+  }
 
+  EMBER_MARK(kAttentionDecode, kPhaseA);  // keys folded
   // merge the block's streams
   if (sub == 0) {
     s_m[sid] = m;
@@ -157,7 +184,10 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   }
   if (dims) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) s_acc[sid][sub * 8 + i] = acc[i];
+    for (int i = 0; i < 4; ++i) {
+      s_acc[sid][sub * 8 + 2 * i] = acc[i].x;
+      s_acc[sid][sub * 8 + 2 * i + 1] = acc[i].y;
+    }
   }
   __syncthreads();
   float M = -INFINITY;
@@ -179,7 +209,11 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     else
       part_acc[(item + c) * hd + d] = A;
   }
-  if (n_valid == 1) return;
+  if (n_valid == 1) {
+    EMBER_MARK(kAttentionDecode, kEnd);
+    return;
+  }
+  EMBER_MARK(kAttentionDecode, kPhaseB);  // streams merged, partial result on its way
   if (threadIdx.x == 0) {
     part_ml[(item + c) * 2] = M;
     part_ml[(item + c) * 2 + 1] = L;
@@ -194,8 +228,42 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     if (s_last) counters[t * n_heads + h] = 0;  // zero again for the next call
   }
   __syncthreads();
-  if (!s_last) return;
+  EMBER_MARK(kAttentionDecode, kPhaseC);  // ticket taken
+  if (!s_last) {
+    EMBER_MARK(kAttentionDecode, kEnd);
+    return;
+  }
   __threadfence();
+  if (n_valid <= kMergeAtOnce) {
+    // Everything a thread needs of up to kMergeAtOnce chunks is asked for at once: one trip to L2
+    // where the loops below make three.  Same sums in the same order.
+    for (int d = threadIdx.x; d < hd; d += kThreads) {
+      float2 ml[kMergeAtOnce];
+      float a[kMergeAtOnce];
+#pragma unroll
+      for (int i = 0; i < kMergeAtOnce; ++i) {
+        const int cc = min(first_chunk + i, last_chunk);
+        ml[i] = __ldcg(reinterpret_cast<const float2*>(part_ml + (item + cc) * 2));
+        a[i] = __ldcg(&part_acc[(item + cc) * hd + d]);
+      }
+      float MM = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < kMergeAtOnce; ++i)
+        if (i < n_valid) MM = fmaxf(MM, ml[i].x);
+      float LL = 0.f, A = 0.f;
+#pragma unroll
+      for (int i = 0; i < kMergeAtOnce; ++i) {
+        if (i < n_valid) {
+          const float w = __expf(ml[i].x - MM);
+          LL += ml[i].y * w;
+          A += a[i] * w;
+        }
+      }
+      o[d] = __float2bfloat16_rn(A / LL);
+    }
+    EMBER_MARK(kAttentionDecode, kMerged);
+    return;
+  }
   float MM = -INFINITY;
   for (int cc = first_chunk; cc <= last_chunk; ++cc) MM = fmaxf(MM, __ldcg(&part_ml[(item + cc) * 2]));
   float LL = 0.f;
@@ -207,6 +275,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
       A += __ldcg(&part_acc[(item + cc) * hd + d]) * __expf(__ldcg(&part_ml[(item + cc) * 2]) - MM);
     o[d] = __float2bfloat16_rn(A / LL);
   }
+  EMBER_MARK(kAttentionDecode, kMerged);
 }
 
 }  // namespace
@@ -223,11 +292,13 @@ EMBER_API size_t ember_attention_decode_partials(int T, int n_heads, int hd, int
 // partials: ember_attention_decode_partials(...) floats of scratch, contents irrelevant.
 // counters: T * n_heads ints of scratch that are zero before the first call; every call leaves
 // them zero.  Calls that share scratch must not overlap on the device.
-EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void* vc, void* out, float* partials,
-                                     int* counters, const int* positions, const int* token_seq, const int* seq_slot,
-                                     const int* pages, int max_blocks, int n_blocks, int T, int n_heads, int kv_heads,
-                                     int hd, float scale, int window, int pages_per_chunk, int store_kv,
-                                     cudaStream_t stream) {
+// ahead_k, ahead_v: null, or the key and value pages of the layer that attends next (same shape, same
+// page table): the rows this call reads are asked into L2 for that layer.
+EMBER_API int ember_attention_decode_ahead(const void* qkv, const void* kc, const void* vc, void* out, float* partials,
+                                           int* counters, const int* positions, const int* token_seq, const int* seq_slot,
+                                           const int* pages, int max_blocks, int n_blocks, int T, int n_heads, int kv_heads,
+                                           int hd, float scale, int window, int pages_per_chunk, int store_kv,
+                                           const void* ahead_k, const void* ahead_v, cudaStream_t stream) {
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0 && n_blocks > 0 && n_blocks <= max_blocks,
               "attention_decode: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_decode: %d heads are not a multiple of %d key/value heads", n_heads,
@@ -248,7 +319,8 @@ EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void
                  (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_ml, part_acc, counters, \
                  positions, token_seq, seq_slot, pages, max_blocks, n_heads, kv_heads, hd, scale, window,           \
                  pages_per_chunk, n_chunks, store_kv ? (__nv_bfloat16*)kc : (__nv_bfloat16*)nullptr,                 \
-                 store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr)
+                 store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr, (const __nv_bfloat16*)ahead_k,                \
+                 (const __nv_bfloat16*)ahead_v)
   if (hd <= 16) EMBER_DECODE(2);
   else if (hd <= 32) EMBER_DECODE(4);
   else if (hd <= 64) EMBER_DECODE(8);
@@ -257,6 +329,16 @@ EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void
 #undef EMBER_DECODE
   if (e != cudaSuccess) return ember_fail("attention_decode: %s", cudaGetErrorString(e));
   return 0;
+}
+
+EMBER_API int ember_attention_decode(const void* qkv, const void* kc, const void* vc, void* out, float* partials,
+                                     int* counters, const int* positions, const int* token_seq, const int* seq_slot,
+                                     const int* pages, int max_blocks, int n_blocks, int T, int n_heads, int kv_heads,
+                                     int hd, float scale, int window, int pages_per_chunk, int store_kv,
+                                     cudaStream_t stream) {
+  return ember_attention_decode_ahead(qkv, kc, vc, out, partials, counters, positions, token_seq, seq_slot, pages,
+                                      max_blocks, n_blocks, T, n_heads, kv_heads, hd, scale, window, pages_per_chunk,
+                                      store_kv, nullptr, nullptr, stream);
 }
 
 // ---------------------------------------------------------------------------- without allocation
@@ -319,3 +401,5 @@ EMBER_API int ember_attention_decode_static(const void* qkv, const void* kc, con
                                 seq_slot, pages, max_blocks, n_blocks, T, n_heads, kv_heads, hd, scale, window,
                                 pages_per_chunk, store_kv, stream);
 }
+
+EMBER_TIMELINE_READER(attention_decode)

@@ -21,6 +21,11 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libember_kernels.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+# EMBER_TIMELINE=1: the kernels of a decode step note when their blocks start, pass their wait for
+# the kernel in front and end (`CudaOps.timeline`).  That library is built beside the ordinary one.
+TIMELINE = os.environ.get("EMBER_TIMELINE", "0") == "1"
+if TIMELINE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DEMBER_TIMELINE"]
 
 
 class BuildError(RuntimeError):
@@ -55,7 +60,7 @@ def _digest() -> str:
 
 
 def _build_dir() -> str:
-    d = os.path.join(HERE, "_build")
+    d = os.path.join(HERE, "_build_timeline" if TIMELINE else "_build")
     try:
         os.makedirs(d, exist_ok=True)
         probe = os.path.join(d, f".probe{os.getpid()}")
@@ -64,7 +69,7 @@ def _build_dir() -> str:
         os.remove(probe)
         return d
     except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"ember_cpp_b200_build_{os.getuid()}")
+        d = os.path.join(tempfile.gettempdir(), f"ember_cpp_b200_build{'_timeline' if TIMELINE else ''}_{os.getuid()}")
         os.makedirs(d, exist_ok=True)
         return d
 

@@ -78,6 +78,82 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
+// Timeline of a step's kernels.  A library built with -DEMBER_TIMELINE (EMBER_TIMELINE=1 in the
+// environment when it is built; it goes to a folder of its own) has every block of the decode
+// step's kernels note the global timer when it starts, when its wait for the kernel before it
+// returns, when it ends, and at a few places between.  Each source file keeps its own log (there is no relocatable device
+// code to share one) and exports a reader; without the flag the marks compile to nothing.
+#ifdef EMBER_TIMELINE
+namespace timeline {
+constexpr unsigned kMarks = 8;          // marks a block can leave
+constexpr unsigned kCap = 1u << 18;     // entries of a file's log
+enum Kernel { kEmbed = 1, kLayerNorm = 2, kLinearDecode = 3, kAttentionDecode = 4, kSample = 5 };
+enum Mark { kStart = 0, kDependency = 1, kEnd = 2, kMerged = 3, kPhaseA = 4, kPhaseB = 5, kPhaseC = 6, kPhaseD = 7 };
+struct Entry {
+  unsigned long long t;  // nanoseconds of the global timer; 0: the block did not leave this mark
+  unsigned what;         // kernel << 8 | mark
+  unsigned block;        // linear block index
+  unsigned grid;         // blocks of the launch
+  unsigned pad;
+};
+static __device__ Entry g_log[kCap];
+static __device__ unsigned g_n;
+__device__ __forceinline__ unsigned long long now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void put(unsigned at, unsigned kernel, unsigned m) {
+  if (at + m < kCap) {
+    Entry e;
+    e.t = now();
+    e.what = kernel << 8 | m;
+    e.block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    e.grid = gridDim.x * gridDim.y * gridDim.z;
+    e.pad = 0;
+    g_log[at + m] = e;
+  }
+}
+// The block's first mark takes its kMarks places in the log (the only atomic: later marks wait
+// for nothing); thread 0 keeps the place.
+__device__ __forceinline__ unsigned start(unsigned kernel) {
+  unsigned at = kCap;
+  if (threadIdx.x == 0) {
+    at = atomicAdd(&g_n, kMarks);
+    put(at, kernel, kStart);
+  }
+  return at;
+}
+__device__ __forceinline__ void mark(unsigned at, unsigned kernel, unsigned m) {
+  if (threadIdx.x == 0) put(at, kernel, m);
+}
+// Copies this file's log to dst (room for cap entries), empties it and returns how many places
+// were taken (places whose time is 0 were not written).
+inline int read(void* dst, unsigned cap) {
+  unsigned n = 0;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&n, g_n, sizeof(n)) != cudaSuccess) return -1;
+  if (n > kCap) n = kCap;
+  if (n > cap) n = cap;
+  if (n && cudaMemcpyFromSymbol(dst, g_log, (size_t)n * sizeof(Entry)) != cudaSuccess) return -1;
+  void* log_at = nullptr;
+  if (cudaGetSymbolAddress(&log_at, g_log) != cudaSuccess) return -1;
+  if (n && cudaMemset(log_at, 0, (size_t)n * sizeof(Entry)) != cudaSuccess) return -1;
+  const unsigned zero = 0;
+  if (cudaMemcpyToSymbol(g_n, &zero, sizeof(zero)) != cudaSuccess) return -1;
+  return (int)n;
+}
+}  // namespace timeline
+#define EMBER_MARK_START(kernel) const unsigned ember_tl = timeline::start(timeline::kernel)
+#define EMBER_MARK(kernel, m) timeline::mark(ember_tl, timeline::kernel, timeline::m)
+#define EMBER_TIMELINE_READER(file) \
+  EMBER_API int ember_timeline_read_##file(void* dst, unsigned cap) { return timeline::read(dst, cap); }
+#else
+#define EMBER_MARK_START(kernel)
+#define EMBER_MARK(kernel, m)
+#define EMBER_TIMELINE_READER(file)
+#endif
+
 // EMBER_PDL=0 in the environment launches these kernels the ordinary way (for measurements).
 inline int pdl_allowed() {
   static const int on = [] {

@@ -25,6 +25,7 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ table, const T* __restrict__ pos_table, float* __restrict__ x,
                              int d) {
+  EMBER_MARK_START(kEmbed);
   const int t = blockIdx.x;
   const T* row = table + (size_t)tokens[t] * d;
   const T* prow = pos_table ? pos_table + (size_t)positions[t] * d : nullptr;
@@ -33,6 +34,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
     if (prow) v += to_float(prow[i]);
     x[(size_t)t * d + i] = v;
   }
+  EMBER_MARK(kEmbed, kEnd);
 }
 
 EMBER_API int ember_embed(const int* tokens, const int* positions, const void* table, const void* pos_table, float* x,
@@ -74,6 +76,7 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float 
 template <typename OutT, bool EARLY>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                                  OutT* __restrict__ out, int rows, int d, float eps) {
+  EMBER_MARK_START(kLayerNorm);
   pdl_trigger();
   const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -89,6 +92,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     }
   }
   pdl_wait();
+  EMBER_MARK(kLayerNorm, kDependency);
   if (row >= rows) return;
   const float* r = x + (size_t)row * d;
   OutT* o = out + (size_t)row * d;
@@ -113,6 +117,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
       }
     }
     const float inv = 1.0f / sqrtf(warp_sum(q) / (float)d + eps);
+    EMBER_MARK(kLayerNorm, kPhaseA);  // statistics taken
 #pragma unroll
     for (int j = 0; j < kRowVecs; ++j) {
       const int i = lane + 32 * j;
@@ -123,6 +128,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
                      (v[j].z - mean) * inv * gm.z + bt.z, (v[j].w - mean) * inv * gm.w + bt.w);
       }
     }
+    EMBER_MARK(kLayerNorm, kEnd);
     return;
   }
   float s = 0.f;
@@ -219,3 +225,5 @@ EMBER_API int ember_act_inplace(void* y, size_t n, int act, int dtype, cudaStrea
   EMBER_LAUNCH_OK("activation");
   return 0;
 }
+
+EMBER_TIMELINE_READER(elementwise)

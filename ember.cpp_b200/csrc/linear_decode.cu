@@ -150,14 +150,20 @@ struct TailNorm {  // all null / zero: no tail norm
   int* counter;        // zero between launches
 };
 
+struct Warm {  // null / 0: nothing
+  const char* at;            // constants of a kernel that runs soon (the next product's weights) ...
+  unsigned long long bytes;  // ... a multiple of 16, which this launch's blocks ask into L2, a share each
+};
+
 // MT: batch tiles of 8 sequences (1 or 2).  LN: float32 input with a fused layer norm.
 template <int MT, bool LN>
 __global__ void __launch_bounds__(kWarps * 32, 3)
 linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gamma, const float* __restrict__ beta,
                      float eps, const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias,
                      const float* residual, void* out, int M, int N, int K, int act, int out_f32, int k_split,
-                     const TailNorm tail) {
+                     const TailNorm tail, const Warm warm) {
   constexpr int kTile = 16 * 8 * MT;
+  EMBER_MARK_START(kLinearDecode);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, c = lane & 3;
@@ -174,6 +180,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   float* red = reinterpret_cast<float*>(wt + 16 * ldw);
   float* gather = red + kWarps * kTile;
   float* stats = gather + k_split * kTile;
+  float* gain_s = stats + 2 * 16;                  // LN only: gamma[k_lo, k_hi) then beta[k_lo, k_hi)
 
   // The block's whole share of the matrix is asked for before anything else: it does not depend
   // on the kernel before this one, whose completion is awaited only after that.  Sixteen bulk
@@ -191,8 +198,19 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   }
   __syncthreads();
   if (warp == 0) {
-    if (lane == 0) asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(16u * row_bytes) : "memory");
+    // with a fused norm, its gain and bias over the block's range of K come the same way
+    const unsigned norm_bytes = LN ? 2u * row_bytes : 0u;  // float32: twice a weight row's bytes, each
+    if (lane == 0)
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(16u * row_bytes + 2u * norm_bytes)
+                   : "memory");
     __syncwarp();
+    if (LN && lane >= 16 && lane < 18 && norm_bytes) {
+      const float* src = (lane == 16 ? gamma : beta) + k_lo;
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(gain_s + (lane == 16 ? 0 : k_hi - k_lo));
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                   "l"(src), "r"(norm_bytes), "r"(bar)
+                   : "memory");
+    }
     if (lane < 16 && row_bytes) {
       const int row = min(row0 + lane, N - 1);
       const unsigned dst = (unsigned)__cvta_generic_to_shared(wt + lane * ldw);
@@ -206,12 +224,15 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
     for (int i = threadIdx.x; i < 16 * tail; i += kWarps * 32)
       wt[(i / tail) * ldw + (k_hi - k_lo) + i % tail] = __float2bfloat16_rn(0.f);
   }
-  if (LN) {
-    // the norm's gain and bias are constants too: bring their lines into L1 now
-    const int lines = (K * (int)sizeof(float) + 127) / 128;
-    for (int i = threadIdx.x; i < 2 * lines; i += kWarps * 32) {
-      const float* p = (i < lines ? gamma : beta) + (size_t)(i % lines) * 32;
-      asm volatile("prefetch.global.L1 [%0];\n" ::"l"(p));
+  if (warm.at && warp == 1) {
+    // A product whose blocks cannot be resident beside this one's (shared memory) starts to stream
+    // its weights only when these blocks leave.  Asked into L2 now, they come from there.
+    constexpr unsigned kPiece = 8192;
+    const unsigned long long share = ((warm.bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+    const unsigned long long lo = share * blockIdx.x, hi = min(warm.bytes, lo + share);
+    for (unsigned long long at = lo + (unsigned long long)lane * kPiece; at < hi; at += 32ull * kPiece) {
+      const unsigned n = (unsigned)min((unsigned long long)kPiece, hi - at);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(warm.at + at), "r"(n) : "memory");
     }
   }
   pdl_trigger();
@@ -223,6 +244,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   const bool e_ok = rank == 0 && threadIdx.x < kTile && e_m < M && e_n < N;
   const float e_bias = (e_ok && bias) ? bias[e_n] : 0.f;
   pdl_wait();
+  EMBER_MARK(kLinearDecode, kDependency);
 
   const float e_res = (e_ok && residual) ? residual[(size_t)e_m * N + e_n] : 0.f;
 
@@ -292,6 +314,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
           : "memory");
     if (!done) g_gave_up = 1;  // the results of this launch are not valid; the host asks with ember_linear_decode_status
     __syncthreads();
+    EMBER_MARK(kLinearDecode, kPhaseA);  // weights landed
   };
 
   float acc[MT][4];
@@ -326,6 +349,45 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
         mma_bf16(acc[0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, xr[j].z, xr[j].w);
       }
     }
+  } else if (MT == 1 && LN && per_block <= kMaxSlices * kWarps) {
+    // The same with the norm: this thread's values of row g (float32, 8 for each of its slices; the
+    // warp that took the row's statistics has just read them, so most come from this SM's L1) are
+    // asked for at once, then normalised with the gain and bias that came with the weights and
+    // rounded to bfloat16 as they enter the MMAs.
+    const float* x = static_cast<const float*>(xin);
+    float4 xa[kMaxSlices], xb[kMaxSlices];
+#pragma unroll
+    for (int j = 0; j < kMaxSlices; ++j) {
+      const int k = (step_lo + warp + j * kWarps) * 32 + c * 8;
+      xa[j] = xb[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (step_lo + warp + j * kWarps < step_hi && k < K && g < M) {
+        xa[j] = *reinterpret_cast<const float4*>(x + (size_t)g * K + k);
+        xb[j] = *reinterpret_cast<const float4*>(x + (size_t)g * K + k + 4);
+      }
+    }
+    wait_for_weights();  // and for the gain and bias; its barrier also publishes the statistics
+    const float mean = g < M ? stats[2 * g] : 0.f, inv = g < M ? stats[2 * g + 1] : 0.f;
+    const float* beta_s = gain_s + (k_hi - k_lo);
+#pragma unroll
+    for (int j = 0; j < kMaxSlices; ++j) {
+      const int sl = step_lo + warp + j * kWarps;
+      if (sl < step_hi) {
+        const int kl = sl * 32 + c * 8 - k_lo;
+        uint4 b = make_uint4(0, 0, 0, 0);
+        if (kl + k_lo < K && g < M) {
+          const float4 g0 = *reinterpret_cast<const float4*>(gain_s + kl), g1 = *reinterpret_cast<const float4*>(gain_s + kl + 4);
+          const float4 b0 = *reinterpret_cast<const float4*>(beta_s + kl), b1 = *reinterpret_cast<const float4*>(beta_s + kl + 4);
+          b.x = pack2((xa[j].x - mean) * inv * g0.x + b0.x, (xa[j].y - mean) * inv * g0.y + b0.y);
+          b.y = pack2((xa[j].z - mean) * inv * g0.z + b0.z, (xa[j].w - mean) * inv * g0.w + b0.w);
+          b.z = pack2((xb[j].x - mean) * inv * g1.x + b1.x, (xb[j].y - mean) * inv * g1.y + b1.y);
+          b.w = pack2((xb[j].z - mean) * inv * g1.z + b1.z, (xb[j].w - mean) * inv * g1.w + b1.w);
+        }
+        const uint4 a_lo = *reinterpret_cast<const uint4*>(wt + g * ldw + kl);
+        const uint4 a_hi = *reinterpret_cast<const uint4*>(wt + (g + 8) * ldw + kl);
+        mma_bf16(acc[0], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);
+        mma_bf16(acc[0], a_lo.z, a_hi.z, a_lo.w, a_hi.w, b.z, b.w);
+      }
+    }
   } else {
     wait_for_weights();
   #pragma unroll 2
@@ -342,8 +404,10 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
           if (LN) {
             const float* r = static_cast<const float*>(xin) + (size_t)m * K + k;
             const float4 v0 = *reinterpret_cast<const float4*>(r), v1 = *reinterpret_cast<const float4*>(r + 4);
-            const float4 g0 = *reinterpret_cast<const float4*>(gamma + k), g1 = *reinterpret_cast<const float4*>(gamma + k + 4);
-            const float4 b0 = *reinterpret_cast<const float4*>(beta + k), b1 = *reinterpret_cast<const float4*>(beta + k + 4);
+            const float* gs = gain_s + (k - k_lo);
+            const float* bs = gs + (k_hi - k_lo);
+            const float4 g0 = *reinterpret_cast<const float4*>(gs), g1 = *reinterpret_cast<const float4*>(gs + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(bs), b1 = *reinterpret_cast<const float4*>(bs + 4);
             const float mean = stats[2 * m], inv = stats[2 * m + 1];
             b.x = pack2((v0.x - mean) * inv * g0.x + b0.x, (v0.y - mean) * inv * g0.y + b0.y);
             b.y = pack2((v0.z - mean) * inv * g0.z + b0.z, (v0.w - mean) * inv * g0.w + b0.w);
@@ -359,6 +423,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
     }
   }
 
+  EMBER_MARK(kLinearDecode, kPhaseB);  // products done
   // warps -> block: tile element (weight row r, sequence m) at [r * 8*MT + m], summed in warp order
 #pragma unroll
   for (int t = 0; t < MT; ++t) {
@@ -393,6 +458,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
     else
       static_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(v);
   }
+  EMBER_MARK(kLinearDecode, kEnd);
   if (tail.out) {  // block 0 of every cluster comes here: one ticket a tile
     __shared__ int s_last;
     __threadfence();  // this thread's store is visible to the whole device before the ticket is taken
@@ -409,7 +475,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
 template <int MT, bool LN>
 int launch(const void* xin, const float* gamma, const float* beta, float eps, const void* W, const float* bias,
            const float* residual, void* out, int M, int N, int K, int act, int out_dtype, const TailNorm& tail,
-           cudaStream_t stream) {
+           const Warm& warm, cudaStream_t stream) {
   const int tiles = (N + 15) / 16;
   const int all_steps = (K + 31) / 32;
   // Split K over a cluster (1, 2 or 4 blocks) so that a block's share of the matrix fits the
@@ -420,7 +486,8 @@ int launch(const void* xin, const float* gamma, const float* beta, float eps, co
   while (k_split < 4 && tiles * k_split * 2 <= 3 * 148 && all_steps / (k_split * 2) >= 2 * kWarps) k_split *= 2;
   const int per_block = (all_steps + k_split - 1) / k_split;
   const size_t smem = (size_t)16 * tile_stride(per_block) * sizeof(__nv_bfloat16) +
-                      (size_t)(kWarps + k_split) * 16 * 8 * MT * sizeof(float) + 2 * 16 * sizeof(float);
+                      (size_t)(kWarps + k_split) * 16 * 8 * MT * sizeof(float) + 2 * 16 * sizeof(float) +
+                      (LN ? (size_t)2 * per_block * 32 * sizeof(float) : 0);
   if (smem > 200 * 1024)
     return ember_fail("linear_decode: K = %d needs %zu bytes of shared memory per block", K, smem);
   static size_t configured = 0;
@@ -446,7 +513,8 @@ int launch(const void* xin, const float* gamma, const float* beta, float eps, co
   cfg.numAttrs = 2;
   const int out_f32 = out_dtype == EMBER_F32;
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_decode_kernel<MT, LN>, xin, gamma, beta, eps,
-                                     (const __nv_bfloat16*)W, bias, residual, out, M, N, K, act, out_f32, k_split, tail);
+                                     (const __nv_bfloat16*)W, bias, residual, out, M, N, K, act, out_f32, k_split, tail,
+                                     warm);
   if (e != cudaSuccess) return ember_fail("linear_decode: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -467,12 +535,15 @@ EMBER_API int ember_linear_decode_status() {
 
 // xin: float32 [M,K] when gamma is given (layer norm fused), else bfloat16 [M,K].
 // residual: float32 [M,N] or null; it may be the output buffer.  out: float32 or bfloat16 [M,N].
+// warm, warm_bytes: null and 0, or constants that a kernel soon after this one reads (the next
+// product's weight matrix): this launch's blocks ask them into L2 before they wait for anything.
 // tail_*: all null, or the layer norm to apply to the float32 output's rows once they are complete
 // (gain and bias float32 [N], result bfloat16 [M,N], a counter that is zero and is left zero).
 EMBER_API int ember_linear_decode(const void* xin, const float* gamma, const float* beta, float eps, const void* W,
                                   const float* bias, const float* residual, void* out, int M, int N, int K, int act,
                                   int out_dtype, const float* tail_gamma, const float* tail_beta, float tail_eps,
-                                  void* tail_out, int* tail_counter, cudaStream_t stream) {
+                                  void* tail_out, int* tail_counter, const void* warm, size_t warm_bytes,
+                                  cudaStream_t stream) {
   EMBER_CHECK(M > 0 && M <= 16 && N > 0 && K > 0, "linear_decode: M = %d (at most 16), N = %d, K = %d", M, N, K);
   EMBER_CHECK(K % 8 == 0, "linear_decode: K = %d is not a multiple of 8 (16-byte rows)", K);
   EMBER_CHECK(act >= 0 && act <= 2, "linear_decode: activation %d", act);
@@ -486,10 +557,15 @@ EMBER_API int ember_linear_decode(const void* xin, const float* gamma, const flo
   } else {
     tail = TailNorm{nullptr, nullptr, 0.f, nullptr, nullptr};
   }
+  EMBER_CHECK(warm_bytes % 16 == 0 && (reinterpret_cast<size_t>(warm) & 15) == 0,
+              "linear_decode: what is to be warmed is 16-byte aligned and a multiple of 16 bytes");
+  const Warm w = {warm_bytes ? static_cast<const char*>(warm) : nullptr, warm_bytes};
   const bool ln = gamma != nullptr;
   if (M <= 8)
-    return ln ? launch<1, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream)
-              : launch<1, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream);
-  return ln ? launch<2, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream)
-            : launch<2, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, stream);
+    return ln ? launch<1, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, w, stream)
+              : launch<1, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, w, stream);
+  return ln ? launch<2, true>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, w, stream)
+            : launch<2, false>(xin, gamma, beta, eps, W, bias, residual, out, M, N, K, act, out_dtype, tail, w, stream);
 }
+
+EMBER_TIMELINE_READER(linear_decode)

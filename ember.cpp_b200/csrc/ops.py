@@ -35,13 +35,16 @@ _SIGNATURES = {
                           _c_void, _c_size, _c_void, _c_void],
     "ember_linear_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
-                            _c_int, _c_int, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void],
+                            _c_int, _c_int, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_size, _c_void],
     "ember_kv_store": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_void],
     "ember_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
                               _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
     "ember_attention_decode": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void],
+    "ember_attention_decode_ahead": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                                     _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                                     _c_int, _c_void, _c_void, _c_void],
     "ember_attention_prefill": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_attention_prefill_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
@@ -120,14 +123,24 @@ class CudaOps:
         self.decode_ctas = 4800        # blocks the decode attention aims for (about four waves of 148 SMs x 8)
         # Run a layer norm inside the following product's kernel when it can be.  Off: measured on
         # GPT-2 XL's shapes a separate norm kernel, overlapped with the product's weight fetch by
-        # programmatic dependent launch, is faster (23.8 against 30.8 microseconds a layer at 8 rows).
-        self.fuse_norm = False
+        # programmatic dependent launch, is faster (a step of 12 layers at 8 rows 0.586 against 0.683 ms
+        # with the norm's gain and bias staged beside the weights): every block of the product reads and
+        # norms all the rows again, 300 to 400 times the norm kernel's traffic from L2.
+        self.fuse_norm = os.environ.get("EMBER_FUSE_NORM", "0") == "1"
+        # A decode attention asks the next layer's rows of the cache into L2 (see `attention`).  Off: the
+        # rows then do come from L2, but the kernel's time does not change (0.5822 against 0.5820 ms a step
+        # of 12 layers): it is bound by what an SM can issue and take in, not by DRAM.
+        self.cache_ahead = os.environ.get("EMBER_CACHE_AHEAD", "0") == "1"
         # The norm that follows a sum into the residual stream can run in the tail of that sum's product
         # (few rows in bfloat16): `expect_norm` announces it, `layernorm` then finds its result ready.
         # Off: measured on GPT-2 XL's shape at batch 8 it changes nothing (0.780 against 0.782 ms a step
         # of 12 layers): the separate norm kernels already hide behind the next product's weight fetch.
         self.tail_norm = os.environ.get("EMBER_TAIL_NORM", "0") == "1"
         self._expected = None          # (gain, bias, eps, dtype) announced for the next sum
+        self._warm = None              # tensor announced by `warm` for the next product
+        # Off: the second product of a feed-forward has its weights 1 microsecond earlier with it, the step
+        # is not shorter (0.589 against 0.586 ms of 12 layers).
+        self.warm_ahead = os.environ.get("EMBER_WARM", "0") == "1"
         self._normed = None            # (stream ptr, gain ptr, bias ptr, eps, dtype, result) of the last tail norm
         self._tail_counter = None
         # Products of more than SMALL_M rows go to cuBLASLt ("lt"), as ember.cpp's own go to cuBLAS, or
@@ -201,6 +214,11 @@ class CudaOps:
         the stream in its own launch, and the `layernorm` call that follows returns that result."""
         self._expected = (w, b, float(eps), out_dtype)
 
+    def warm(self, tensor) -> None:
+        """Announces constants that a kernel soon after the next product reads (the weights of the product
+        after it).  A hint: a small product's kernel asks them into L2 while it waits for its own input."""
+        self._warm = tensor if self.warm_ahead else None
+
     def layernorm(self, x, w, b, eps, out_dtype, lazy=False):
         """Layer norm of float32 rows.  With `lazy` the caller promises to hand the result to
         `linear` and nothing else; for a few rows in bfloat16 the norm then runs inside that
@@ -220,6 +238,35 @@ class CudaOps:
         out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
         self._call("ember_layernorm", self._dense(x, "layernorm input").data_ptr(), w.data_ptr(), b.data_ptr(),
                    out.data_ptr(), rows, d, float(eps), _code(out_dtype))
+        return out
+
+    AHEAD_BYTES = 48 << 20   # rows of one layer's cache that are worth asking into L2 a layer early
+
+    TIMELINE_KERNELS = {1: "embed", 2: "layernorm", 3: "linear_decode", 4: "attention_decode", 5: "sample"}
+    TIMELINE_FILES = ("elementwise", "linear_decode", "attention_decode", "sampling")
+
+    def timeline(self):
+        """What the kernels of a library built with EMBER_TIMELINE=1 noted since the last call: a list of
+        (nanoseconds, kernel name, mark, block, blocks of the launch) sorted by time; mark 0 = the block
+        started, 1 = its wait for the kernel in front returned, 2 = it ended (3: it ended after merging
+        the partial results of a decode attention), 4 to 7 = places in between that the kernel's source
+        names.  Synchronizes with the device."""
+        import struct
+        if not hasattr(self.lib, "ember_timeline_read_elementwise"):
+            raise KernelError("this library was built without EMBER_TIMELINE=1")
+        cap, out = 1 << 18, []
+        buf = ctypes.create_string_buffer(cap * 24)
+        for name in self.TIMELINE_FILES:
+            fn = getattr(self.lib, f"ember_timeline_read_{name}")
+            fn.argtypes, fn.restype = [_c_void, ctypes.c_uint], _c_int
+            n = fn(ctypes.cast(buf, ctypes.c_void_p), cap)
+            if n < 0:
+                raise KernelError(f"timeline: reading the log of {name}.cu failed")
+            for i in range(n):
+                t, what, block, grid, _ = struct.unpack_from("<QIIII", buf, i * 24)
+                if t:
+                    out.append((t, self.TIMELINE_KERNELS.get(what >> 8, str(what >> 8)), what & 255, block, grid))
+        out.sort()
         return out
 
     def take_tokens(self, tokens, token_src, ids, vocab_size: int) -> None:
@@ -243,6 +290,7 @@ class CudaOps:
         if act not in _ACT:
             raise KernelError(f"linear: activation {act!r}")
         expected, self._expected = self._expected, None
+        warm, self._warm = self._warm, None
         if residual is not None:
             self._normed = None        # the stream changes: an earlier norm of it is stale
         norm = None
@@ -283,7 +331,9 @@ class CudaOps:
                        w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(), M, N, K, _ACT[act],
                        _code(target), None if tail is None else expected[0].data_ptr(),
                        None if tail is None else expected[1].data_ptr(), 0.0 if tail is None else expected[2],
-                       self._ptr(tail), None if tail is None else self._tail_counter.data_ptr())
+                       self._ptr(tail), None if tail is None else self._tail_counter.data_ptr(),
+                       None if warm is None else warm.data_ptr(),
+                       0 if warm is None else warm.numel() * warm.element_size() // 16 * 16)
             if tail is not None:
                 self._normed = (out.data_ptr(), expected[0].data_ptr(), expected[1].data_ptr(), expected[2], expected[3], tail)
             return out
@@ -356,10 +406,16 @@ class CudaOps:
             per_chunk = max(min(2, blocks), min(blocks, plan.T * n_heads * blocks // self.decode_ctas))
             n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
             partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
-            self._call("ember_attention_decode", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
-                       partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(),
-                       plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, blocks, plan.T, n_heads, kv_heads,
-                       head_dim, float(scale), int(window), per_chunk, 1 if store else 0)
+            # The layer that attends next from the same group of the cache reads the same rows of its own
+            # pages: while they all fit in L2 beside a layer's weights, this launch asks them there.
+            ahead = getattr(cache, "following", None) if self.cache_ahead else None
+            rows_bytes = plan.T * blocks * 64 * kv_heads * head_dim * 2 * 2
+            ahead_k, ahead_v = (ahead[0].data_ptr(), ahead[1].data_ptr()) if ahead and rows_bytes <= self.AHEAD_BYTES else (0, 0)
+            self._call("ember_attention_decode_ahead", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                       out.data_ptr(), partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(),
+                       plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, blocks,
+                       plan.T, n_heads, kv_heads, head_dim, float(scale), int(window), per_chunk, 1 if store else 0,
+                       ahead_k, ahead_v)
             return out
         if store:
             self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim)

@@ -297,6 +297,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   __shared__ u64 s_before;
   __shared__ int s_hit, s_result, s_n;
 
+  EMBER_MARK_START(kSample);
   const float* rowp = logits + (size_t)blockIdx.x * V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
@@ -446,3 +447,5 @@ EMBER_API int ember_sample(const float* logits, int* out, int rows, int V, float
   EMBER_LAUNCH_OK("sample");
   return 0;
 }
+
+EMBER_TIMELINE_READER(sampling)

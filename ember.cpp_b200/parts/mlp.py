@@ -49,6 +49,9 @@ class DenseFeedForward(FeedForward):
             self.b_down = runtime.vector(get(self.down_name + ".bias"))
 
     def forward(self, ctx, h, residual):
+        warm = getattr(ctx.ops, "warm", None)
+        if warm is not None:
+            warm(self.w_down)  # a hint: the second product's weights can be on their way during the first
         u = ctx.ops.linear(h, self.w_up, self.b_up, act=self.activation, out_dtype=ctx.dtype)
         return ctx.ops.linear(u, self.w_down, self.b_down, residual=residual)
 

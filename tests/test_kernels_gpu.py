@@ -230,6 +230,58 @@ def test_linear_with_the_norm_in_its_prologue(ops, M, N, K):
     assert torch.is_tensor(ops.layernorm(x, gw, gb, 1e-5, torch.float32, lazy=True))
 
 
+@pytest.mark.parametrize("M, N, K", [(8, 6400, 1600), (3, 100, 72), (16, 48, 4104)])
+def test_linear_few_rows_warms_what_it_is_told_to(M, N, K):
+    """A tensor announced with `warm` is asked into L2 by the next small product: the product is the
+    same bit for bit, the tensor is not changed, and the announcement is used once."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    ops = CudaOps()
+    ops.warm_ahead = True
+    a, w, bias = gen((M, K), 41, torch.bfloat16), gen((N, K), 42, torch.bfloat16, 0.1), gen((N,), 43)
+    for numel in (16, 8 * 1024 * 1024 + 24, 1600 * 6400):
+        other = torch.full((numel,), 7.0, dtype=torch.bfloat16, device="cuda")
+        plain = ops.linear(a, w, bias, act="gelu_tanh", out_dtype=torch.bfloat16)
+        ops.warm(other)
+        warmed = ops.linear(a, w, bias, act="gelu_tanh", out_dtype=torch.bfloat16)
+        assert ops._warm is None
+        torch.cuda.synchronize()
+        assert torch.equal(plain, warmed) and bool((other == 7.0).all())
+    ops.check()
+
+
+def test_timeline_of_a_step_from_an_instrumented_build(tmp_path):
+    """A library built with EMBER_TIMELINE=1 notes when the blocks of the decode kernels start, pass
+    their wait and end; the ordinary build refuses to give a timeline."""
+    import subprocess
+    import sys
+    with pytest.raises(Exception, match="EMBER_TIMELINE"):
+        from ember_cpp_b200.csrc.ops import CudaOps
+        CudaOps().timeline()
+    code = """
+import torch
+from ember_cpp_b200.csrc.ops import CudaOps
+ops = CudaOps()
+x = torch.randn(8, 320, device="cuda")
+w, b = torch.ones(320, device="cuda"), torch.zeros(320, device="cuda")
+ops.timeline()
+h = ops.layernorm(x, w, b, 1e-5, torch.bfloat16)
+y = ops.linear(h, torch.randn(96, 320, device="cuda").bfloat16(), None)
+marks = ops.timeline()
+names = {(k, m) for _, k, m, _, _ in marks}
+assert {("layernorm", 0), ("layernorm", 1), ("layernorm", 2), ("linear_decode", 0), ("linear_decode", 1),
+        ("linear_decode", 2)} <= names, names
+assert sum(1 for _, k, m, _, _ in marks if k == "linear_decode" and m == 0) == 6   # 96 / 16 tiles
+assert all(a[0] <= b[0] for a, b in zip(marks, marks[1:]))
+assert ops.timeline() == []
+print("ok")
+"""
+    import os
+    env = dict(os.environ, EMBER_TIMELINE="1")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", code], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stdout + r.stderr
+
+
 def test_linear_float32_rows_do_not_depend_on_the_batch(ops):
     """The 32-bit product adds each output element in one fixed order: a row computed alone is
     bit-identical to the same row of a large batch."""
@@ -289,10 +341,13 @@ def attention_ref(q, k, v, heads, kv_heads, hd, scale, window, start):
     return out
 
 
-def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poison=None, qkv_fn=None):
+def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poison=None, qkv_fn=None, ahead=False):
     """Stores `cached` positions per sequence in one step, then runs the step of `new` positions;
-    returns (got, want) for the second step's tokens."""
+    returns (got, want) for the second step's tokens.  ahead: the view names the storage of a layer
+    that attends next (which a kernel may warm but must not change)."""
     cache, view, slots, width, g = make_step(seqs, heads, kv_heads, hd, dtype, window, True, seed, poison)
+    if ahead:
+        view.following = (torch.full_like(view.k, 3.0), torch.full_like(view.v, 5.0))
     scale = 0.37 / math.sqrt(hd)
     tables = [cache.groups[0].table]
     data = [torch.randn(a + b, width, generator=g) for a, b in seqs]
@@ -313,6 +368,9 @@ def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poiso
     if first:
         step(first, [d[:a] for d, (a, b) in zip(data, seqs) if a > 0])
     got = step([(s, b) for s, (a, b) in zip(slots, seqs)], [d[a:] for d, (a, b) in zip(data, seqs)])
+    if ahead:
+        torch.cuda.synchronize()
+        assert bool((view.following[0] == 3.0).all()) and bool((view.following[1] == 5.0).all())
     want = []
     qw, kw = heads * hd, kv_heads * hd
     for d, (a, b) in zip(data, seqs):
@@ -335,6 +393,21 @@ def test_attention_one_token_each_over_the_cache(ops, dtype, heads, kv_heads, hd
     seqs = [(199, 1), (63, 1), (64, 1), (0, 1), (300, 1), (127, 1), (128, 1)]
     got, want = run_attention(ops, seqs, heads, kv_heads, hd, dtype, seed=hd + 1, poison=1e30)
     assert (got - want).abs().max().item() < ATOL[dtype]
+
+
+@pytest.mark.parametrize("heads, kv_heads, hd, window", [(25, 25, 64, 0), (6, 2, 32, 0), (3, 1, 80, 100)])
+def test_attention_one_token_each_warms_the_next_layers_rows(heads, kv_heads, hd, window):
+    """Asked to, the decode attention asks the same rows of the next layer's pages into L2: the same
+    output bit for bit, and that storage is not changed."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    seqs = [(199, 1), (63, 1), (64, 1), (0, 1), (300, 1), (127, 1), (128, 1)]
+    plain, warming = CudaOps(), CudaOps()
+    plain.cache_ahead, warming.cache_ahead = False, True
+    got, want = run_attention(warming, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=hd + 1, poison=1e30,
+                              ahead=True)
+    same, _ = run_attention(plain, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=hd + 1, poison=1e30)
+    assert (got - want).abs().max().item() < ATOL["bfloat16"]
+    assert torch.equal(got, same)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
