@@ -186,6 +186,7 @@ def main() -> int:
 
     def decode_run(B: int, warm: int, steps: int):
         """Prefill B prompts of prompt_len, then warm + steps decode steps; times the last `steps`."""
+        engine.capture_decode(B)   # the step's graphs for every bucket of lengths, before anything is timed
         slots = [engine.open() for _ in range(B)]
         prompts = [rng.integers(0, V, prompt_len).tolist() for _ in range(B)]
         logits = engine.step([(s, p, [prompt_len - 1]) for s, p in zip(slots, prompts)])

@@ -26,9 +26,18 @@ constexpr int kThreads = 128;
 constexpr int kUnroll = 4;          // keys a stream has in flight
 constexpr int kMaxChunkPages = 64;  // page numbers of a chunk kept in shared memory
 constexpr int kMergeAtOnce = 8;     // chunks whose partial results the merging block fetches in one batch
+static_assert(kMaxChunkPages <= kThreads, "a thread fetches at most one page number of its chunk");
 
-template <int LPK>  // lanes per key; each lane owns 8 consecutive dims
-__global__ void __launch_bounds__(kThreads, 8)
+__device__ int g_gave_up = 0;  // set when a block's wait for its bulk copies ran out
+
+// LPK: lanes per key; each lane owns 8 consecutive dims.  BULK: the chunk's keys and values come
+// into shared memory by bulk copies, a page's rows for one head each (they are contiguous), two
+// pages in flight; else by 16-byte loads into registers.  An SM has far more bytes of bulk copies
+// in flight than of loads (a burst of loads of all resident blocks drained at about 30 KB a
+// microsecond and SM, whether it came from DRAM or from L2), and the copies of a whole chunk are
+// under way before the kernel in front has finished.
+template <int LPK, bool BULK>
+__global__ void __launch_bounds__(kThreads, BULK ? 6 : 8)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ kc,
                         const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ part_ml, float* __restrict__ part_acc, int* __restrict__ counters,
@@ -44,6 +53,8 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   __shared__ float s_w[kStreams];
   __shared__ int s_last;
   __shared__ int s_pages[kMaxChunkPages];
+  extern __shared__ __align__(128) unsigned char s_stage[];  // BULK: [2 stages][K, V][kPage][hd]
+  __shared__ unsigned long long s_bar[2];                    // BULK: a stage's copies have landed
 
   // Before waiting for the kernel in front (which makes this step's q, k and v), everything that
   // does not depend on it is fetched: the step's description, which the host wrote before the
@@ -54,13 +65,25 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   const int c = blockIdx.x, h = blockIdx.y, t = blockIdx.z;
   const int s = t;
   __nv_bfloat16* o = out + ((size_t)t * n_heads + h) * hd;
-  if (seq_slot[s] < 0) {  // padding: a defined output, nothing read
+  // The step's description is three loads that do not depend on one another (the sequence's slot,
+  // the token's position, this chunk's page numbers): asked for together they are one trip to L2
+  // in front of the keys' fetch, not three.  (A block that starts late, when the kernel in front
+  // leaves an SM, has that chain on the step's critical path.)
+  const int* my_pages = pages + (size_t)s * max_blocks;
+  const bool cached_pages = pages_per_chunk <= kMaxChunkPages;  // at most one page number a thread
+  const int slot = seq_slot[s];
+  const int p = positions[t];
+  int my_page = -1;
+  if (cached_pages && (int)threadIdx.x < pages_per_chunk) {
+    const int blk = c * pages_per_chunk + threadIdx.x;
+    if (blk < max_blocks) my_page = my_pages[blk];
+  }
+  if (slot < 0) {  // padding: a defined output, nothing read
     pdl_wait();
     if (c == 0)
       for (int d = threadIdx.x; d < hd; d += kThreads) o[d] = __float2bfloat16_rn(0.f);
     return;
   }
-  const int p = positions[t];
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int chunk_keys = pages_per_chunk * kPage;
   const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
@@ -73,13 +96,12 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   const int end = min(k_store ? p : p + 1, (c + 1) * chunk_keys);
   const int kvh = h / (n_heads / kv_heads);
   const int width = (n_heads + 2 * kv_heads) * hd;
-  const int* my_pages = pages + (size_t)s * max_blocks;
-  const bool cached_pages = pages_per_chunk <= kMaxChunkPages;
-  if (cached_pages)
-    for (int i = threadIdx.x; i < pages_per_chunk; i += kThreads) {
-      const int blk = c * pages_per_chunk + i;
-      s_pages[i] = blk < max_blocks ? my_pages[blk] : -1;
-    }
+  if (cached_pages && (int)threadIdx.x < pages_per_chunk) s_pages[threadIdx.x] = my_page;
+  if (BULK && threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"((unsigned)__cvta_generic_to_shared(&s_bar[0])));
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;\n" ::"r"((unsigned)__cvta_generic_to_shared(&s_bar[1])));
+    asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+  }
   __syncthreads();
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -108,8 +130,36 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   // fetched while the kernels in front finish.  A cache that another layer stored into earlier in
   // this same step (this launch only reads it) may not be touched before the wait: kernels that
   // were launched this way can be several deep in their waits.
+  // BULK: pages of the chunk that hold keys of [begin, end), and the copy of one of them into a
+  // stage (thread 0): rows r0 to r1 of the page, K and then V, counted on the stage's barrier.
+  const int first_pg = begin / kPage, last_pg = end > begin ? (end - 1) / kPage : first_pg - 1;
+  const unsigned half_stage = (unsigned)kPage * hd * 2;  // bytes of a page's keys for one head
+  auto issue = [&](int pg, int st) {
+    const int r0 = max(begin, pg * kPage) - pg * kPage, r1 = min(end, (pg + 1) * kPage) - pg * kPage;
+    const int page = cached_pages ? s_pages[pg - c * pages_per_chunk] : my_pages[pg];
+    const unsigned bytes = page >= 0 ? (unsigned)(r1 - r0) * hd * 2 : 0u;
+    const unsigned bar = (unsigned)__cvta_generic_to_shared(&s_bar[st]);
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(2u * bytes) : "memory");
+    if (bytes) {
+      const size_t row = (((size_t)page * kv_heads + kvh) * kPage + r0) * hd;
+      const unsigned dst = (unsigned)__cvta_generic_to_shared(s_stage) + (unsigned)st * 2u * half_stage + (unsigned)r0 * hd * 2;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+                   "l"(kc + row), "r"(bytes), "r"(bar)
+                   : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst + half_stage),
+                   "l"(vc + row), "r"(bytes), "r"(bar)
+                   : "memory");
+    }
+  };
   if (!k_store) pdl_wait();
-  fetch(begin);
+  if (BULK) {
+    if (threadIdx.x == 0) {
+      if (first_pg <= last_pg) issue(first_pg, 0);
+      if (first_pg + 1 <= last_pg) issue(first_pg + 1, 1);
+    }
+  } else {
+    fetch(begin);
+  }
   if (ahead_k && h % (n_heads / kv_heads) == 0) {
     // The cache of the layer that attends next holds the same rows in the same pages.  Asking them
     // into L2 now, a layer early, turns that layer's trips to DRAM into trips to L2.  One bulk
@@ -141,7 +191,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
     // launch; blocks of other heads of the same group write the same bytes; nothing in this launch
     // reads the row), and into stream 0 of this block.
     const __nv_bfloat16* src = qkv + (size_t)t * width + (size_t)(n_heads + kvh) * hd;
-    const int page = my_pages[p / kPage];
+    const int page = cached_pages ? s_pages[p / kPage - c * pages_per_chunk] : my_pages[p / kPage];
     if (page >= 0) {
       const size_t dst = (((size_t)page * kv_heads + kvh) * kPage + (p % kPage)) * hd;
       const int vecs = hd / 8;
@@ -166,9 +216,56 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   // Every lane of a warp makes the same number of trips (the shuffles name all 32 lanes).  A trip
   // takes kUnroll keys per stream: their loads are issued together, then they are folded into the
   // stream's running softmax one after the other.
-  for (int j0 = begin; j0 < end; j0 += kUnroll * kStreams) {
-    if (j0 != begin) fetch(j0);
-    fold_keys<LPK, kUnroll>(kraw, vraw, have, q, scale, m, l, acc);
+  if (BULK) {
+    constexpr int kPerStream = kPage / kStreams;                // keys of a page that a stream takes
+    constexpr int kTogether = kPerStream < 4 ? kPerStream : 4;  // ... folded together
+    for (int pg = first_pg, it = 0; pg <= last_pg; ++pg, ++it) {
+      const int st = it & 1;
+      {  // the stage's copies have landed (a wait with a limit: a copy that never completes must not hang the GPU)
+        const unsigned bar = (unsigned)__cvta_generic_to_shared(&s_bar[st]);
+        const unsigned parity = (unsigned)(it >> 1) & 1u;
+        unsigned done = 0;
+        for (unsigned spin = 0; !done && spin < (1u << 24); ++spin)
+          asm volatile(
+              "{\n.reg .pred p;\n"
+              "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+              "selp.u32 %0, 1, 0, p;\n}\n"
+              : "=r"(done)
+              : "r"(bar), "r"(parity)
+              : "memory");
+        if (!done) g_gave_up = 1;  // the results of this launch are not valid; the host asks with ember_attention_decode_status
+      }
+      const int page = cached_pages ? s_pages[pg - c * pages_per_chunk] : my_pages[pg];
+      const unsigned char* ks = s_stage + (size_t)st * 2 * half_stage;
+      const unsigned char* vs = ks + half_stage;
+#pragma unroll
+      for (int b = 0; b < kPerStream / kTogether; ++b) {
+        uint4 kr[kTogether], vr[kTogether];
+        bool hv[kTogether];
+#pragma unroll
+        for (int u = 0; u < kTogether; ++u) {
+          const int r = sid + (b * kTogether + u) * kStreams;
+          const int j = pg * kPage + r;
+          hv[u] = page >= 0 && j >= begin && j < end;
+          kr[u] = make_uint4(0, 0, 0, 0);
+          vr[u] = make_uint4(0, 0, 0, 0);
+          if (dims && hv[u]) {
+            kr[u] = *reinterpret_cast<const uint4*>(ks + ((size_t)r * hd + sub * 8) * 2);
+            vr[u] = *reinterpret_cast<const uint4*>(vs + ((size_t)r * hd + sub * 8) * 2);
+          }
+        }
+        fold_keys<LPK, kTogether>(kr, vr, hv, q, scale, m, l, acc);
+      }
+      if (pg + 2 <= last_pg) {  // the stage is read: its next page can come
+        __syncthreads();
+        if (threadIdx.x == 0) issue(pg + 2, st);
+      }
+    }
+  } else {
+    for (int j0 = begin; j0 < end; j0 += kUnroll * kStreams) {
+      if (j0 != begin) fetch(j0);
+      fold_keys<LPK, kUnroll>(kraw, vraw, have, q, scale, m, l, acc);
+    }
   }
   if (own && warp == 0) {  // all of warp 0: its shuffles are whole-warp
     const uint4 ok[1] = {own_k}, ov[1] = {own_v};
@@ -292,6 +389,18 @@ EMBER_API size_t ember_attention_decode_partials(int T, int n_heads, int hd, int
 // partials: ember_attention_decode_partials(...) floats of scratch, contents irrelevant.
 // counters: T * n_heads ints of scratch that are zero before the first call; every call leaves
 // them zero.  Calls that share scratch must not overlap on the device.
+// 0, or 1 if a block of some launch since the last call gave up waiting for its bulk copies (its
+// results are not valid); the flag is cleared.  Synchronizes with the device.
+EMBER_API int ember_attention_decode_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_gave_up, sizeof(int)) != cudaSuccess) return 0;
+  if (v) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_gave_up, &zero, sizeof(int));
+  }
+  return v;
+}
+
 // ahead_k, ahead_v: null, or the key and value pages of the layer that attends next (same shape, same
 // page table): the rows this call reads are asked into L2 for that layer.
 EMBER_API int ember_attention_decode_ahead(const void* qkv, const void* kc, const void* vc, void* out, float* partials,
@@ -314,19 +423,41 @@ EMBER_API int ember_attention_decode_ahead(const void* qkv, const void* kc, cons
   float* part_acc = part_ml + items * n_chunks * 2;
   dim3 grid(n_chunks, n_heads, T);
   cudaError_t e;
+  // Bulk copies for head sizes up to 128 (two stages of a page's keys and values: 512 bytes per
+  // value of the head size); EMBER_DECODE_BULK=0 in the environment takes the loads (for measurements).
+  static const bool bulk_allowed = [] {
+    const char* v = getenv("EMBER_DECODE_BULK");
+    return !(v && v[0] == '0');
+  }();
+  const bool bulk = bulk_allowed && hd <= 128;
+  const size_t smem = bulk ? (size_t)4 * kPage * hd * 2 : 0;
 #define EMBER_DECODE(LPK)                                                                                           \
-  e = launch_pdl(attention_decode_kernel<LPK>, grid, dim3(kThreads), 0, stream, (const __nv_bfloat16*)qkv,          \
+  if (bulk) {                                                                                                       \
+    static size_t configured = 0;                                                                                   \
+    if (smem > 48 * 1024 && smem > configured) {                                                                    \
+      e = cudaFuncSetAttribute(attention_decode_kernel<LPK, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                               (int)smem);                                                                          \
+      if (e != cudaSuccess) return ember_fail("attention_decode: %s", cudaGetErrorString(e));                       \
+      configured = smem;                                                                                            \
+    }                                                                                                               \
+    e = launch_pdl(attention_decode_kernel<LPK, true>, grid, dim3(kThreads), smem, stream, EMBER_DECODE_ARGS);      \
+  } else {                                                                                                          \
+    e = launch_pdl(attention_decode_kernel<LPK, false>, grid, dim3(kThreads), 0, stream, EMBER_DECODE_ARGS);        \
+  }
+#define EMBER_DECODE_ARGS                                                                                           \
+  (const __nv_bfloat16*)qkv,                                                                                        \
                  (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, part_ml, part_acc, counters, \
                  positions, token_seq, seq_slot, pages, max_blocks, n_heads, kv_heads, hd, scale, window,           \
                  pages_per_chunk, n_chunks, store_kv ? (__nv_bfloat16*)kc : (__nv_bfloat16*)nullptr,                 \
                  store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr, (const __nv_bfloat16*)ahead_k,                \
-                 (const __nv_bfloat16*)ahead_v)
-  if (hd <= 16) EMBER_DECODE(2);
-  else if (hd <= 32) EMBER_DECODE(4);
-  else if (hd <= 64) EMBER_DECODE(8);
-  else if (hd <= 128) EMBER_DECODE(16);
-  else EMBER_DECODE(32);
+                 (const __nv_bfloat16*)ahead_v
+  if (hd <= 16) { EMBER_DECODE(2) }
+  else if (hd <= 32) { EMBER_DECODE(4) }
+  else if (hd <= 64) { EMBER_DECODE(8) }
+  else if (hd <= 128) { EMBER_DECODE(16) }
+  else e = launch_pdl(attention_decode_kernel<32, false>, grid, dim3(kThreads), 0, stream, EMBER_DECODE_ARGS);
 #undef EMBER_DECODE
+#undef EMBER_DECODE_ARGS
   if (e != cudaSuccess) return ember_fail("attention_decode: %s", cudaGetErrorString(e));
   return 0;
 }

@@ -218,11 +218,38 @@ class Engine:
         return self.model.forward(ctx)
 
     # ------------------------------------------------------------------ one token each, as a replayed graph
+    def _length_bucket(self, pages: int) -> int:
+        """The pages of the longest sequence, rounded up to 4, 6, 8, 12, 16, 24, ... (or to all the cache
+        gives a sequence): a captured graph's launches are sized for that many, so that the attention
+        can cut a short context and a long one differently."""
+        top = self.cache.max_blocks
+        size = 4
+        while size < pages and size < top:
+            size = size * 3 // 2 if (size & (size - 1)) == 0 else size * 4 // 3
+        return min(size, top)
+
+    def capture_decode(self, batch: int) -> int:
+        """Captures the one-token step's graphs for batches of up to `batch` sequences (its bucket) at every
+        bucket of lengths, with padding in place of sequences, so that no later step pays for a capture.
+        Returns how many graphs were captured."""
+        bucket = 1
+        while bucket < batch:
+            bucket *= 2
+        made, pages = 0, 0
+        while pages < self.cache.max_blocks:
+            pages = self._length_bucket(pages + 1)
+            if (bucket, pages) not in self._graphs:
+                tables = [g.table for g in self.cache.groups]
+                host = build_step([], self.cache.lengths, tables, self.cache.max_blocks, bucket, True, None)
+                self._graphs[(bucket, pages)] = _DecodeGraph(self, host, pages)
+                made += 1
+        return made
+
     def _graph_step(self, entries, borrow: bool, device_tokens=None):
         """A step in which every sequence brings one token runs as a CUDA graph captured once per
-        batch-size bucket (ember.cpp captures its one-token step once and replays it with
-        [token, pos, kv_row] in device memory, graph_ir.cpp:4306-4373).  The batch is padded to the
-        bucket with sequences of slot -1; the description of the step is the only thing that
+        bucket of batch sizes and of lengths (ember.cpp captures its one-token step once and replays
+        it with [token, pos, kv_row] in device memory, graph_ir.cpp:4306-4373).  The batch is padded
+        to the bucket with sequences of slot -1; the description of the step is the only thing that
         changes between replays."""
         n_real = len(entries)
         bucket = 1
@@ -230,6 +257,7 @@ class Engine:
             bucket *= 2
         host, shape = self.prepare(entries, pad_to=bucket, want_all=True, device_tokens=device_tokens)
         ids = None if device_tokens is None else device_tokens[0]
+        pages = self._length_bucket(-(-host.max_end // 64))
         g = None
         if self.decode_programs and bucket <= 8:
             g = self._programs.get(bucket)
@@ -240,9 +268,9 @@ class Engine:
                     self.decode_programs = False     # some part asks for what the kernel does not do
                     g = None
         if g is None:
-            g = self._graphs.get(bucket)
+            g = self._graphs.get((bucket, pages))
             if g is None:
-                g = self._graphs[bucket] = _DecodeGraph(self, host)
+                g = self._graphs[(bucket, pages)] = _DecodeGraph(self, host, pages)
         g.replay(self, host, ids)
         self._account(host, shape)
         rows = [i for i, (_, _, want) in enumerate(entries) for _ in want]
@@ -310,13 +338,13 @@ class _DecodeProgramStep:
 
 
 class _DecodeGraph:
-    def __init__(self, engine: Engine, host):
+    def __init__(self, engine: Engine, host, pages: int):
         dev = engine.runtime.device
         self.buffer = torch.zeros(host.packed.shape[0], dtype=torch.int32, device=dev)
         self.staging = _Staging(dev)
         self.size = host.packed.shape[0]
-        # launches are sized for the longest sequence the cache can hold, lengths come from the buffer
-        sized = dataclasses.replace(host, max_end=engine.cache.max_blocks * 64)
+        # launches are sized for sequences of up to `pages` pages, lengths come from the buffer
+        sized = dataclasses.replace(host, max_end=pages * 64)
         self.plan = StepPlan(sized, self.buffer)
         engine._stage(self.staging, host, self.buffer)
         if dev.type != "cuda":
