@@ -224,17 +224,6 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
     for (int i = threadIdx.x; i < 16 * tail; i += kWarps * 32)
       wt[(i / tail) * ldw + (k_hi - k_lo) + i % tail] = __float2bfloat16_rn(0.f);
   }
-  if (warm.at && warp == 1) {
-    // A product whose blocks cannot be resident beside this one's (shared memory) starts to stream
-    // its weights only when these blocks leave.  Asked into L2 now, they come from there.
-    constexpr unsigned kPiece = 8192;
-    const unsigned long long share = ((warm.bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
-    const unsigned long long lo = share * blockIdx.x, hi = min(warm.bytes, lo + share);
-    for (unsigned long long at = lo + (unsigned long long)lane * kPiece; at < hi; at += 32ull * kPiece) {
-      const unsigned n = (unsigned)min((unsigned long long)kPiece, hi - at);
-      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(warm.at + at), "r"(n) : "memory");
-    }
-  }
   pdl_trigger();
   // the element of the output tile that this thread finishes (block 0 of the cluster only); its
   // bias is a constant of the model and is fetched before the wait (in a decode step it comes from
@@ -243,6 +232,27 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   const int e_n = row0 + e_r;
   const bool e_ok = rank == 0 && threadIdx.x < kTile && e_m < M && e_n < N;
   const float e_bias = (e_ok && bias) ? bias[e_n] : 0.f;
+  if (warm.at && warp == 1) {
+    // A product whose blocks cannot be resident beside this one's (shared memory) starts to stream
+    // its weights only when these blocks leave.  Asked into L2 once this block's own weights have
+    // landed (they are needed first, and DRAM is idle after them), they come from there.
+    unsigned done = 0;
+    for (unsigned spin = 0; !done && spin < (1u << 24); ++spin)
+      asm volatile(
+          "{\n.reg .pred p;\n"
+          "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n"
+          "selp.u32 %0, 1, 0, p;\n}\n"
+          : "=r"(done)
+          : "r"(bar)
+          : "memory");
+    constexpr unsigned kPiece = 8192;
+    const unsigned long long share = ((warm.bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+    const unsigned long long lo = share * blockIdx.x, hi = min(warm.bytes, lo + share);
+    for (unsigned long long at = lo + (unsigned long long)lane * kPiece; at < hi; at += 32ull * kPiece) {
+      const unsigned n = (unsigned)min((unsigned long long)kPiece, hi - at);
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(warm.at + at), "r"(n) : "memory");
+    }
+  }
   pdl_wait();
   EMBER_MARK(kLinearDecode, kDependency);
 

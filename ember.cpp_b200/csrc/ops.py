@@ -139,9 +139,10 @@ class CudaOps:
         self.tail_norm = os.environ.get("EMBER_TAIL_NORM", "0") == "1"
         self._expected = None          # (gain, bias, eps, dtype) announced for the next sum
         self._warm = None              # tensor announced by `warm` for the next product
-        # Off: the second product of a feed-forward has its weights 1 microsecond earlier with it, the step
-        # is not shorter (0.589 against 0.586 ms of 12 layers).
-        self.warm_ahead = os.environ.get("EMBER_WARM", "0") == "1"
+        # The second product of a feed-forward has its weights landed about a microsecond earlier with it
+        # (its blocks cannot be resident beside the first product's); a step of 12 layers 0.519 against
+        # 0.521 ms.  Warming the next block's first weights during that second product as well gained nothing.
+        self.warm_ahead = os.environ.get("EMBER_WARM", "1") == "1"
         self._normed = None            # (stream ptr, gain ptr, bias ptr, eps, dtype, result) of the last tail norm
         self._tail_counter = None
         # Products of more than SMALL_M rows go to cuBLASLt ("lt"), as ember.cpp's own go to cuBLAS, or
@@ -218,7 +219,8 @@ class CudaOps:
     def warm(self, tensor) -> None:
         """Announces constants that a kernel soon after the next product reads (the weights of the product
         after it).  A hint: a small product's kernel asks them into L2 while it waits for its own input."""
-        self._warm = tensor if self.warm_ahead else None
+        fits = tensor is not None and tensor.numel() * tensor.element_size() <= self.AHEAD_BYTES
+        self._warm = tensor if self.warm_ahead and fits else None
 
     def layernorm(self, x, w, b, eps, out_dtype, lazy=False):
         """Layer norm of float32 rows.  With `lazy` the caller promises to hand the result to
