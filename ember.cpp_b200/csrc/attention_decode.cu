@@ -184,7 +184,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
   float2 q[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) q[i] = make_float2(0.f, 0.f);
-  if (dims) unpack8(*reinterpret_cast<const uint4*>(qkv + (size_t)t * width + (size_t)h * hd + sub * 8), q);
+  if (dims) unpack8(__ldcg(reinterpret_cast<const uint4*>(qkv + (size_t)t * width + (size_t)h * hd + sub * 8)), q);
   uint4 own_k = make_uint4(0, 0, 0, 0), own_v = make_uint4(0, 0, 0, 0);
   if (own) {
     // The token's own key and value: from the step's activations into the cache (no separate
@@ -198,13 +198,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat
       for (int i = threadIdx.x; i < 2 * vecs; i += kThreads) {
         const bool is_v = i >= vecs;
         const int j = (is_v ? i - vecs : i) * 8;
-        const uint4 val = *reinterpret_cast<const uint4*>(src + (is_v ? kv_heads * hd : 0) + j);
+        const uint4 val = __ldcg(reinterpret_cast<const uint4*>(src + (is_v ? kv_heads * hd : 0) + j));
         *reinterpret_cast<uint4*>((is_v ? v_store : k_store) + dst + j) = val;
       }
     }
     if (sid == 0 && dims) {
-      own_k = *reinterpret_cast<const uint4*>(src + sub * 8);
-      own_v = *reinterpret_cast<const uint4*>(src + kv_heads * hd + sub * 8);
+      own_k = __ldcg(reinterpret_cast<const uint4*>(src + sub * 8));
+      own_v = __ldcg(reinterpret_cast<const uint4*>(src + kv_heads * hd + sub * 8));
     }
   }
 

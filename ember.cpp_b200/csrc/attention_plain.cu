@@ -34,8 +34,8 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T
   for (int i = threadIdx.x * kVec; i < kv_width; i += blockDim.x * kVec) {
     const int h = i / hd, d = i % hd;
     const size_t dst = (((size_t)page * kv_heads + h) * kPage + (p % kPage)) * hd + d;
-    const uint4 k = *reinterpret_cast<const uint4*>(src + i);
-    const uint4 v = *reinterpret_cast<const uint4*>(src + kv_width + i);
+    const uint4 k = __ldcg(reinterpret_cast<const uint4*>(src + i));
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + kv_width + i));
     *reinterpret_cast<uint4*>(kc + dst) = k;
     *reinterpret_cast<uint4*>(vc + dst) = v;
   }

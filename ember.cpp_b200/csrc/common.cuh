@@ -74,7 +74,14 @@ __device__ __forceinline__ float apply_act(float v, int act) {
 // before it in the stream is still running; it must call pdl_wait() before it reads anything
 // that kernel wrote and before it writes anything at all.  pdl_trigger() lets the kernel after
 // this one begin early in the same way.  In a kernel that was launched the ordinary way both are
-// no-ops.
+// no-ops.  What the kernel before wrote must not be read through the read-only data path
+// (`ld.global.nc`, which the compiler may choose for a plain load through a const __restrict__
+// pointer): that path is only right for data that does not change during the kernel's life, and
+// this kernel's life begins before its producer's ends.  Such data is read with `__ldcg` (L2), by
+// TMA, or with an explicit `ld.global.ca` where blocks of one SM share it (L1 is made coherent
+// between dependent grids; the read-only path is not).  Seen once: a decode attention that moved
+// its keys by TMA, so that nothing swept L1 any more, read q through the read-only path and got
+// an earlier step's values in a replayed graph.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 

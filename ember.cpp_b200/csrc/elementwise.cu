@@ -70,6 +70,8 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float 
   d2[1] = __floats2bfloat162_rn(c, d);
 }
 
+// The rows were written by the kernel in front, during this kernel's life (programmatic dependent
+// launch): they are read with loads that go to L2 (`__ldcg`), never through the read-only data path.
 // EARLY: the gain and the bias (constants of the model; in a decode step each layer's come from
 // DRAM) are fetched into registers before the kernel in front is waited for, so that they are
 // not a second trip to memory after the row's statistics.  Costs registers: for a few rows only.
@@ -104,7 +106,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 #pragma unroll
     for (int j = 0; j < kRowVecs; ++j) {
       const int i = lane + 32 * j;
-      v[j] = i < nv ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      v[j] = i < nv ? __ldcg(r4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
       s += (v[j].x + v[j].y) + (v[j].z + v[j].w);
     }
     const float mean = warp_sum(s) / (float)d;
@@ -132,16 +134,16 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
     return;
   }
   float s = 0.f;
-  for (int i = lane; i < d; i += 32) s += r[i];
+  for (int i = lane; i < d; i += 32) s += __ldcg(r + i);
   const float mean = warp_sum(s) / (float)d;
   float q = 0.f;
   for (int i = lane; i < d; i += 32) {
-    const float c = r[i] - mean;
+    const float c = __ldcg(r + i) - mean;
     q += c * c;
   }
   const float var = warp_sum(q) / (float)d;
   const float inv = 1.0f / sqrtf(var + eps);
-  for (int i = lane; i < d; i += 32) o[i] = from_float<OutT>((r[i] - mean) * inv * w[i] + b[i]);
+  for (int i = lane; i < d; i += 32) o[i] = from_float<OutT>((__ldcg(r + i) - mean) * inv * w[i] + b[i]);
 }
 
 EMBER_API int ember_layernorm(const float* x, const float* w, const float* b, void* out, int rows, int d, float eps,

@@ -25,7 +25,10 @@
 // The kernel is launched with programmatic stream serialization: the weight copies are issued
 // first, and only then does it wait for the kernel before it (griddepcontrol.wait), so that
 // weights stream while the producer of X is still finishing.  Nothing is written to global memory
-// before the wait.
+// before the wait.  What that producer wrote (X, the residual) is read with loads that go to L2
+// (`__ldcg`) or explicitly through L1 (`ld.global.ca`), never with plain loads that the compiler
+// may send through the read-only data path: this kernel's life began before the producer's ended,
+// and that path can hold what was there before.
 //
 // Tail norm: when the caller says that the sum this product adds into the residual stream is
 // normed next, the block that finishes last (a ticket from an atomic counter, which it sets back to
@@ -52,6 +55,14 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
 }
 
 __device__ int g_gave_up = 0;  // set when a block's wait for its weight copies ran out
+
+// 16 bytes of what the kernel in front wrote, through L1 (blocks of one SM read the same rows) but
+// never through the read-only data path.
+__device__ __forceinline__ uint4 ld_ca(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 
 constexpr int kWarps = 8;
 constexpr int kRowVecs = 16;  // float4 per lane of a row held in registers (K <= 2048)
@@ -256,7 +267,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
   pdl_wait();
   EMBER_MARK(kLinearDecode, kDependency);
 
-  const float e_res = (e_ok && residual) ? residual[(size_t)e_m * N + e_n] : 0.f;
+  const float e_res = (e_ok && residual) ? __ldcg(residual + (size_t)e_m * N + e_n) : 0.f;
 
   if (LN) {
     const float* x = static_cast<const float*>(xin);
@@ -274,7 +285,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
 #pragma unroll
         for (int j = 0; j < kRowVecs; ++j) {
           const int i = lane + 32 * j;
-          v[j] = i < nv ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+          v[j] = i < nv ? __ldcg(r4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
 #pragma unroll
         for (int j = 0; j < kRowVecs; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
@@ -292,14 +303,14 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
         float sum = 0.f;
 #pragma unroll 8
         for (int i = lane; i < nv; i += 32) {
-          const float4 v = r4[i];
+          const float4 v = __ldcg(r4 + i);
           sum += (v.x + v.y) + (v.z + v.w);
         }
         mean = warp_sum(sum) / (float)K;
         float sq = 0.f;
 #pragma unroll 8
         for (int i = lane; i < nv; i += 32) {
-          const float4 v = r4[i];
+          const float4 v = __ldcg(r4 + i);
           const float a0 = v.x - mean, a1 = v.y - mean, a2 = v.z - mean, a3 = v.w - mean;
           sq += (a0 * a0 + a1 * a1) + (a2 * a2 + a3 * a3);
         }
@@ -345,7 +356,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
       const int k = (step_lo + warp + j * kWarps) * 32 + c * 8;
       xr[j] = make_uint4(0, 0, 0, 0);
       if (step_lo + warp + j * kWarps < step_hi && k < K && g < M)
-        xr[j] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)g * K + k);
+        xr[j] = ld_ca(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)g * K + k));
     }
     wait_for_weights();
 #pragma unroll
@@ -371,8 +382,8 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
       const int k = (step_lo + warp + j * kWarps) * 32 + c * 8;
       xa[j] = xb[j] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (step_lo + warp + j * kWarps < step_hi && k < K && g < M) {
-        xa[j] = *reinterpret_cast<const float4*>(x + (size_t)g * K + k);
-        xb[j] = *reinterpret_cast<const float4*>(x + (size_t)g * K + k + 4);
+        xa[j] = __ldcg(reinterpret_cast<const float4*>(x + (size_t)g * K + k));
+        xb[j] = __ldcg(reinterpret_cast<const float4*>(x + (size_t)g * K + k + 4));
       }
     }
     wait_for_weights();  // and for the gain and bias; its barrier also publishes the statistics
@@ -413,7 +424,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
         if (ok && m < M) {
           if (LN) {
             const float* r = static_cast<const float*>(xin) + (size_t)m * K + k;
-            const float4 v0 = *reinterpret_cast<const float4*>(r), v1 = *reinterpret_cast<const float4*>(r + 4);
+            const float4 v0 = __ldcg(reinterpret_cast<const float4*>(r)), v1 = __ldcg(reinterpret_cast<const float4*>(r + 4));
             const float* gs = gain_s + (k - k_lo);
             const float* bs = gs + (k_hi - k_lo);
             const float4 g0 = *reinterpret_cast<const float4*>(gs), g1 = *reinterpret_cast<const float4*>(gs + 4);
@@ -424,7 +435,7 @@ linear_decode_kernel(const void* __restrict__ xin, const float* __restrict__ gam
             b.z = pack2((v1.x - mean) * inv * g1.x + b1.x, (v1.y - mean) * inv * g1.y + b1.y);
             b.w = pack2((v1.z - mean) * inv * g1.z + b1.z, (v1.w - mean) * inv * g1.w + b1.w);
           } else {
-            b = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)m * K + k);
+            b = __ldcg(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(xin) + (size_t)m * K + k));
           }
         }
         mma_bf16(acc[t], a_lo.x, a_hi.x, a_lo.y, a_hi.y, b.x, b.y);

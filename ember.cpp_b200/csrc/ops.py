@@ -45,6 +45,9 @@ _SIGNATURES = {
     "ember_attention_decode_ahead": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
                                      _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                                      _c_int, _c_void, _c_void, _c_void],
+    "ember_attention_decode_mma": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                                   _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                                   _c_int, _c_int, _c_void],
     "ember_attention_prefill": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_attention_prefill_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
@@ -102,7 +105,8 @@ def load_library() -> ctypes.CDLL:
         getattr(lib, name).restype = _c_int
     lib.ember_decode_program_run.argtypes = [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void]
     lib.ember_decode_program_run.restype = _c_int
-    for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status"):
+    for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status",
+                 "ember_attention_decode_mma_status"):
         getattr(lib, name).argtypes = []
         getattr(lib, name).restype = _c_int
     lib._path = path
@@ -120,7 +124,6 @@ class CudaOps:
         self._counters = None          # ... and its per-(token, head) counters, zero between calls
         self._retired = []             # outgrown scratch stays alive: captured graphs may still name it
         self.launches = 0
-        self.decode_ctas = 4800        # blocks the decode attention aims for (about four waves of 148 SMs x 8)
         self.decode_slots = 6 * torch.cuda.get_device_properties(0).multi_processor_count  # ... that are resident at once
         # Run a layer norm inside the following product's kernel when it can be.  Off: measured on
         # GPT-2 XL's shapes a separate norm kernel, overlapped with the product's weight fetch by
@@ -132,6 +135,9 @@ class CudaOps:
         # rows then do come from L2, but the kernel's time does not change (0.5822 against 0.5820 ms a step
         # of 12 layers): it is bound by what an SM can issue and take in, not by DRAM.
         self.cache_ahead = os.environ.get("EMBER_CACHE_AHEAD", "0") == "1"
+        # Decode attention on the tensor cores where that kernel has an instantiation (head size 64 or 128,
+        # up to 8 query heads to a key/value head); EMBER_DECODE_MMA=0 takes the other kernel (for measurements).
+        self.decode_mma = os.environ.get("EMBER_DECODE_MMA", "1") == "1"
         # The norm that follows a sum into the residual stream can run in the tail of that sum's product
         # (few rows in bfloat16): `expect_norm` announces it, `layernorm` then finds its result ready.
         # Off: measured on GPT-2 XL's shape at batch 8 it changes nothing (0.780 against 0.782 ms a step
@@ -246,7 +252,7 @@ class CudaOps:
     AHEAD_BYTES = 48 << 20   # rows of one layer's cache that are worth asking into L2 a layer early
 
     TIMELINE_KERNELS = {1: "embed", 2: "layernorm", 3: "linear_decode", 4: "attention_decode", 5: "sample"}
-    TIMELINE_FILES = ("elementwise", "linear_decode", "attention_decode", "sampling")
+    TIMELINE_FILES = ("elementwise", "linear_decode", "attention_decode", "attention_decode_mma", "sampling")
 
     def timeline(self):
         """What the kernels of a library built with EMBER_TIMELINE=1 noted since the last call: a list of
@@ -375,7 +381,7 @@ class CudaOps:
         synchronized with the device (it has just read a step's results)."""
         if self.lib.ember_linear_decode_status():
             raise KernelError("linear_decode: a block gave up waiting for its weight copies; the results of that launch are not valid")
-        if self.lib.ember_attention_decode_status():
+        if self.lib.ember_attention_decode_status() or self.lib.ember_attention_decode_mma_status():
             raise KernelError("attention_decode: a block gave up waiting for its copies of keys and values; the results of that launch are not valid")
         code = self.lib.ember_tc_status()
         if code:
@@ -406,16 +412,26 @@ class CudaOps:
         pages = plan.pages[cache.group_index]
         if qkv.dtype == torch.bfloat16 and plan.all_single:
             blocks = min(plan.max_blocks, max(1, -(-plan.max_end // 64)))
-            # at least two pages a chunk (a block's fixed costs are then shared by 128 keys), more while
-            # the launch still has several waves of blocks
-            per_chunk = max(min(2, blocks), min(blocks, plan.T * n_heads * blocks // self.decode_ctas))
-            pairs = plan.T * n_heads
-            if pairs * -(-blocks // per_chunk) > self.decode_slots >= pairs:
-                # longer chunks, so that all blocks are resident at once: a block that waits for an SM
-                # starts its copies late (a step of 12 layers at a context of 900 to 1,024: 0.557 against 0.593 ms)
-                per_chunk = max(per_chunk, -(-blocks // (self.decode_slots // pairs)))
+            # The context is cut into chunks for separate blocks so that the launch fills the chip once: as
+            # many chunks as resident blocks per (token, head) pair allow, at least two pages each (a block's
+            # fixed costs are then shared by 128 keys).  Pairs that fill the chip by themselves are not cut:
+            # their blocks write the output directly, with no partial results to merge.  (A block that waits
+            # for an SM starts its copies late: a step of 12 layers at batch 8 and a context of 900 to 1,024
+            # 0.557 against 0.593 ms.)
+            mma = self.decode_mma and head_dim in (64, 128) and n_heads // kv_heads <= 8
+            pairs = plan.T * (kv_heads if mma else n_heads)   # the tensor-core kernel takes a group of heads a block
+            n_chunks = max(1, min(self.decode_slots // pairs, -(-blocks // 2)))
+            per_chunk = -(-blocks // n_chunks)
             n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
             partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
+            if self.decode_mma:
+                rc = self._call("ember_attention_decode_mma", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                                out.data_ptr(), partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(),
+                                plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks,
+                                blocks, cache.k.shape[0], plan.T, n_heads, kv_heads, head_dim, float(scale), int(window),
+                                per_chunk, 1 if store else 0, allow=(2,))
+                if rc == 0:
+                    return out
             # The layer that attends next from the same group of the cache reads the same rows of its own
             # pages: while they all fit in L2 beside a layer's weights, this launch asks them there.
             ahead = getattr(cache, "following", None) if self.cache_ahead else None
