@@ -395,6 +395,27 @@ def test_attention_one_token_each_over_the_cache(ops, dtype, heads, kv_heads, hd
     assert (got - want).abs().max().item() < ATOL[dtype]
 
 
+@pytest.mark.parametrize("heads, kv_heads, hd, window", [(25, 25, 64, 0), (16, 2, 64, 0), (4, 2, 128, 0), (8, 8, 64, 150),
+                                                        (18, 2, 64, 0)])
+def test_attention_one_token_each_on_the_tensor_cores(heads, kv_heads, hd, window):
+    """The decode attention that runs its products on the tensor cores against the reference and against
+    the kernel it replaces, with so many sequences that a block keeps a whole context (its warps refill
+    their stages page after page) and with few (the context is cut into chunks that are merged).  Nine
+    query heads to a key/value head are more than it takes as rows: the other kernel runs."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    tensor, other = CudaOps(), CudaOps()
+    tensor.decode_mma, other.decode_mma = True, False
+    many = [(n, 1) for n in (700, 1, 0, 63, 64, 65, 127, 128, 129, 300, 511, 512, 640)] * (5 if kv_heads > 2 else 40)
+    for seqs in (many, [(700, 1), (64, 1), (0, 1), (129, 1)]):
+        got, want = run_attention(tensor, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=1e30)
+        old, _ = run_attention(other, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=1e30)
+        assert (got - want).abs().max().item() < ATOL["bfloat16"]
+        assert (old - want).abs().max().item() < ATOL["bfloat16"]
+        tensor.check()
+    if heads // kv_heads > 8:
+        assert torch.equal(got, old)
+
+
 @pytest.mark.parametrize("heads, kv_heads, hd, window", [(25, 25, 64, 0), (6, 2, 32, 0), (3, 1, 80, 100)])
 def test_attention_one_token_each_warms_the_next_layers_rows(heads, kv_heads, hd, window):
     """Asked to, the decode attention asks the same rows of the next layer's pages into L2: the same
