@@ -66,7 +66,8 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             const int* __restrict__ positions, const int* __restrict__ seq_slot,
                             const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, float scale_log2,
                             int window, int pages_per_chunk, int n_chunks, __nv_bfloat16* __restrict__ k_store,
-                            __nv_bfloat16* __restrict__ v_store) {
+                            __nv_bfloat16* __restrict__ v_store, const __nv_bfloat16* __restrict__ ahead_k,
+                            const __nv_bfloat16* __restrict__ ahead_v) {
   constexpr int KS = HD / 16;                   // 16-wide steps over the head's dims
   constexpr int kBoxes = HD / 64;               // TMA boxes (64 dims wide) of a page's keys
   constexpr unsigned kBox = kPage * 128;        // bytes of a box
@@ -143,6 +144,18 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   // step may not be touched before the wait.
   if (!k_store) pdl_wait();
   if (lane == 0 && first_pg + warp <= last_pg) issue(first_pg + warp);
+  if (ahead_k) {
+    // The cache of the layer that attends next holds the same rows in the same pages: asked into L2
+    // now, a layer early, that layer's boxes (above all those a warp fetches after its first) come
+    // from there.  One bulk prefetch per page and tensor, a lane each.
+    for (int i = threadIdx.x; i < 2 * (last_pg - first_pg + 1); i += kThreads) {
+      const int page = page_of(first_pg + (i >> 1));
+      if (page >= 0) {
+        const __nv_bfloat16* at = ((i & 1) ? ahead_v : ahead_k) + ((size_t)page * kv_heads + kvh) * kPage * HD;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(at), "r"((unsigned)(kPage * HD * 2)) : "memory");
+      }
+    }
+  }
   if (k_store) pdl_wait();
   EMBER_MARK(kAttentionDecode, kDependency);
 
@@ -432,7 +445,7 @@ template <int HD>
 int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, void* kc, void* vc, void* out,
            float* part_ml, float* part_acc, int* counters, const int* positions, const int* seq_slot, const int* pages,
            int max_blocks, int n_chunks, int T, int n_heads, int kv_heads, float scale, int window, int pages_per_chunk,
-           int store_kv, cudaStream_t stream) {
+           int store_kv, const void* ahead_k, const void* ahead_v, cudaStream_t stream) {
   constexpr size_t smem = (size_t)kWarps * 2 * (HD / 64) * kPage * 128 + 1024;
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -444,7 +457,8 @@ int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, 
                              map_v, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, part_ml, part_acc, counters, positions,
                              seq_slot, pages, max_blocks, n_heads, kv_heads, scale * 1.4426950408889634f, window,
                              pages_per_chunk, n_chunks, store_kv ? (__nv_bfloat16*)kc : (__nv_bfloat16*)nullptr,
-                             store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr);
+                             store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr, (const __nv_bfloat16*)ahead_k,
+                             (const __nv_bfloat16*)ahead_v);
   if (e != cudaSuccess) return ember_fail("attention_decode_mma: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -463,14 +477,14 @@ EMBER_API int ember_attention_decode_mma_status() {
   return v;
 }
 
-// The arguments of ember_attention_decode, and n_pages, the pages that kc and vc hold.  Returns 2
+// The arguments of ember_attention_decode_ahead, and n_pages, the pages that kc and vc hold.  Returns 2
 // (and launches nothing) for what this kernel has no instantiation for: a head size other than 64
 // or 128, more than 8 query heads to a key/value head.
 EMBER_API int ember_attention_decode_mma(const void* qkv, void* kc, void* vc, void* out, float* partials, int* counters,
                                          const int* positions, const int* token_seq, const int* seq_slot,
                                          const int* pages, int max_blocks, int n_blocks, int n_pages, int T, int n_heads,
                                          int kv_heads, int hd, float scale, int window, int pages_per_chunk, int store_kv,
-                                         cudaStream_t stream) {
+                                         const void* ahead_k, const void* ahead_v, cudaStream_t stream) {
   (void)token_seq;
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0 && n_blocks > 0 && n_blocks <= max_blocks && n_pages > 0,
               "attention_decode_mma: bad sizes");
@@ -490,9 +504,9 @@ EMBER_API int ember_attention_decode_mma(const void* qkv, void* kc, void* vc, vo
   if (cache_map(kc, rows, hd, &map_k) || cache_map(vc, rows, hd, &map_v)) return 1;
   if (hd == 64)
     return launch<64>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
-                      n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, stream);
+                      n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
   return launch<128>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
-                     n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, stream);
+                     n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
 }
 
 EMBER_TIMELINE_READER(attention_decode_mma)

@@ -47,7 +47,7 @@ _SIGNATURES = {
                                      _c_int, _c_void, _c_void, _c_void],
     "ember_attention_decode_mma": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
                                    _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
-                                   _c_int, _c_int, _c_void],
+                                   _c_int, _c_int, _c_void, _c_void, _c_void],
     "ember_attention_prefill": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_attention_prefill_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
@@ -131,9 +131,11 @@ class CudaOps:
         # with the norm's gain and bias staged beside the weights): every block of the product reads and
         # norms all the rows again, 300 to 400 times the norm kernel's traffic from L2.
         self.fuse_norm = os.environ.get("EMBER_FUSE_NORM", "0") == "1"
-        # A decode attention asks the next layer's rows of the cache into L2 (see `attention`).  Off: the
-        # rows then do come from L2, but the kernel's time does not change (0.5822 against 0.5820 ms a step
-        # of 12 layers): it is bound by what an SM can issue and take in, not by DRAM.
+        # A decode attention asks the next layer's rows of the cache into L2 (see `attention`).  Off: with
+        # the kernel that loads keys into registers the step's time did not change (0.5822 against 0.5820 ms
+        # of 12 layers); with the tensor-core kernel it grew (0.538 against 0.516 ms; at a context of 900 to
+        # 1,024, 0.605 against 0.551): a layer's rows and weights together do not stay in L2 that long, and
+        # the rows are then fetched twice.
         self.cache_ahead = os.environ.get("EMBER_CACHE_AHEAD", "0") == "1"
         # Decode attention on the tensor cores where that kernel has an instantiation (head size 64 or 128,
         # up to 8 query heads to a key/value head); EMBER_DECODE_MMA=0 takes the other kernel (for measurements).
@@ -424,19 +426,19 @@ class CudaOps:
             per_chunk = -(-blocks // n_chunks)
             n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
             partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
-            if self.decode_mma:
-                rc = self._call("ember_attention_decode_mma", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
-                                out.data_ptr(), partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(),
-                                plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks,
-                                blocks, cache.k.shape[0], plan.T, n_heads, kv_heads, head_dim, float(scale), int(window),
-                                per_chunk, 1 if store else 0, allow=(2,))
-                if rc == 0:
-                    return out
             # The layer that attends next from the same group of the cache reads the same rows of its own
             # pages: while they all fit in L2 beside a layer's weights, this launch asks them there.
             ahead = getattr(cache, "following", None) if self.cache_ahead else None
             rows_bytes = plan.T * blocks * 64 * kv_heads * head_dim * 2 * 2
             ahead_k, ahead_v = (ahead[0].data_ptr(), ahead[1].data_ptr()) if ahead and rows_bytes <= self.AHEAD_BYTES else (0, 0)
+            if self.decode_mma:
+                rc = self._call("ember_attention_decode_mma", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                                out.data_ptr(), partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(),
+                                plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks,
+                                blocks, cache.k.shape[0], plan.T, n_heads, kv_heads, head_dim, float(scale), int(window),
+                                per_chunk, 1 if store else 0, ahead_k, ahead_v, allow=(2,))
+                if rc == 0:
+                    return out
             self._call("ember_attention_decode_ahead", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                        out.data_ptr(), partials.data_ptr(), counters.data_ptr(), plan.positions.data_ptr(),
                        plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, blocks,
