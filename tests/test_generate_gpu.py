@@ -178,6 +178,18 @@ def test_graph_replay_equals_launch_by_launch(tiny_folders, plains):
         out.append(run_batch(eng, seqs, (10, 1, 30))[0])
     for a, b in zip(*out):
         assert np.array_equal(a, b)
+    # graphs captured ahead of time over padding, for every bucket of lengths: the same rows, and no capture later
+    for dtype in DTYPES:
+        eng = Engine.from_folder(tiny_folders["tiny_a"], dtype=dtype, max_tokens=512)
+        made = eng.capture_decode(3)
+        assert made == len(eng._graphs) > 0 and all(batch == 4 for batch, _ in eng._graphs)
+        kept = dict(eng._graphs)
+        ahead = run_batch(eng, seqs, (10, 1, 30))[0]            # the batch shrinks to 2 and 1: those buckets are made then
+        assert all(eng._graphs[key] is graph for key, graph in kept.items())
+        late = run_batch(Engine.from_folder(tiny_folders["tiny_a"], dtype=dtype, max_tokens=512), seqs, (10, 1, 30))[0]
+        for a, b in zip(ahead, late):
+            assert np.array_equal(a, b)
+        eng.ops.check()
 
 
 @pytest.mark.parametrize("name", NAMES)

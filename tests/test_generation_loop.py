@@ -108,6 +108,32 @@ def test_steps_equal_whole_sequences(cpu_engine, plains, name):
         eng.cuda_graphs = False
 
 
+def test_one_token_steps_are_kept_per_bucket_of_batch_and_length(cpu_engine, plains):
+    """The replayed one-token step is kept per bucket of batch sizes (powers of two) and of lengths
+    (4, 6, 8, 12, 16, ... pages, at most what the cache gives a sequence); `capture_decode` makes a
+    batch size's steps ahead of time, and a step then finds its bucket made."""
+    eng, plain = cpu_engine["tiny_a"], plains["tiny_a"]
+    top = eng.cache.max_blocks
+    assert [eng._length_bucket(p) for p in (1, 4, 5, 6, 7, 9, 13, 17, 1000)] == [min(b, top) for b in (4, 4, 6, 6, 8, 12, 16, 24, 10 ** 9)]
+    eng.cuda_graphs = True
+    try:
+        eng._graphs.clear()
+        made = eng.capture_decode(3)
+        lengths = sorted({eng._length_bucket(p) for p in range(1, top + 1)})
+        assert made == len(lengths) and sorted(eng._graphs) == [(4, n) for n in lengths]
+        assert eng.capture_decode(4) == 0                      # the same bucket: nothing new
+        ids = [random_ids(40 + i, plain.vocab, 20) for i in range(3)]
+        rows, _ = run_batch(eng, ids, (12, 12, 12))            # prompts, then eight one-token steps of three sequences
+        for seq, got in zip(ids, rows):
+            assert rel_error(got, plain.logits(seq)) < 1e-5
+        assert sorted(eng._graphs) == [(4, n) for n in lengths]   # the steps found their bucket made
+        eng.cache.check()
+        assert eng.cache.slots.held == 0
+    finally:
+        eng.cuda_graphs = False
+        eng._graphs.clear()
+
+
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_generate_equals_plain(tiny_folders, plains, name):
     plain = plains[name]
