@@ -14,14 +14,19 @@
 // conflicts), requested before the kernel in front is waited for; a warp that has more than one
 // page in its chunk refills its own stage.  Every wait has a limit, after which the launch's
 // results are marked invalid (ember_attention_decode_status).
+#include <cooperative_groups.h>
+
 #include <unordered_map>
 
 #include "common.cuh"
 #include "tc_common.cuh"
 
+namespace cg = cooperative_groups;
+
 namespace {
 
 constexpr int kWarps = 2;
+constexpr int kMaxCluster = 8;      // chunks of a (token, head) that can merge through distributed shared memory
 constexpr int kThreads = kWarps * 32;
 constexpr int kMaxChunkPages = 64;  // page numbers of a chunk kept in shared memory
 constexpr int kMergeAtOnce = 8;     // chunks whose partial results the merging block fetches in one batch
@@ -58,7 +63,15 @@ __device__ __forceinline__ float weight(float m, float top) { return m == -INFIN
 // Byte offset of (row, 16-byte chunk) in a box of 64 rows of 128 bytes under the 128-byte swizzle.
 __device__ __forceinline__ unsigned swz(int row, int chunk) { return (unsigned)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
-template <int HD>
+// CLUSTER: the chunks of a (token, head) are the blocks of one thread-block cluster (plain multi-head
+// attention, at most 8 chunks): each writes its partial result into the shared memory of the block
+// that holds the token's own key and arrives at the cluster's barrier; that block waits for the
+// barrier and merges.  No scratch in global memory, no ticket, no second trip to L2.  Every block
+// of a cluster that is not padding arrives exactly once, whatever it finds to do.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
+
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads, 6)
 attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out,
@@ -76,6 +89,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   __shared__ int s_pages[kMaxChunkPages];
   __shared__ __align__(8) unsigned long long s_bar[kWarps];
   __shared__ int s_last;
+  __shared__ float s_part[CLUSTER ? kMaxCluster : 1][HD + 2];  // CLUSTER: the chunks' results, in the merging block
 
   pdl_trigger();
   const int c = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
@@ -103,7 +117,10 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int lo = window > 0 ? max(0, p - window + 1) : 0;
   const int chunk_keys = pages_per_chunk * kPage;
   const int first_chunk = lo / chunk_keys, last_chunk = p / chunk_keys;
-  if (c < first_chunk || c > last_chunk) return;
+  if (c < first_chunk || c > last_chunk) {
+    if (CLUSTER) cluster_arrive();
+    return;
+  }
   EMBER_MARK_START(kAttentionDecode);
   const bool own = k_store != nullptr && c == last_chunk;  // this block also takes the token's own key
   const int begin = max(lo, c * chunk_keys);
@@ -340,6 +357,14 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const size_t item = ((size_t)t * n_heads + h) * n_chunks + c;
     if (n_valid == 1) {
       out[((size_t)t * n_heads + h) * HD + d] = __float2bfloat16_rn(A / L);
+    } else if (CLUSTER) {  // one query head a block: row 0
+      float* mine = c == last_chunk ? &s_part[c - first_chunk][0]
+                                    : cg::this_cluster().map_shared_rank(&s_part[c - first_chunk][0], last_chunk);
+      mine[d] = A;
+      if (d == 0) {
+        mine[HD] = M;
+        mine[HD + 1] = L;
+      }
     } else {
       part_acc[item * HD + d] = A;
       if (d == 0) {
@@ -347,6 +372,26 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         part_ml[item * 2 + 1] = L;
       }
     }
+  }
+  if (CLUSTER) {
+    cluster_arrive();
+    if (n_valid == 1 || c != last_chunk) {
+      EMBER_MARK(kAttentionDecode, kEnd);
+      return;
+    }
+    cluster_wait();  // every chunk's result is in s_part
+    for (int d = threadIdx.x; d < HD; d += kThreads) {
+      float MM = -INFINITY, LL = 0.f, A = 0.f;
+      for (int k = 0; k < n_valid; ++k) MM = fmaxf(MM, s_part[k][HD]);
+      for (int k = 0; k < n_valid; ++k) {
+        const float w = weight(s_part[k][HD], MM);
+        LL += s_part[k][HD + 1] * w;
+        A += s_part[k][d] * w;
+      }
+      out[((size_t)t * n_heads + kvh) * HD + d] = __float2bfloat16_rn(A / LL);
+    }
+    EMBER_MARK(kAttentionDecode, kMerged);
+    return;
   }
   if (n_valid == 1) {
     EMBER_MARK(kAttentionDecode, kEnd);
@@ -449,16 +494,46 @@ int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, 
   constexpr size_t smem = (size_t)kWarps * 2 * (HD / 64) * kPage * 128 + 1024;
   static bool configured = false;  // per instantiation
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ember_fail("attention_decode_mma: %s", cudaGetErrorString(e));
     configured = true;
   }
-  cudaError_t e = launch_pdl(attention_decode_mma_kernel<HD>, dim3(n_chunks, kv_heads, T), dim3(kThreads), smem, stream, map_k,
-                             map_v, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)out, part_ml, part_acc, counters, positions,
-                             seq_slot, pages, max_blocks, n_heads, kv_heads, scale * 1.4426950408889634f, window,
-                             pages_per_chunk, n_chunks, store_kv ? (__nv_bfloat16*)kc : (__nv_bfloat16*)nullptr,
-                             store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr, (const __nv_bfloat16*)ahead_k,
-                             (const __nv_bfloat16*)ahead_v);
+  // EMBER_DECODE_CLUSTER=0 in the environment merges through global scratch and a ticket (for measurements)
+  static const bool cluster_allowed = [] {
+    const char* v = getenv("EMBER_DECODE_CLUSTER");
+    return !(v && v[0] == '0');
+  }();
+  const bool cluster = cluster_allowed && n_heads == kv_heads && n_chunks >= 2 && n_chunks <= kMaxCluster;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_chunks, kv_heads, T);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[0].val.programmaticStreamSerializationAllowed = pdl_allowed();
+  attrs[1].id = cudaLaunchAttributeClusterDimension;
+  attrs[1].val.clusterDim.x = n_chunks;
+  attrs[1].val.clusterDim.y = 1;
+  attrs[1].val.clusterDim.z = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = cluster ? 2 : 1;
+  const __nv_bfloat16* q = (const __nv_bfloat16*)qkv;
+  __nv_bfloat16* o = (__nv_bfloat16*)out;
+  const float scale_log2 = scale * 1.4426950408889634f;
+  __nv_bfloat16* ks = store_kv ? (__nv_bfloat16*)kc : (__nv_bfloat16*)nullptr;
+  __nv_bfloat16* vs = store_kv ? (__nv_bfloat16*)vc : (__nv_bfloat16*)nullptr;
+  const __nv_bfloat16* ak = (const __nv_bfloat16*)ahead_k;
+  const __nv_bfloat16* av = (const __nv_bfloat16*)ahead_v;
+  cudaError_t e =
+      cluster ? cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, true>, map_k, map_v, q, o, part_ml, part_acc, counters,
+                                   positions, seq_slot, pages, max_blocks, n_heads, kv_heads, scale_log2, window,
+                                   pages_per_chunk, n_chunks, ks, vs, ak, av)
+              : cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, false>, map_k, map_v, q, o, part_ml, part_acc, counters,
+                                   positions, seq_slot, pages, max_blocks, n_heads, kv_heads, scale_log2, window,
+                                   pages_per_chunk, n_chunks, ks, vs, ak, av);
   if (e != cudaSuccess) return ember_fail("attention_decode_mma: %s", cudaGetErrorString(e));
   return 0;
 }
