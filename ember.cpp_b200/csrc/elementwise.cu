@@ -74,7 +74,7 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float 
 // launch): they are read with loads that go to L2 (`__ldcg`), never through the read-only data path.
 // EARLY: the gain and the bias (constants of the model; in a decode step each layer's come from
 // DRAM) are fetched into registers before the kernel in front is waited for, so that they are
-// not a second trip to memory after the row's statistics.  Costs registers: for a few rows only.
+// not a second trip to memory after the row's statistics.  Costs registers: for a decode step's rows only.
 template <typename OutT, bool EARLY>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
                                  OutT* __restrict__ out, int rows, int d, float eps) {
@@ -149,10 +149,10 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 EMBER_API int ember_layernorm(const float* x, const float* w, const float* b, void* out, int rows, int d, float eps,
                               int out_dtype, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && d > 0, "layernorm: rows = %d, width = %d", rows, d);
-  const int warps = rows < 64 ? 1 : 4;  // a few rows: a block each, so that they run on different SMs
+  const int warps = rows <= 148 ? 1 : 4;  // a decode step's rows: a block each, so that they run on different SMs
   const int grid = (rows + warps - 1) / warps;
   cudaError_t e;
-  const bool early = rows < 64;
+  const bool early = rows <= 512;  // a decode step's rows: the gain and bias come from DRAM, once per layer
   if (out_dtype == EMBER_F32)
     e = early ? launch_pdl(layernorm_kernel<float, true>, dim3(grid), dim3(warps * 32), 0, stream, x, w, b, (float*)out, rows,
                            d, eps)
