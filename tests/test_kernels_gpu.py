@@ -341,7 +341,8 @@ def attention_ref(q, k, v, heads, kv_heads, hd, scale, window, start):
     return out
 
 
-def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poison=None, qkv_fn=None, ahead=False):
+def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poison=None, qkv_fn=None, ahead=False,
+                  store_apart=False):
     """Stores `cached` positions per sequence in one step, then runs the step of `new` positions;
     returns (got, want) for the second step's tokens.  ahead: the view names the storage of a layer
     that attends next (which a kernel may warm but must not change)."""
@@ -360,7 +361,11 @@ def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poiso
         host = build_step([(s, [0] * n, []) for s, n in entries], cache.lengths, tables, cache.max_blocks)
         plan = StepPlan(host, torch.from_numpy(host.packed).cuda())
         qkv = torch.cat(rows).cuda().contiguous()
-        out = ops.attention(qkv, view, plan, heads, kv_heads, hd, scale, window, DT[dtype], store=True)
+        if store_apart:      # as a layer does that reads a cache which another layer has stored into in this step
+            ops.kv_store(qkv, view, plan, heads, kv_heads, hd)
+            out = ops.attention(qkv, view, plan, heads, kv_heads, hd, scale, window, DT[dtype], store=False)
+        else:
+            out = ops.attention(qkv, view, plan, heads, kv_heads, hd, scale, window, DT[dtype], store=True)
         cache.commit([(s, n) for s, n in entries])
         return out
 
@@ -396,7 +401,7 @@ def test_attention_one_token_each_over_the_cache(ops, dtype, heads, kv_heads, hd
 
 
 @pytest.mark.parametrize("heads, kv_heads, hd, window", [(25, 25, 64, 0), (16, 2, 64, 0), (4, 2, 128, 0), (8, 8, 64, 150),
-                                                        (18, 2, 64, 0)])
+                                                        (18, 2, 64, 0), (3, 3, 128, 0), (2, 2, 128, 200)])
 def test_attention_one_token_each_on_the_tensor_cores(heads, kv_heads, hd, window):
     """The decode attention that runs its products on the tensor cores against the reference and against
     the kernel it replaces, with so many sequences that a block keeps a whole context (its warps refill
@@ -414,6 +419,9 @@ def test_attention_one_token_each_on_the_tensor_cores(heads, kv_heads, hd, windo
         tensor.check()
     if heads // kv_heads > 8:
         assert torch.equal(got, old)
+    # the token's own key already in the cache (stored by a launch of its own): the same output
+    apart, _ = run_attention(tensor, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=1e30, store_apart=True)
+    assert (apart - want).abs().max().item() < ATOL["bfloat16"]
 
 
 @pytest.mark.parametrize("heads, kv_heads, hd, window", [(25, 25, 64, 0), (6, 2, 32, 0), (3, 1, 80, 100)])
