@@ -134,8 +134,6 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--decode-program", action="store_true",
-                    help="run one-token steps as one launch of the persistent decode kernel instead of a graph")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each prompt before decoding starts")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -170,8 +168,7 @@ def main() -> int:
     tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=0, dtype=torch.bfloat16, device="cuda")
     log(f"random weights: {sum(t.numel() for t in tensors.values()) / 1e9:.3f} G parameters in {time.time() - t0:.1f} s")
     biggest = max(args.batch, 1 if args.no_points else 64)
-    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=max(biggest, PREFILL[0]) * ctx,
-                              decode_programs=args.decode_program)
+    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=max(biggest, PREFILL[0]) * ctx)
     engine.config = cfg
     del tensors
     sampler = E.Sampler(engine.ops)

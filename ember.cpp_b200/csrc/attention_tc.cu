@@ -168,18 +168,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ready when the softmax warps come for them.
     const unsigned idesc_s = instr_desc_bf16(kQRows, kKeys, false), idesc_o = instr_desc_bf16(kQRows, HD, true);
     const unsigned long long dq = smem_desc_sw128(sQ);
-    bool ok = mbar_wait(q_full, 0);
+    bool ok = __all_sync(0xffffffffu, mbar_wait(q_full, 0));
     auto issue_s = [&](int it) -> bool {  // S[it & 1] = Q K_it^T
       const int st = it % kStages, b = it & 1;
-      if (!mbar_wait(kv_full + 8 * st, (it / kStages) & 1) || !mbar_wait(s_free + 8 * b, ((it >> 1) & 1) ^ 1)) return false;
+      if (!__all_sync(0xffffffffu, mbar_wait(kv_full + 8 * st, (it / kStages) & 1) && mbar_wait(s_free + 8 * b, ((it >> 1) & 1) ^ 1)))
+        return false;
       fence_after();
-      if (lane == 0) {
-        const unsigned long long dk = smem_desc_sw128(sKV + st * 2 * kPageBytes);
+      // every lane holds the same operands and one elected lane issues (tc_common.cuh: that is the fast way)
+      const unsigned long long dk = smem_desc_sw128(sKV + st * 2 * kPageBytes);
 #pragma unroll
-        for (int k = 0; k < HD / 16; ++k) umma_1cta(tmem + 64 * b, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);  // 32 bytes of a row a step
-        umma_commit_1cta(s_full + 8 * b);
-      }
-      __syncwarp();
+      for (int k = 0; k < HD / 16; ++k) umma_1cta_elect(tmem + 64 * b, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);  // 32 bytes of a row a step
+      umma_commit_1cta_elect(s_full + 8 * b);
       return true;
     };
     if (ok) ok = issue_s(0);
@@ -187,19 +186,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       const int st = it % kStages, b = it & 1;
       if (it + 1 < n_steps) ok = issue_s(it + 1);
       if (!ok) break;
-      ok = mbar_wait(p_full + 8 * b, (it >> 1) & 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(p_full + 8 * b, (it >> 1) & 1));
       if (!ok) break;
       fence_after();
-      if (lane == 0) {
-        const unsigned long long dp = smem_desc_sw128(sP + b * kPBytes);
-        const unsigned long long dv = smem_desc_sw128(sKV + st * 2 * kPageBytes + kPageBytes);
+      const unsigned long long dp = smem_desc_sw128(sP + b * kPBytes);
+      const unsigned long long dv = smem_desc_sw128(sKV + st * 2 * kPageBytes + kPageBytes);
 #pragma unroll
-        for (int k = 0; k < kKeys / 16; ++k)  // 16 keys a step: 32 bytes of a row of P, 16 rows (2,048 bytes) of V
-          umma_1cta(tmem + 128, dp + 2 * k, dv + 128 * k, idesc_o, (it | k) != 0);
-        umma_commit_1cta(pv_done + 8 * b);
-        umma_commit_1cta(kv_empty + 8 * st);
-      }
-      __syncwarp();
+      for (int k = 0; k < kKeys / 16; ++k)  // 16 keys a step: 32 bytes of a row of P, 16 rows (2,048 bytes) of V
+        umma_1cta_elect(tmem + 128, dp + 2 * k, dv + 128 * k, idesc_o, (it | k) != 0);
+      umma_commit_1cta_elect(pv_done + 8 * b);
+      umma_commit_1cta_elect(kv_empty + 8 * st);
     }
     if (!ok && lane == 0) atomicCAS(p.status, 0, ATT_PRODUCTS);
   } else {

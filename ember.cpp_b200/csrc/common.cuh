@@ -94,7 +94,7 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\
 namespace timeline {
 constexpr unsigned kMarks = 8;          // marks a block can leave
 constexpr unsigned kCap = 1u << 18;     // entries of a file's log
-enum Kernel { kEmbed = 1, kLayerNorm = 2, kLinearDecode = 3, kAttentionDecode = 4, kSample = 5 };
+enum Kernel { kEmbed = 1, kLayerNorm = 2, kLinearDecode = 3, kAttentionDecode = 4, kSample = 5, kLinearStream = 6 };
 enum Mark { kStart = 0, kDependency = 1, kEnd = 2, kMerged = 3, kPhaseA = 4, kPhaseB = 5, kPhaseC = 6, kPhaseD = 7 };
 struct Entry {
   unsigned long long t;  // nanoseconds of the global timer; 0: the block did not leave this mark

@@ -78,21 +78,26 @@ __device__ __forceinline__ void load_2d(unsigned dst, const CUtensorMap* map, in
         : "memory");
 }
 
+// Issued by a whole, converged warp whose lanes all hold the same operands; one elected lane
+// issues (tc_common.cuh says why: from a single thread's branch a product costs 156 cycles to issue
+// against 128 of arithmetic for N = 256).
 template <int CTAS>
 __device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
                                      unsigned accumulate) {
   if constexpr (CTAS == 2)
     asm volatile(
-        "{\n.reg .pred p;\n"
+        "{\n.reg .pred p, e;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "elect.sync _|e, 0xffffffff;\n"
+        "@e tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
         "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
         : "memory");
   else
     asm volatile(
-        "{\n.reg .pred p;\n"
+        "{\n.reg .pred p, e;\n"
         "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+        "elect.sync _|e, 0xffffffff;\n"
+        "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
         "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
@@ -101,11 +106,18 @@ __device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsi
 template <int CTAS>
 __device__ __forceinline__ void umma_commit(unsigned bar) {
   if constexpr (CTAS == 2)
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n" ::"r"(bar),
-                 "h"((unsigned short)3)
-                 : "memory");
+    asm volatile(
+        "{\n.reg .pred e;\n"
+        "elect.sync _|e, 0xffffffff;\n"
+        "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n}\n" ::"r"(bar),
+        "h"((unsigned short)3)
+        : "memory");
   else
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+    asm volatile(
+        "{\n.reg .pred e;\n"
+        "elect.sync _|e, 0xffffffff;\n"
+        "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(bar)
+        : "memory");
 }
 __device__ __forceinline__ void cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
@@ -243,29 +255,25 @@ __global__ void __launch_bounds__(kThreads, 1)
       bool ok = true;
       for (int tile = group; tile < n_tiles && ok; tile += groups, ++t) {
         const int as = t & 1;
-        ok = mbar_wait(acc_empty0 + 8 * as, ((t >> 1) & 1) ^ 1);
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty0 + 8 * as, ((t >> 1) & 1) ^ 1));
         if (!ok) break;
         fence_after();
         const unsigned acc = tmem + as * kAccStride;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int s = it % p.stages;
-          ok = mbar_wait(full0 + 8 * s, (it / p.stages) & 1);
+          ok = __all_sync(0xffffffffu, mbar_wait(full0 + 8 * s, (it / p.stages) & 1));
           if (!ok) break;
           fence_after();
-          if (lane == 0) {
-            const unsigned a_addr = base + s * stage_bytes;
+          const unsigned a_addr = base + s * stage_bytes;
 #pragma unroll
-            for (int j = 0; j < KSUB; ++j) {
-              const unsigned long long da = smem_desc_sw128(a_addr + j * a_bytes), db = smem_desc_sw128(a_addr + KSUB * a_bytes + j * b_bytes);
+          for (int j = 0; j < KSUB; ++j) {
+            const unsigned long long da = smem_desc_sw128(a_addr + j * a_bytes), db = smem_desc_sw128(a_addr + KSUB * a_bytes + j * b_bytes);
 #pragma unroll
-              for (int k = 0; k < BK / 16; ++k) umma<CTAS>(acc, da + 2 * k, db + 2 * k, idesc, (kb | j | k) != 0);  // 32 bytes a step
-            }
-            umma_commit<CTAS>(empty0 + 8 * s);
+            for (int k = 0; k < BK / 16; ++k) umma<CTAS>(acc, da + 2 * k, db + 2 * k, idesc, (kb | j | k) != 0);  // 32 bytes a step
           }
-          __syncwarp();
+          umma_commit<CTAS>(empty0 + 8 * s);
         }
-        if (ok && lane == 0) umma_commit<CTAS>(acc_full0 + 8 * as);
-        __syncwarp();
+        if (ok) umma_commit<CTAS>(acc_full0 + 8 * as);
       }
       if (!ok && lane == 0) atomicCAS(p.status, TC_OK, TC_MMA);
     }
@@ -398,21 +406,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 std::mutex g_mutex;
 int g_sms = 0;
 
-struct MapKey {
-  const void* ptr;
-  int rows, cols, box_rows;
-  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
-};
-struct MapHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = (size_t)k.ptr * 1099511628211ull;
-    h = (h ^ (size_t)k.rows) * 1099511628211ull;
-    h = (h ^ (size_t)k.cols) * 1099511628211ull;
-    return (h ^ (size_t)k.box_rows) * 1099511628211ull;
-  }
-};
-std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;  // weights come back with every call: their maps are kept
-
 int tc_setup() {
   if (g_sms) return 0;
   if (!tc::encoder()) return ember_fail("linear_tc: the driver has no cuTensorMapEncodeTiled");
@@ -425,24 +418,6 @@ int tc_setup() {
     e = cudaFuncSetAttribute(linear_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit - 1024);
   if (e != cudaSuccess) return ember_fail("linear_tc: shared memory: %s", cudaGetErrorString(e));
   g_sms = sms;
-  return 0;
-}
-
-// A [rows, cols] bfloat16 row-major matrix, copied in boxes of box_rows x 64 with the 128-byte
-// swizzle; what lies outside the matrix reads as zero.
-int tensor_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
-  const MapKey key{ptr, rows, cols, box_rows};
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) {
-    *out = it->second;
-    return 0;
-  }
-  CUtensorMap m;
-  if (!tc::encode_bf16_sw128(&m, ptr, (size_t)rows, (size_t)cols, (size_t)cols * 2, box_rows))
-    return ember_fail("linear_tc: the driver refused a tensor map for [%d, %d]", rows, cols);
-  if (g_maps.size() > 4096) g_maps.clear();
-  g_maps.emplace(key, m);
-  *out = m;
   return 0;
 }
 
@@ -461,6 +436,57 @@ int pick_bn(int M, int N, int groups, int ctas) {
 }
 
 }  // namespace
+
+// Tensor maps are kept by (address, shape, box): weights come back with every call, activations
+// with every replay of a graph.  Declared in tc_common.cuh; shared by the kernels that use TMA.
+namespace tc {
+namespace map_cache {
+struct MapKey {
+  const void* ptr;
+  int rows, cols, box_rows, kind;  // kind 0: bfloat16, 128-byte swizzle; 1: float32, unswizzled
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && box_rows == o.box_rows && kind == o.kind;
+  }
+};
+struct MapHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = (size_t)k.ptr * 1099511628211ull;
+    h = (h ^ (size_t)k.rows) * 1099511628211ull;
+    h = (h ^ (size_t)k.cols) * 1099511628211ull;
+    return (h ^ (size_t)(k.box_rows * 2 + k.kind)) * 1099511628211ull;
+  }
+};
+std::mutex g_map_mutex;
+std::unordered_map<MapKey, CUtensorMap, MapHash> g_maps;
+}  // namespace map_cache
+
+static int cached_map_kind(const void* ptr, int rows, int cols, int box_rows, int kind, CUtensorMap* out) {
+  using namespace map_cache;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const MapKey key{ptr, rows, cols, box_rows, kind};
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *out = it->second;
+    return 0;
+  }
+  CUtensorMap m;
+  const bool made = kind == 0 ? encode_bf16_sw128(&m, ptr, (size_t)rows, (size_t)cols, (size_t)cols * 2, box_rows)
+                              : encode_f32_plain(&m, ptr, (size_t)rows, (size_t)cols, (size_t)cols * 4, box_rows);
+  if (!made)
+    return ember_fail("the driver refused a tensor map for a [%d, %d] %s matrix in boxes of %d rows", rows, cols,
+                      kind == 0 ? "bfloat16" : "float32", box_rows);
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps.emplace(key, m);
+  *out = m;
+  return 0;
+}
+int cached_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+  return cached_map_kind(ptr, rows, cols, box_rows, 0, out);
+}
+int cached_map_f32(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out) {
+  return cached_map_kind(ptr, rows, cols, box_rows, 1, out);
+}
+}  // namespace tc
 
 // 0 when every launch of the tcgen05 kernels so far ran to its end; else the code of the role
 // whose wait ran out (linear_tc: 1 producer, 2 products, 3 epilogue, 4 copies that never landed;
@@ -496,8 +522,8 @@ EMBER_API int ember_linear_tc(const void* A, const void* W, const float* bias, c
     if (int rc = tc_setup()) return rc;
     groups = g_sms / ctas;
     bn = tile_n ? tile_n : pick_bn(M, N, groups, ctas);
-    if (int rc = tensor_map(A, M, K, BM, &map_a)) return rc;
-    if (int rc = tensor_map(W, N, K, bn / ctas, &map_w)) return rc;
+    if (int rc = tc::cached_map(A, M, K, BM, &map_a)) return rc;
+    if (int rc = tc::cached_map(W, N, K, bn / ctas, &map_w)) return rc;
   }
   TcArgs p;
   p.bias = bias, p.residual = residual, p.out = out;

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "ember_linear_bf16": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_void, _c_size, _c_void, _c_void],
     "ember_linear_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_linear_stream": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                            _c_void],
     "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_size, _c_void],
     "ember_kv_store": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
@@ -60,7 +62,8 @@ class KernelError(RuntimeError):
     pass
 
 
-SMALL_M = 16          # rows up to which the weight-streaming product is used instead of the library's
+SMALL_M = 16          # rows up to which the mma.sync weight-streaming product (linear_decode.cu) is used
+STREAM_M = 64         # rows up to which the tcgen05 weight-streaming product (linear_stream.cu) is used above that
 TC_MIN_M = 64         # rows above which the tcgen05 product is used (its tiles have 128 rows)
 
 
@@ -100,11 +103,6 @@ def load_library() -> ctypes.CDLL:
         fn.restype = _c_int
     lib.ember_attention_decode_partials.argtypes = [_c_int] * 5
     lib.ember_attention_decode_partials.restype = _c_size
-    for name in ("ember_decode_program_op_size", "ember_decode_program_state_size"):
-        getattr(lib, name).argtypes = []
-        getattr(lib, name).restype = _c_int
-    lib.ember_decode_program_run.argtypes = [_c_void, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void]
-    lib.ember_decode_program_run.restype = _c_int
     for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status",
                  "ember_attention_decode_mma_status"):
         getattr(lib, name).argtypes = []
@@ -158,6 +156,9 @@ class CudaOps:
         # Measured on GPT-2 XL's four products the library is ahead: at 2,048 rows 133 against 205
         # microseconds a layer, at 16,384 rows the tcgen05 kernel reaches 87 % of it on the QKV product.
         self.gemm = os.environ.get("EMBER_GEMM", "lt")
+        # Products of SMALL_M + 1 to STREAM_M rows stream the weights through this library's tcgen05 kernel with
+        # the operands swapped (linear_stream.cu); EMBER_LINEAR_STREAM=0 sends them to cuBLASLt (for measurements).
+        self.linear_stream_on = os.environ.get("EMBER_LINEAR_STREAM", "1") == "1"
         self.lt_tune = os.environ.get("EMBER_LT_TUNE", "1") != "0"
         self._lt_tuned = set()
         # Prefill attention with head size 64 runs on the tcgen05 kernel; EMBER_ATTENTION=mma keeps it
@@ -253,8 +254,8 @@ class CudaOps:
 
     AHEAD_BYTES = 48 << 20   # rows of one layer's cache that are worth asking into L2 a layer early
 
-    TIMELINE_KERNELS = {1: "embed", 2: "layernorm", 3: "linear_decode", 4: "attention_decode", 5: "sample"}
-    TIMELINE_FILES = ("elementwise", "linear_decode", "attention_decode", "attention_decode_mma", "sampling")
+    TIMELINE_KERNELS = {1: "embed", 2: "layernorm", 3: "linear_decode", 4: "attention_decode", 5: "sample", 6: "linear_stream"}
+    TIMELINE_FILES = ("elementwise", "linear_decode", "linear_stream", "attention_decode", "attention_decode_mma", "sampling")
 
     def timeline(self):
         """What the kernels of a library built with EMBER_TIMELINE=1 noted since the last call: a list of
@@ -350,6 +351,8 @@ class CudaOps:
             return out
         if norm is not None:
             a = norm.materialize()
+        if self.linear_stream_on and M <= STREAM_M and K % 8 == 0:
+            return self.linear_stream(a, w, bias, act, residual, out)
         # an output width that is no multiple of 8 (a vocabulary of 50,257) leaves the library only unaligned,
         # slow kernels (167 against 50 microseconds for the head at 64 rows): those products take the tcgen05 kernel
         if K % 8 == 0 and ((self.gemm == "tc" and M > TC_MIN_M) or N % 8 != 0):
@@ -378,6 +381,14 @@ class CudaOps:
                    M, w.shape[0], K, _ACT[act], _code(out.dtype), tile_n)
         return out
 
+    def linear_stream(self, a, w, bias, act, residual, out, k_split: int = 0, stages: int = 0):
+        """The tcgen05 weight-streaming product for up to 64 rows with its epilogue into `out`; `k_split` and
+        `stages` 0 let the kernel choose how many blocks share a tile and how deep its ring is."""
+        M, K = a.shape
+        self._call("ember_linear_stream", a.data_ptr(), w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(),
+                   M, w.shape[0], K, _ACT[act], _code(out.dtype), int(k_split), int(stages))
+        return out
+
     def check(self) -> None:
         """Raises if a kernel with bounded waits gave up since the last call.  The caller has
         synchronized with the device (it has just read a step's results)."""
@@ -387,9 +398,10 @@ class CudaOps:
             raise KernelError("attention_decode: a block gave up waiting for its copies of keys and values; the results of that launch are not valid")
         code = self.lib.ember_tc_status()
         if code:
-            kernel = "linear_tc" if code < 10 else "attention_prefill_tc"
+            kernel = "linear_tc" if code < 10 else ("attention_prefill_tc" if code < 20 else "linear_stream")
             role = {1: "the TMA producer", 2: "the product issuer", 3: "the epilogue", 4: "copies in flight",
-                    11: "the TMA loader", 12: "the product issuer", 13: "the softmax warps"}.get(code, code)
+                    11: "the TMA loader", 12: "the product issuer", 13: "the softmax warps",
+                    21: "the TMA producer", 22: "the product issuer", 23: "the epilogue", 24: "copies in flight"}.get(code, code)
             raise KernelError(f"{kernel}: a wait ran out ({role}); the results of that launch are not valid")
 
     # ------------------------------------------------------------------ cache and attention

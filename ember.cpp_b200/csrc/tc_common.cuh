@@ -40,17 +40,24 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
       : "memory");
   return ok != 0;
 }
-// Waits for the phase of the given parity to complete.  False when the time ran out.
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-  if (mbar_try(bar, parity)) return true;
+// Waits for the phase of the given parity to complete.  False when the time ran out.  The polling
+// loop is one function for the whole kernel, not a copy at every wait: these kernels run their code
+// once, straight through, and a kernel of 96 KB (what inlined, unrolled polling loops made of the
+// weight-streaming product) waits on its instruction fetches.
+static __device__ __noinline__ bool mbar_wait_poll(unsigned bar, unsigned parity) {
   unsigned long long t0, t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (;;) {
+#pragma unroll 1
     for (int i = 0; i < 256; ++i)
       if (mbar_try(bar, parity)) return true;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     if (t - t0 > kWaitNs) return false;
   }
+}
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  if (mbar_try(bar, parity)) return true;
+  return mbar_wait_poll(bar, parity);
 }
 
 // One box of a tensor map into this block's shared memory; completion counted on `bar`.  No
@@ -89,6 +96,29 @@ __device__ __forceinline__ void umma_1cta(unsigned tmem_d, unsigned long long a,
       "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same two instructions issued by a whole, converged warp whose lanes all hold the same
+// operands: one elected lane issues.  This is the fast way: operands that are the same in every
+// lane live in the warp's uniform registers, which is where the instruction reads them; issued
+// from inside `if (lane == 0)` every operand is first moved there from an ordinary register, and a
+// product costs 156 cycles to issue whatever its size, against 64 to 67 (measured; a product of
+// N = 256 needs 128 cycles of arithmetic, so the slow way caps a kernel at about 0.8 of the peak).
+__device__ __forceinline__ void umma_1cta_elect(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
+                                                unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p, e;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(tmem_d),
+      "l"(a), "l"(b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_1cta_elect(unsigned bar) {
+  asm volatile(
+      "{\n.reg .pred e;\n"
+      "elect.sync _|e, 0xffffffff;\n"
+      "@e tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}\n" ::"r"(bar)
+      : "memory");
+}
 // Arrives on the barrier once the products issued so far by this thread are complete.
 __device__ __forceinline__ void umma_commit_1cta(unsigned bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
@@ -115,6 +145,14 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned (&r)[32]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]),
         "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]),
         "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+// 16 consecutive accumulator columns of this thread's lane (issue only; tmem_wait before use)
+__device__ __forceinline__ void tmem_ld16(unsigned taddr, unsigned (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
@@ -148,6 +186,28 @@ inline bool encode_bf16_sw128(CUtensorMap* out, const void* ptr, size_t rows, si
              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
+
+// A [rows, cols] float32 matrix whose rows are `row_bytes` apart, copied in boxes of box_rows x 128
+// values as they lie (no swizzle: a row of the box is 512 consecutive bytes of shared memory); what
+// lies outside the matrix reads as zero.
+inline bool encode_f32_plain(CUtensorMap* out, const void* ptr, size_t rows, size_t cols, size_t row_bytes, int box_rows) {
+  EncodeTiled enc = encoder();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)row_bytes};
+  const cuuint32_t box[2] = {128u, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  return enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// A [rows, cols] bfloat16 row-major matrix (16-byte aligned, cols a multiple of 8), copied in boxes
+// of box_rows x 64 values with the 128-byte swizzle; what lies outside the matrix reads as zero.
+// Maps are kept by (address, shape, box).  0, or an error code after ember_fail.  (gemm_tc.cu)
+int cached_map(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out);
+// The same for a [rows, cols] float32 row-major matrix (cols a multiple of 4) in boxes of box_rows x 128 values, unswizzled.
+int cached_map_f32(const void* ptr, int rows, int cols, int box_rows, CUtensorMap* out);
 
 // One host-visible status word per process (pinned and mapped): kernels write a code there when a
 // wait ran out; the host reads and clears it after it has synchronized.

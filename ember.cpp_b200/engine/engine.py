@@ -21,7 +21,6 @@ from ..config.base import ModelConfig, get_architecture, load_config
 from ..parts.model import DecoderModel
 from ..parts.spec import ModelSpec
 from ..weights.loader import check_tensors, load_checked
-from ..csrc.program import NotRecordable
 from .plan import StepPlan, build_step
 
 DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
@@ -82,7 +81,7 @@ class Engine:
     """A model, its cache and the step function."""
 
     def __init__(self, model: DecoderModel, runtime: Runtime, max_tokens: int, max_slots: int | None = None,
-                 config: ModelConfig | None = None, cuda_graphs: bool = True, decode_programs: bool = False):
+                 config: ModelConfig | None = None, cuda_graphs: bool = True):
         self.model, self.runtime, self.config = model, runtime, config
         self.ops = runtime.ops
         spec = model.spec
@@ -98,21 +97,12 @@ class Engine:
         # Python) cannot be replayed from a captured graph; it says so with graph_safe = False
         self.cuda_graphs = (bool(cuda_graphs) and runtime.device.type == "cuda"
                             and all(getattr(p, "graph_safe", True) for p in model.all_parts()))
-        # On request, one-token steps of up to 16 sequences in bfloat16 run as one launch of the
-        # persistent decode kernel, if every part can be recorded (does all its device work through
-        # `ops`).  Off by default: as it stands the kernel is slower than the replayed graph (5.2
-        # against 2.4 ms a step at GPT-2 XL shape, batch 8).
-        blocks = [b for b in model.blocks]
-        self.decode_programs = (bool(decode_programs) and self.cuda_graphs and runtime.dtype == torch.bfloat16
-                                and all(getattr(p, "ops_only", False) for p in model.all_parts())
-                                and all(getattr(b, "ops_only", False) for b in blocks))
-        self._programs: dict[int, "_DecodeProgramStep"] = {}
         self.counters = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0}
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda", ops=None,
-                    max_slots: int | None = None, cuda_graphs: bool = True, decode_programs: bool = False) -> "Engine":
+                    max_slots: int | None = None, cuda_graphs: bool = True) -> "Engine":
         """Config, model class and weights from `<folder>/config.json` and `model.safetensors`."""
         config = load_config(folder)
         spec = get_architecture(config.architecture).build_spec(config)
@@ -120,17 +110,16 @@ class Engine:
         runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
         tensors = load_checked(folder, model.weight_specs(), spec.ignored_tensors)
         model.load(tensors, runtime)
-        return cls(model, runtime, max_tokens, max_slots, config, cuda_graphs, decode_programs)
+        return cls(model, runtime, max_tokens, max_slots, config, cuda_graphs)
 
     @classmethod
     def from_spec(cls, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096, device="cuda",
-                  ops=None, max_slots: int | None = None, cuda_graphs: bool = True,
-                  decode_programs: bool = False) -> "Engine":
+                  ops=None, max_slots: int | None = None, cuda_graphs: bool = True) -> "Engine":
         """A model given as data, with its tensors by name (how tests build toy models)."""
         model = DecoderModel(spec)
         runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
         model.load(check_tensors("tensors", tensors, model.weight_specs(), spec.ignored_tensors), runtime)
-        return cls(model, runtime, max_tokens, max_slots, None, cuda_graphs, decode_programs)
+        return cls(model, runtime, max_tokens, max_slots, None, cuda_graphs)
 
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
@@ -258,19 +247,9 @@ class Engine:
         host, shape = self.prepare(entries, pad_to=bucket, want_all=True, device_tokens=device_tokens)
         ids = None if device_tokens is None else device_tokens[0]
         pages = self._length_bucket(-(-host.max_end // 64))
-        g = None
-        if self.decode_programs and bucket <= 8:
-            g = self._programs.get(bucket)
-            if g is None:
-                try:
-                    g = self._programs[bucket] = _DecodeProgramStep(self, host)
-                except NotRecordable:
-                    self.decode_programs = False     # some part asks for what the kernel does not do
-                    g = None
+        g = self._graphs.get((bucket, pages))
         if g is None:
-            g = self._graphs.get((bucket, pages))
-            if g is None:
-                g = self._graphs[(bucket, pages)] = _DecodeGraph(self, host, pages)
+            g = self._graphs[(bucket, pages)] = _DecodeGraph(self, host, pages)
         g.replay(self, host, ids)
         self._account(host, shape)
         rows = [i for i, (_, _, want) in enumerate(entries) for _ in want]
@@ -305,36 +284,6 @@ class _Staging:
             if self.event is None:
                 self.event = torch.cuda.Event()
             self.event.record()
-
-
-class _DecodeProgramStep:
-    """A one-token step recorded once and run as one launch of the persistent decode kernel."""
-
-    def __init__(self, engine: Engine, host):
-        from ..csrc.program import DecodeProgram, RecordingOps
-        dev = engine.runtime.device
-        self.buffer = torch.zeros(host.packed.shape[0], dtype=torch.int32, device=dev)
-        self.staging = _Staging(dev)
-        self.size = host.packed.shape[0]
-        sized = dataclasses.replace(host, max_end=engine.cache.max_blocks * 64)
-        self.plan = StepPlan(sized, self.buffer)
-        recording = RecordingOps()
-        ctx = StepContext(recording, engine.runtime.dtype, self.plan, engine.apps, engine.model.position)
-        self.logits = engine.model.forward(ctx)
-        self.program = DecodeProgram(engine.ops.lib, recording, host.n, dev)
-        self.ran = False
-
-    def replay(self, engine: Engine, host, ids=None) -> None:
-        if host.packed.shape[0] != self.size:
-            raise StepError("the step's description changed size under a recorded program")
-        if self.ran:
-            self.program.check()      # the step before: by now it is over, so this does not wait for long
-        engine._stage(self.staging, host, self.buffer)
-        if ids is not None:
-            engine.ops.take_tokens(self.plan.tokens, self.plan.token_src, ids, engine.vocab_size)
-        self.program.run()
-        self.ran = True
-        engine.ops.launches += 1
 
 
 class _DecodeGraph:

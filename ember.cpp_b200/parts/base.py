@@ -57,10 +57,6 @@ class Part:
     # False for a part whose forward works on the host (reads device values back, loops in Python):
     # an engine with such a part runs every step launch by launch instead of replaying a graph
     graph_safe = True
-    # True for a part that does all its device work through the methods of `ctx.ops` (no torch
-    # operations of its own on the step's tensors): its step can then be recorded once and run by
-    # the persistent decode kernel
-    ops_only = False
 
     def __init__(self, prefix: str = ""):
         self.prefix = prefix

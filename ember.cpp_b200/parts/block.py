@@ -13,7 +13,6 @@ from .base import Block, register_part
 
 
 class PreNormBlock(Block):
-    ops_only = True
 
     def forward(self, ctx, x, app):
         h = self.norm1.forward(ctx, x, ctx.dtype, lazy=self.mixer.takes_lazy_norm)

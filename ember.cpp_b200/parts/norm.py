@@ -11,7 +11,6 @@ from .base import Norm, WeightSpec, register_part
 
 
 class LayerNorm(Norm):
-    ops_only = True
 
     def __init__(self, prefix: str, width: int, eps: float, weight: str = "weight", bias: str = "bias"):
         super().__init__(prefix)

@@ -11,7 +11,6 @@ from .base import Position, WeightSpec, register_part
 
 
 class LearnedAbsolute(Position):
-    ops_only = True
 
     def __init__(self, prefix: str, width: int, n_positions: int, table: str = "weight", init_std: float = 0.02):
         super().__init__(prefix)
@@ -34,7 +33,6 @@ class LearnedAbsolute(Position):
 
 
 class NoPosition(Position):
-    ops_only = True
 
     def __init__(self, prefix: str = ""):
         super().__init__(prefix)

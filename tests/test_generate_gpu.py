@@ -96,21 +96,36 @@ def test_padding_changes_no_result(engines, plains, dtype):
 
 
 @pytest.mark.parametrize("name", NAMES)
-def test_one_launch_decode_program_equals_the_graph(tiny_folders, plains, name):
-    """The persistent decode kernel (a recorded step run as one launch) against the replayed graph
-    and the plain implementation: unequal batches, padding, a sequence that leaves early."""
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_batches_of_20_40_and_64_sequences(tiny_folders, plains, name, dtype):
+    """Decoding with more sequences than one weight-streaming tile of 16: 20, 40 and 64 sequences of
+    unequal lengths whose shorter ones leave on the way (so the step passes through every bucket of
+    batch sizes from 64 down, padded to 32 and 64 in between), one batch after another in the same
+    slots.  Every row against the plain implementation; in 32-bit a sequence's rows are the same
+    bits as when it runs alone."""
     plain = plains[name]
-    seqs = [random_ids(450 + i, plain.vocab, n) for i, n in enumerate((plain.n_positions, 40, 70))]
-    out = []
-    for programs in (True, False):
-        eng = Engine.from_folder(tiny_folders[name], dtype="bfloat16", max_tokens=1024, decode_programs=programs)
-        assert eng.decode_programs == programs
-        out.append(run_batch(eng, seqs, (10, 1, 30))[0])
-        if programs:
-            assert eng._programs and not eng._graphs
-    for ids, a, b in zip(seqs, *out):
-        assert rel_error(a, plain.logits(ids)) < TOL["bfloat16"]
-        assert rel_error(a, b) < TOL["bfloat16"]
+    P = plain.n_positions
+    eng = Engine.from_folder(tiny_folders[name], dtype=dtype, max_tokens=64 * 128, max_slots=64)
+    rng = np.random.default_rng(11)
+    first_slots = None
+    for b, count in enumerate((64, 20, 40)):
+        lengths = [int(n) for n in rng.integers(2, P + 1, count)]
+        lengths[0], lengths[-1] = P, 2                               # one to the last position, one that leaves at once
+        prompts = [int(rng.integers(1, n)) for n in lengths]
+        seqs = [random_ids(600 + 100 * b + i, plain.vocab, n) for i, n in enumerate(lengths)]
+        rows, slots = run_batch(eng, seqs, prompts)
+        eng.ops.check()
+        worst = max(rel_error(got, plain.logits(ids)) for ids, got in zip(seqs, rows))
+        assert worst < TOL[dtype], (count, worst)
+        if dtype == "float32":
+            for i in (0, count // 2, count - 1):
+                alone, _ = run_batch(eng, [seqs[i]], (prompts[i],))
+                assert np.array_equal(alone[0], rows[i]), (count, i)
+        eng.cache.check()
+        assert eng.cache.slots.held == 0 and eng.cache.groups[0].pages.held == 0
+        first_slots = first_slots or set(slots)
+        assert set(slots) <= first_slots                              # the slots of the first batch, used again
+    assert {b for b, _ in eng._graphs} >= {64, 32, 16, 8, 4, 2, 1}    # every bucket of batch sizes was replayed
 
 
 @pytest.mark.parametrize("name", NAMES)

@@ -130,6 +130,51 @@ def test_linear_few_rows_streams_the_weights(ops, M, N, K, act, with_bias, with_
     assert (got.double() - want).abs().max().item() / scale < (2e-4 if out == "float32" else 2 ** -7)
 
 
+STREAM_SHAPES = [(4800, 1600), (1600, 1600), (6400, 1600), (1600, 6400), (50257, 1600), (200, 328), (130, 72), (77, 64)]
+
+
+@pytest.mark.parametrize("N, K", STREAM_SHAPES)
+@pytest.mark.parametrize("M", [17, 32, 33, 48, 64])
+def test_linear_17_to_64_rows_streams_the_weights(ops, M, N, K):
+    """17 to 64 rows take the tcgen05 weight-streaming kernel (operands swapped, K split over a
+    cluster): GPT-2 XL's four products and its head (an output width that is no multiple of 8), and
+    small shapes with tails in N (no multiple of 128) and K (no multiple of 64), with each epilogue."""
+    a, w = gen((M, K), 40, torch.bfloat16), gen((N, K), 41, torch.bfloat16, 0.1)
+    bias, res = gen((N,), 42), gen((M, N), 43)
+    launches = ops.launches
+    for act, with_bias, with_res, out in [(None, True, False, "bfloat16"), ("gelu_tanh", True, False, "bfloat16"),
+                                          ("gelu_erf", False, False, "bfloat16"), (None, True, True, "float32"),
+                                          (None, False, False, "float32")]:
+        want = linear_ref(a, w, bias if with_bias else None, act, res if with_res else None)
+        got = ops.linear(a, w, bias if with_bias else None, act=act, residual=res.clone() if with_res else None,
+                         out_dtype=DT[out])
+        assert got.dtype == DT[out]
+        scale = want.abs().max().item() + 1e-6
+        assert (got.double() - want).abs().max().item() / scale < (2e-4 if out == "float32" else 2 ** -7), (act, out)
+    assert ops.launches == launches + 5          # one launch each: no separate activation or sum
+    ops.check()
+
+
+@pytest.mark.parametrize("M", [1, 16, 23, 64])
+@pytest.mark.parametrize("N, K", [(1600, 1600), (300, 6400), (129, 200)])
+def test_linear_stream_every_split_and_ring(ops, M, N, K):
+    """Every number of blocks to a tile (1 to 8) and rings shorter than a block's share of K give the
+    same sums up to float32 rounding, and each of them twice the same bits (no atomics, no timing)."""
+    a, w = gen((M, K), 44, torch.bfloat16), gen((N, K), 45, torch.bfloat16, 0.1)
+    bias, res = gen((N,), 46), gen((M, N), 47)
+    want = linear_ref(a, w, bias, None, res)
+    scale = want.abs().max().item()
+    for k_split in range(1, 9):
+        for stages in (0, 2, 3):
+            first = res.clone()
+            ops.linear_stream(a, w, bias, None, first, first, k_split, stages)
+            again = res.clone()
+            ops.linear_stream(a, w, bias, None, again, again, k_split, stages)
+            assert torch.equal(first, again), (k_split, stages)
+            assert (first.double() - want).abs().max().item() / scale < 2e-4, (k_split, stages)
+    ops.check()
+
+
 @pytest.mark.parametrize("M, N, K", [(1, 1600, 1600), (8, 1600, 6400), (9, 96, 64), (16, 2056, 72), (5, 100, 1600), (16, 1600, 1600)])
 def test_linear_norms_the_stream_in_its_tail(ops, M, N, K):
     """A product that sums into the residual stream and was told which norm follows leaves that
