@@ -60,15 +60,20 @@ class CacheGroup:
         first = self.first_needed_block(start)
         return sum(1 for b in range(first, blocks) if b >= len(have) or have[b] < 0)
 
-    def ensure(self, slot: int, start: int, n_new: int) -> None:
+    def ensure(self, slot: int, start: int, n_new: int) -> list[int]:
+        """Takes the pages that positions start .. start + n_new - 1 need; returns the blocks (64-position
+        runs of the sequence) whose page is new."""
         blocks = -(-(start + n_new) // PAGE)
         have = self.held[slot]
         first = self.first_needed_block(start)
         while len(have) < blocks:
             have.append(-1)
+        fresh = []
         for b in range(first, blocks):
             if have[b] < 0:
                 have[b] = self.pages.take()
+                fresh.append(b)
+        return fresh
 
     def trim(self, slot: int, length: int) -> None:
         """Gives back what no later query can read (window groups), or what lies past `length`."""
@@ -174,9 +179,19 @@ class SequenceCache:
         return self.lengths[slot]
 
     # ------------------------------------------------------------------ a step's storage
-    def reserve(self, step: list[tuple[int, int]]) -> None:
+    def reserve(self, step: list[tuple[int, int]]) -> list[list[tuple[int, int]]]:
         """`step`: (slot, number of new positions) per sequence.  Checks everything, then takes
-        the pages; on an error nothing has changed."""
+        the pages; on an error nothing has changed.
+
+        Returns, per group and per sequence of the step, (page, first row) of a tail to clear, or
+        (-1, 0): pages are not cleared when they change hands (ember.cpp does not clear its cache
+        between requests either: rows are written before they are read, api.cpp:943-944), so a page
+        that is new to a sequence holds whatever its last owner left, possibly NaN or Inf.  Kernels
+        that load whole pages multiply a probability of exactly zero with the rows past a
+        sequence's end, and zero times NaN is NaN.  So when the page that will hold a sequence's
+        last position after this step is new to it, the rows of that page past the step's end are
+        cleared before the step runs (`tails`); every other row of a new page is written by the
+        step itself.  A held page then holds finite values in every row."""
         seen = set()
         for slot, n_new in step:
             if not self.slots.is_held(slot):
@@ -196,9 +211,16 @@ class SequenceCache:
             if missing > g.pages.free:
                 raise CacheError(f"the cache is full: this step needs {missing} more pages of {PAGE} positions, "
                                  f"{g.pages.free} of {g.pages.size} are free (max_tokens = {self.max_tokens})")
+        tails = []
         for g in self.groups:
+            of_group = []
             for slot, n in step:
-                g.ensure(slot, self.lengths[slot], n)
+                fresh = g.ensure(slot, self.lengths[slot], n)
+                end = self.lengths[slot] + n
+                last = (end - 1) // PAGE
+                of_group.append((g.held[slot][last], end % PAGE) if last in fresh and end % PAGE else (-1, 0))
+            tails.append(of_group)
+        return tails
 
     def commit(self, step: list[tuple[int, int]]) -> None:
         """The step ran: lengths advance, window groups give back what fell out of the window."""

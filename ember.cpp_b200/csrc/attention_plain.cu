@@ -61,6 +61,37 @@ EMBER_API int ember_kv_store(const void* qkv, void* kc, void* vc, const int* pos
   return 0;
 }
 
+// ---------------------------------------------------------------------------- tails of new pages
+// Pages are not cleared when they pass from one sequence to the next, so a page that is new to a
+// sequence holds what its last owner left there, NaN and Inf included.  The rows of such a page that
+// the step does not write (those past the step's end) are zeroed here, in every tensor of the
+// cache group, before the step runs: a kernel that loads whole pages and masks by selection still
+// multiplies a probability of zero with those rows.  ember.cpp's kernel tests fill their caches
+// with NaN to catch such reads (tools/window_attention_cuda_test.cu:57-86).
+// grid (sequences, tensors); tails[i] = (page, first row) or (-1, 0).
+__global__ void clear_tails_kernel(void* const* __restrict__ tensors, const int* __restrict__ tails, int kv_heads,
+                                   int row_bytes) {
+  const int page = tails[2 * blockIdx.x], row0 = tails[2 * blockIdx.x + 1];
+  if (page < 0 || row0 >= kPage) return;
+  char* base = static_cast<char*>(tensors[blockIdx.y]);
+  const int vecs = (kPage - row0) * row_bytes / 16;  // a row is a multiple of 16 bytes
+  for (int h = 0; h < kv_heads; ++h) {
+    uint4* dst = reinterpret_cast<uint4*>(base + (((size_t)page * kv_heads + h) * kPage + row0) * row_bytes);
+    for (int i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+EMBER_API int ember_clear_tails(void* const* tensors, int n_tensors, const int* tails, int n, int kv_heads, int hd,
+                                int elem_bytes, cudaStream_t stream) {
+  EMBER_CHECK(n_tensors > 0 && n > 0 && kv_heads > 0 && hd > 0, "clear_tails: bad sizes");
+  EMBER_CHECK((elem_bytes == 2 || elem_bytes == 4) && hd * elem_bytes % 16 == 0, "clear_tails: rows of %d x %d bytes", hd,
+              elem_bytes);
+  EMBER_CHECK(n <= 65535 * 32 && n_tensors <= 65535, "clear_tails: %d sequences x %d tensors exceed one launch", n, n_tensors);
+  clear_tails_kernel<<<dim3(n, n_tensors), 128, 0, stream>>>(tensors, tails, kv_heads, hd * elem_bytes);
+  EMBER_LAUNCH_OK("clear_tails");
+  return 0;
+}
+
 // ---------------------------------------------------------------------------- plain attention
 constexpr int kMaxHeadDim = 256;
 

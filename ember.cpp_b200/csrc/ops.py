@@ -38,6 +38,7 @@ _SIGNATURES = {
                             _c_void],
     "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_size, _c_void],
+    "ember_clear_tails": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_kv_store": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_void],
     "ember_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
@@ -405,6 +406,17 @@ class CudaOps:
             raise KernelError(f"{kernel}: a wait ran out ({role}); the results of that launch are not valid")
 
     # ------------------------------------------------------------------ cache and attention
+    def clear_tails(self, group, tails) -> None:
+        """Zeroes, in every key and value tensor of a cache group, the rows from `row` on of each page
+        named in tails [n, 2] = (page, row) (page < 0: nothing)."""
+        table = getattr(group, "_tensor_table", None)
+        if table is None:      # the addresses of the group's tensors, once
+            tensors = list(group.k) + list(group.v)
+            table = group._tensor_table = torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=tensors[0].device)
+        need = group.need
+        self._call("ember_clear_tails", table.data_ptr(), table.numel(), tails.data_ptr(), tails.shape[0], need.kv_heads,
+                   need.head_dim, group.k[0].element_size())
+
     def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):
         if qkv.dtype != cache.k.dtype:
             raise KernelError(f"kv_store: activations are {qkv.dtype}, the cache is {cache.k.dtype}")

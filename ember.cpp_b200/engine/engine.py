@@ -158,11 +158,20 @@ class Engine:
                 raise StepError("tokens taken from the device: rows of a one-dimensional int32 tensor of sampled ids")
         shape = [(slot, len(tokens)) for slot, tokens, _ in entries]
         try:
-            self.cache.reserve(shape)
+            tails = self.cache.reserve(shape)
         except CacheError as e:
             raise StepError(str(e)) from None
         tables = [g.table for g in self.cache.groups]
-        return build_step(entries, self.cache.lengths, tables, self.cache.max_blocks, pad_to, want_all, rows), shape
+        return build_step(entries, self.cache.lengths, tables, self.cache.max_blocks, pad_to, want_all, rows, tails), shape
+
+    def clear_tails(self, plan: StepPlan) -> None:
+        """Clears the rows past the step's end in pages that are new to their sequences (see
+        `SequenceCache.reserve`), in every layer's keys and values.  Before the step's own launches,
+        and outside a captured graph: most steps have none."""
+        if not plan.has_tails:
+            return
+        for g, group in enumerate(self.cache.groups):
+            self.ops.clear_tails(group, plan.tails[g])
 
     def _stage(self, staging: "_Staging", host, device_buffer) -> None:
         """Host description -> pinned memory -> device, without racing an earlier copy."""
@@ -193,6 +202,7 @@ class Engine:
         plan = self.upload(host)
         if device_tokens is not None:
             self.ops.take_tokens(plan.tokens, plan.token_src, device_tokens[0], self.vocab_size)
+        self.clear_tails(plan)
         logits = self.run(plan)
         self._account(host, shape)
         return logits
@@ -296,6 +306,7 @@ class _DecodeGraph:
         sized = dataclasses.replace(host, max_end=pages * 64)
         self.plan = StepPlan(sized, self.buffer)
         engine._stage(self.staging, host, self.buffer)
+        engine.clear_tails(self.plan)
         if dev.type != "cuda":
             self.graph = None
             return
@@ -314,6 +325,9 @@ class _DecodeGraph:
         engine._stage(self.staging, host, self.buffer)
         if ids is not None:           # outside the graph: the ids' address changes from step to step
             engine.ops.take_tokens(self.plan.tokens, self.plan.token_src, ids, engine.vocab_size)
+        if host.has_tails:            # outside the graph as well: a step in 64 has any
+            self.plan.has_tails = True
+            engine.clear_tails(self.plan)
         if self.graph is None:
             self.logits = engine.run(self.plan)
         else:

@@ -12,6 +12,8 @@ once:
   seq_slot[n] seq_start[n] seq_new[n] cu_new[n+1] one entry per sequence (slot -1: padding)
   want_rows[R]                                   rows of the token list whose logits are wanted
   pages[g][n, max_blocks]                        per cache group, each sequence's page numbers
+  tails[g][n, 2]                                 per cache group and sequence: (page, first row) of a new page's
+                                                 rows past the step's end, which are cleared first, or (-1, 0)
 
 Padding sequences (slot -1, no tokens of their own in prefill; one dummy token in a padded decode
 batch) are skipped by every kernel that touches the cache and change no result.
@@ -51,6 +53,7 @@ class StepLayout:
         self.cu_new = take(self.n + 1)
         self.want_rows = take(max(self.R, 1))
         self.pages = [take(self.n * self.max_blocks) for _ in range(self.n_groups)]
+        self.tails = [take(2 * self.n) for _ in range(self.n_groups)]
         self.size = off
 
 
@@ -67,17 +70,19 @@ class HostStep:
     all_from_zero: bool           # every real sequence starts at position 0
     all_single: bool              # every sequence brings one token
     wants_every_row: bool = False # the wanted rows are all rows, in order
+    has_tails: bool = False       # some sequence's new last page has rows to clear before the step
 
 
 def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, want_all: bool = False,
-               token_rows=None) -> HostStep:
+               token_rows=None, tails=None) -> HostStep:
     """entries: (slot, tokens, want) per sequence, `want` being indices into that sequence's new
     tokens.  lengths: slot -> positions held before the step.  page_tables: per group, a function
     (slots, width) -> int32 [n, width].  pad_to: pad a one-token-each batch with dummy sequences
     up to this many (0: no padding).  want_all: every token's row is wanted, padding included, and
     the entries' own `want` is left to the caller (the shape a replayed graph needs).  token_rows:
     per entry the row of a device array of sampled ids that holds its (single) token, which the
-    device puts in place of the entry's own token value."""
+    device puts in place of the entry's own token value.  tails: what `SequenceCache.reserve`
+    returned for this step (per group and entry, (page, first row) to clear, or (-1, 0))."""
     n_real = len(entries)
     single = all(len(t) == 1 for _, t, _ in entries)
     n = max(n_real, pad_to) if (single and pad_to) else n_real
@@ -123,8 +128,16 @@ def build_step(entries, lengths, page_tables, max_blocks: int, pad_to: int = 0, 
     buf[lay.cu_new + n] = t0
     for g, table in enumerate(page_tables):
         buf[lay.pages[g]: lay.pages[g] + n * max_blocks] = table(slots, max_blocks).reshape(-1)
+    has_tails = False
+    for g in range(len(page_tables)):
+        pairs = np.full((n, 2), (-1, 0), dtype=np.int32)
+        if tails is not None:
+            for i, (page, row) in enumerate(tails[g]):
+                pairs[i] = (page, row)
+                has_tails = has_tails or page >= 0
+        buf[lay.tails[g]: lay.tails[g] + 2 * n] = pairs.reshape(-1)
     every = R == T and bool((buf[lay.want_rows:lay.want_rows + R] == np.arange(T)).all())
-    return HostStep(lay, buf, T, n, R, max_new, max_end, from_zero, single, every)
+    return HostStep(lay, buf, T, n, R, max_new, max_end, from_zero, single, every, has_tails)
 
 
 class StepPlan:
@@ -152,3 +165,5 @@ class StepPlan:
         self.cu_new = view(lay.cu_new, lay.n + 1)
         self.want_rows = view(lay.want_rows, max(lay.R, 1))
         self.pages = [view(p, lay.n * lay.max_blocks).view(lay.n, lay.max_blocks) for p in lay.pages]
+        self.tails = [view(p, 2 * lay.n).view(lay.n, 2) for p in lay.tails]
+        self.has_tails = host.has_tails

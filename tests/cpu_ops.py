@@ -43,6 +43,12 @@ class CpuOps:
             return residual + y
         return y.to(out_dtype)
 
+    def clear_tails(self, group, tails):
+        for page, row in tails.tolist():
+            if page >= 0:
+                for t in list(group.k) + list(group.v):
+                    t[page, :, row:, :] = 0
+
     def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):
         g = cache.group_index
         q_w = n_heads * head_dim

@@ -166,3 +166,21 @@ def test_random_traffic_keeps_the_books():
         c.close(s)
     c.check()
     assert all(g.pages.free == g.pages.size for g in c.groups) and c.slots.free == c.n_slots
+
+
+def test_tails_of_new_pages_are_named_for_clearing():
+    """`reserve` names, per group and sequence, the rows past the step's end in a page that is new to
+    the sequence: those rows hold what the page's last owner left and the step does not write them."""
+    c = make(max_tokens=64 * 8)
+    a, b = c.open(), c.open()
+    tails = c.reserve([(a, 70), (b, 64)])                 # a: pages 0 and 1, ends at row 6 of page 1; b: one full page
+    page_a1 = c.groups[0].held[a][1]
+    assert tails == [[(page_a1, 6), (-1, 0)]]
+    c.commit([(a, 70), (b, 64)])
+    tails = c.reserve([(a, 1), (b, 1)])                   # a stays in its page; b takes a new page and writes row 0
+    assert tails == [[(-1, 0), (c.groups[0].held[b][1], 1)]]
+    c.commit([(a, 1), (b, 1)])
+    tails = c.reserve([(a, 57), (b, 63)])                 # both end exactly at a page's edge: nothing to clear
+    assert tails == [[(-1, 0), (-1, 0)]]
+    c.commit([(a, 57), (b, 63)])
+    c.check()

@@ -97,6 +97,33 @@ def test_padding_changes_no_result(engines, plains, dtype):
 
 @pytest.mark.parametrize("name", NAMES)
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_a_request_that_left_nan_behind_does_not_reach_the_next(tiny_folders, plains, name, dtype):
+    """Pages are not cleared when they change hands.  After a batch has ended, every page of the cache
+    is filled with NaN (what a request whose activations overflowed leaves behind); the next batch
+    takes the same pages and must equal the plain implementation, prompts that end inside a page,
+    on a page's edge and one token at a time across page edges included."""
+    plain = plains[name]
+    P = plain.n_positions
+    eng = Engine.from_folder(tiny_folders[name], dtype=dtype, max_tokens=4 * 128, max_slots=4)
+    lengths, prompts = (P, 70, 65, 3), (P - 40, 64, 1, 2)
+    first = [random_ids(700 + i, plain.vocab, n) for i, n in enumerate(lengths)]
+    run_batch(eng, first, prompts)
+    for group in eng.cache.groups:
+        for t in list(group.k) + list(group.v):
+            t.fill_(float("nan"))
+    for b in range(2):                                             # twice: graphs captured, then replayed
+        seqs = [random_ids(710 + 10 * b + i, plain.vocab, n) for i, n in enumerate(lengths)]
+        rows, _ = run_batch(eng, seqs, prompts)
+        for ids, got in zip(seqs, rows):
+            assert np.isfinite(got).all()
+            assert rel_error(got, plain.logits(ids)) < TOL[dtype]
+        for group in eng.cache.groups:
+            for t in list(group.k) + list(group.v):
+                t.fill_(float("nan"))
+
+
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_batches_of_20_40_and_64_sequences(tiny_folders, plains, name, dtype):
     """Decoding with more sequences than one weight-streaming tile of 16: 20, 40 and 64 sequences of
     unequal lengths whose shorter ones leave on the way (so the step passes through every bucket of

@@ -15,6 +15,10 @@ from ember_cpp_b200.parts import CacheNeed
 pytestmark = pytest.mark.gpu
 
 DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# Caches start full of NaN (ember.cpp's kernel tests do the same to catch reads of rows that no query may
+# see, tools/window_attention_cuda_test.cu:57-86): a page that is new to a sequence holds what its last owner
+# left, and only the rows past the step's end in such a page are cleared, as the engine clears them.
+NAN = float("nan")
 # against a float64 evaluation of the same inputs: float32 kernels differ by accumulation order
 # only; bfloat16 outputs carry one rounding to 8 bits of mantissa (2^-9 relative) on top
 ATOL = {"float32": 2e-5, "bfloat16": 2e-2}
@@ -402,9 +406,11 @@ def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poiso
     data = [d.to(DT[dtype]) for d in data]
 
     def step(entries, rows):
-        cache.reserve([(s, n) for s, n in entries])
-        host = build_step([(s, [0] * n, []) for s, n in entries], cache.lengths, tables, cache.max_blocks)
+        tails = cache.reserve([(s, n) for s, n in entries])
+        host = build_step([(s, [0] * n, []) for s, n in entries], cache.lengths, tables, cache.max_blocks, tails=tails)
         plan = StepPlan(host, torch.from_numpy(host.packed).cuda())
+        if plan.has_tails:   # as the engine does: the rows past the step's end in pages new to their sequences
+            ops.clear_tails(cache.groups[0], plan.tails[0])
         qkv = torch.cat(rows).cuda().contiguous()
         if store_apart:      # as a layer does that reads a cache which another layer has stored into in this step
             ops.kv_store(qkv, view, plan, heads, kv_heads, hd)
@@ -433,7 +439,7 @@ def run_attention(ops, seqs, heads, kv_heads, hd, dtype, window=0, seed=0, poiso
 @pytest.mark.parametrize("heads, kv_heads, hd", [(4, 4, 16), (25, 25, 64), (6, 2, 32), (3, 1, 80), (2, 2, 128),
                                                  (5, 5, 256), (8, 4, 48)])
 def test_attention_prompts_of_unequal_length(ops, dtype, heads, kv_heads, hd):
-    got, want = run_attention(ops, [(0, 70), (0, 1), (0, 129), (0, 64)], heads, kv_heads, hd, dtype, seed=hd, poison=1e30)
+    got, want = run_attention(ops, [(0, 70), (0, 1), (0, 129), (0, 64)], heads, kv_heads, hd, dtype, seed=hd, poison=NAN)
     assert (got - want).abs().max().item() < ATOL[dtype]
 
 
@@ -441,7 +447,7 @@ def test_attention_prompts_of_unequal_length(ops, dtype, heads, kv_heads, hd):
 @pytest.mark.parametrize("heads, kv_heads, hd", [(4, 4, 16), (25, 25, 64), (6, 2, 32), (3, 1, 80), (4, 2, 128)])
 def test_attention_one_token_each_over_the_cache(ops, dtype, heads, kv_heads, hd):
     seqs = [(199, 1), (63, 1), (64, 1), (0, 1), (300, 1), (127, 1), (128, 1)]
-    got, want = run_attention(ops, seqs, heads, kv_heads, hd, dtype, seed=hd + 1, poison=1e30)
+    got, want = run_attention(ops, seqs, heads, kv_heads, hd, dtype, seed=hd + 1, poison=NAN)
     assert (got - want).abs().max().item() < ATOL[dtype]
 
 
@@ -457,15 +463,15 @@ def test_attention_one_token_each_on_the_tensor_cores(heads, kv_heads, hd, windo
     tensor.decode_mma, other.decode_mma = True, False
     many = [(n, 1) for n in (700, 1, 0, 63, 64, 65, 127, 128, 129, 300, 511, 512, 640)] * (5 if kv_heads > 2 else 40)
     for seqs in (many, [(700, 1), (64, 1), (0, 1), (129, 1)]):
-        got, want = run_attention(tensor, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=1e30)
-        old, _ = run_attention(other, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=1e30)
+        got, want = run_attention(tensor, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=NAN)
+        old, _ = run_attention(other, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=NAN)
         assert (got - want).abs().max().item() < ATOL["bfloat16"]
         assert (old - want).abs().max().item() < ATOL["bfloat16"]
         tensor.check()
     if heads // kv_heads > 8:
         assert torch.equal(got, old)
     # the token's own key already in the cache (stored by a launch of its own): the same output
-    apart, _ = run_attention(tensor, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=1e30, store_apart=True)
+    apart, _ = run_attention(tensor, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=7, poison=NAN, store_apart=True)
     assert (apart - want).abs().max().item() < ATOL["bfloat16"]
 
 
@@ -477,9 +483,9 @@ def test_attention_one_token_each_warms_the_next_layers_rows(heads, kv_heads, hd
     seqs = [(199, 1), (63, 1), (64, 1), (0, 1), (300, 1), (127, 1), (128, 1)]
     plain, warming = CudaOps(), CudaOps()
     plain.cache_ahead, warming.cache_ahead = False, True
-    got, want = run_attention(warming, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=hd + 1, poison=1e30,
+    got, want = run_attention(warming, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=hd + 1, poison=NAN,
                               ahead=True)
-    same, _ = run_attention(plain, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=hd + 1, poison=1e30)
+    same, _ = run_attention(plain, seqs, heads, kv_heads, hd, "bfloat16", window=window, seed=hd + 1, poison=NAN)
     assert (got - want).abs().max().item() < ATOL["bfloat16"]
     assert torch.equal(got, same)
 
@@ -487,7 +493,7 @@ def test_attention_one_token_each_warms_the_next_layers_rows(heads, kv_heads, hd
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_attention_tokens_added_to_a_cache(ops, dtype):
     """More than one new token on top of cached ones: the general case of the step function."""
-    got, want = run_attention(ops, [(50, 30), (64, 64), (1, 5), (100, 130)], 6, 3, 32, dtype, seed=3, poison=1e30)
+    got, want = run_attention(ops, [(50, 30), (64, 64), (1, 5), (100, 130)], 6, 3, 32, dtype, seed=3, poison=NAN)
     assert (got - want).abs().max().item() < ATOL[dtype]
 
 
@@ -509,13 +515,13 @@ def test_attention_on_the_tcgen05_kernel(ops, heads, kv_heads, window):
     seqs = [(0, 300), (0, 128), (0, 1), (70, 129), (64, 64), (200, 57), (0, 127)]
     assert ops.attention_tc
     launches = ops.launches
-    got, want = run_attention(ops, seqs, heads, kv_heads, 64, "bfloat16", window=window, seed=7 + window, poison=1e30)
+    got, want = run_attention(ops, seqs, heads, kv_heads, 64, "bfloat16", window=window, seed=7 + window, poison=NAN)
     torch.cuda.synchronize()
     ops.check()
     assert (got - want).abs().max().item() < ATOL["bfloat16"]
     twin = CudaOps()
     twin.attention_tc = False
-    other, _ = run_attention(twin, seqs, heads, kv_heads, 64, "bfloat16", window=window, seed=7 + window, poison=1e30)
+    other, _ = run_attention(twin, seqs, heads, kv_heads, 64, "bfloat16", window=window, seed=7 + window, poison=NAN)
     assert (got - other).abs().max().item() < ATOL["bfloat16"]
 
 
@@ -584,6 +590,95 @@ def test_kv_store_writes_only_its_rows(ops, dtype):
     assert (k[:, 70:] == 7.0).all()
     untouched = [p for p in range(cache.n_pages) if p not in pages]
     assert (view.k[untouched] == 7.0).all() and (view.v[untouched] == 7.0).all()
+
+
+def rounded(v: float) -> float:
+    """The value as the cache holds it in bfloat16."""
+    return float(torch.tensor(v).bfloat16())
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("mma", [True, False])
+def test_decode_attention_finds_one_far_key(hd, mma):
+    """One-token steps (the decode kernels, on the tensor cores and on the CUDA cores) with one key in
+    page 0 that stands out among 700 and more: every sequence must return that key's value.  Few
+    sequences cut the context into chunks that are merged (in a cluster, and through scratch and a
+    ticket where heads are grouped); many sequences let one block walk all pages.  Random inputs
+    would hide a skipped, misplaced or double-counted page: the softmax over hundreds of keys is
+    nearly flat, and one key moves the output by less than the tolerance."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    ops = CudaOps()
+    ops.decode_mma = mma
+    far = 37
+
+    def shape(heads, kv_heads):
+        def fn(data):
+            qw, kw = heads * hd, kv_heads * hd
+            for d in data:
+                n = d.shape[0]
+                d[:, :qw + kw] *= 0.05
+                d[far, qw:qw + kw] = 4.0                      # the key that stands out, in every head
+                d[far + 1:, :qw] = 4.0                        # the later queries aligned with it
+                d[:, qw + kw:] = torch.arange(n)[:, None].float() / 8
+            return data
+        return fn
+
+    for heads, kv_heads in ((2, 2), (8, 2)):
+        few = [(700, 1), (895, 1), (64, 1), (far + 1, 1)]
+        many = [(700 + 3 * i, 1) for i in range(90)]
+        for seqs in (few, many):
+            for apart in (False, True):
+                got, want = run_attention(ops, seqs, heads, kv_heads, hd, "bfloat16", seed=5, qkv_fn=shape(heads, kv_heads),
+                                          poison=NAN, store_apart=apart)
+                ops.check()
+                assert (got - rounded(far / 8)).abs().max().item() < 5e-2, (heads, kv_heads, len(seqs), apart)
+                assert (got - want).abs().max().item() < 5e-2
+
+
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("mma", [True, False])
+@pytest.mark.parametrize("p", [63, 64, 65, 191, 192, 511, 700])
+def test_decode_attention_window_edge_and_own_key(hd, mma, p):
+    """A window of 150 on one-token steps at positions around page and chunk edges: a key that stands
+    out just outside the window (position p - 150) must be ignored, the same key just inside it
+    (p - 149) must be found, and a token whose own key stands out must return its own value,
+    whether its key is stored by the attention's launch or by a launch of its own."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    ops = CudaOps()
+    ops.decode_mma = mma
+    heads, window = 4, 150
+
+    def shape(at):
+        def fn(data):
+            qw = heads * hd
+            for d in data:
+                n = d.shape[0]
+                d[:, :2 * qw] *= 0.05
+                if 0 <= at < n:
+                    d[at, qw:2 * qw] = 4.0
+                d[n - 1, :qw] = 4.0                            # the last token's query looks for it
+                d[:, 2 * qw:] = torch.arange(n)[:, None].float() / 8
+            return data
+        return fn
+
+    seqs = [(p, 1)] * 3
+    for apart in (False, True):
+        if p - window + 1 >= 0:
+            inside = p - window + 1
+            got, want = run_attention(ops, seqs, heads, heads, hd, "bfloat16", window=window, seed=6, qkv_fn=shape(inside),
+                                      poison=NAN, store_apart=apart)
+            assert (got - rounded(inside / 8)).abs().max().item() < 5e-2, ("inside", apart)
+        if p - window >= 0:
+            outside = p - window
+            got, want = run_attention(ops, seqs, heads, heads, hd, "bfloat16", window=window, seed=6, qkv_fn=shape(outside),
+                                      poison=NAN, store_apart=apart)
+            # (the mean of about 150 values around p / 8, rounded to bfloat16's 8 bits)
+            assert (got - want).abs().max().item() < 2 ** -7 * want.abs().max().item() + 2e-2, ("outside", apart)
+            assert (got - outside / 8).abs().min().item() > 1.0          # nowhere near the ignored key's value
+        got, want = run_attention(ops, seqs, heads, heads, hd, "bfloat16", window=window, seed=6, qkv_fn=shape(p),
+                                  poison=NAN, store_apart=apart)
+        assert (got - rounded(p / 8)).abs().max().item() < 5e-2, ("own", apart)
+    ops.check()
 
 
 # ------------------------------------------------------------------------------ sampling
