@@ -13,7 +13,9 @@ from .engine.generate import Generation, GenerationParams, Generator
 from .sampling import Sampler, SamplingParams
 from .api import Session, TinyLlamaSession
 from .weights import WeightError, write_random_model
+from .options import OptionError, RuntimeOptions
 
-__all__ = ["ConfigError", "Engine", "GPT2Config", "Generation", "GenerationParams", "Generator", "ModelSpec", "Sampler",
+__all__ = ["ConfigError", "Engine", "GPT2Config", "Generation", "GenerationParams", "Generator", "ModelSpec", "OptionError",
+           "RuntimeOptions", "Sampler",
            "SamplingParams", "Session", "StepError", "TinyLlamaSession", "WeightError", "load_config",
            "register_architecture", "register_part", "write_random_model"]

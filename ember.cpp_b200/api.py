@@ -8,7 +8,8 @@ apply_q_a_format=True)`, `.generate_batch(prompts, ...)` and `.get_config()`
 library works on token ids (it has no tokenizer), so a prompt is a list of ids and the reply is a
 list of ids; it runs on one GPU only, so `n_gpu_layers` may be -1 (all) and nothing else;
 quantised caches are not built, so `use_kv_quant` must stay False.  `dtype` and `max_tokens` (the
-cache's size in positions) are additions.
+cache's size in positions) are additions, and so is `options` (a RuntimeOptions: every switch of
+the runtime in one struct; dtype and max_tokens given here override its fields).
 """
 from __future__ import annotations
 
@@ -22,8 +23,8 @@ from .sampling.sampler import SamplingParams
 class Session:
     def __init__(self, model_path: str, tokenizer_path: str | None = None, threads: int = 1, n_gpu_layers: int = -1,
                  use_mmap: bool = True, use_kv_quant: bool = False, use_batch_generation: bool = True,
-                 max_batch_size: int = 8, dtype: str = "bfloat16", max_tokens: int | None = None, seed: int = 0,
-                 ops=None, device: str = "cuda"):
+                 max_batch_size: int = 8, dtype: str | None = None, max_tokens: int | None = None, seed: int = 0,
+                 ops=None, device: str = "cuda", options=None):
         if n_gpu_layers != -1:
             raise ValueError("n_gpu_layers: this library runs every layer on the GPU (-1); it has no CPU path")
         if use_kv_quant:
@@ -39,7 +40,8 @@ class Session:
             cfg = load_config(self.model_path)
             positions = DecoderModel(get_architecture(cfg.architecture).build_spec(cfg)).max_positions() or 4096
             max_tokens = self.max_batch_size * (-(-positions // 64) * 64)
-        self._attach(Engine.from_folder(self.model_path, dtype=dtype, max_tokens=max_tokens, ops=ops, device=device))
+        self._attach(Engine.from_folder(self.model_path, dtype=dtype, max_tokens=max_tokens, ops=ops, device=device,
+                                        options=options))
 
     def _attach(self, engine: Engine) -> None:
         self.engine = engine

@@ -52,6 +52,8 @@ def build_spec(cfg: GPT2Config) -> ModelSpec:
         # also repeat the token table as lm_head.weight
         ignored_tensors=(r"h\.\d+\.attn\.bias", r"h\.\d+\.attn\.masked_bias") +
                         ((r"lm_head\.weight",) if cfg.tie_word_embeddings else ()),
+        # GPT2LMHeadModel keeps its blocks in a module named `transformer`
+        strip_prefixes=("transformer.",),
     )
 
 

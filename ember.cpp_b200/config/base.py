@@ -53,6 +53,10 @@ class ModelConfig:
     def validate(self) -> None:  # pragma: no cover - overridden
         pass
 
+    def check_dtype(self, dtype: str) -> None:
+        """Refuses a configuration that the kernels of compute type `dtype` cannot run, naming the
+        key; called before any weight is read.  The default refuses nothing."""
+
     def to_dict(self) -> dict[str, Any]:
         d = dataclasses.asdict(self)
         d["architectures"] = [self.architecture]

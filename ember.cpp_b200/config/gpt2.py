@@ -64,3 +64,17 @@ class GPT2Config(ModelConfig):
             v = getattr(self, key)
             if v is not None and not 0 <= v < self.vocab_size:
                 raise ConfigError(f"GPT2Config: {key} = {v} is outside the vocabulary [0, {self.vocab_size})")
+
+    def check_dtype(self, dtype: str) -> None:
+        """Refuses, before any weight is read, a model that the kernels of `dtype` cannot run; the
+        error names the keys.  The true 32-bit path takes every size the configuration allows (head
+        sizes up to 256); the bfloat16 kernels read rows in 16-byte pieces."""
+        if self.head_dim > 256:
+            raise ConfigError(f"GPT2Config: n_embd / n_head = {self.head_dim}: the attention kernels take head sizes up to 256")
+        if dtype in ("bfloat16", "bf16"):
+            if self.head_dim % 16:
+                raise ConfigError(f"GPT2Config: n_embd / n_head = {self.n_embd} / {self.n_head} = {self.head_dim} is not a "
+                                  "multiple of 16, which the bfloat16 attention kernels need; --dtype float32 runs this model")
+            if self.inner % 8:
+                raise ConfigError(f"GPT2Config: n_inner = {self.inner} is not a multiple of 8 (rows of 16 bytes), which the "
+                                  "bfloat16 products need; --dtype float32 runs this model")

@@ -424,11 +424,8 @@ EMBER_API int ember_attention_decode_ahead(const void* qkv, const void* kc, cons
   dim3 grid(n_chunks, n_heads, T);
   cudaError_t e;
   // Bulk copies for head sizes up to 128 (two stages of a page's keys and values: 512 bytes per
-  // value of the head size); EMBER_DECODE_BULK=0 in the environment takes the loads (for measurements).
-  static const bool bulk_allowed = [] {
-    const char* v = getenv("EMBER_DECODE_BULK");
-    return !(v && v[0] == '0');
-  }();
+  // value of the head size); the option EMBER_OPT_DECODE_BULK switched off takes the loads (for measurements).
+  const bool bulk_allowed = g_ember_options[EMBER_OPT_DECODE_BULK] != 0;
   const bool bulk = bulk_allowed && hd <= 128;
   const size_t smem = bulk ? (size_t)4 * kPage * hd * 2 : 0;
 #define EMBER_DECODE(LPK)                                                                                           \

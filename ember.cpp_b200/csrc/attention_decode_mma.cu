@@ -500,11 +500,8 @@ int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, 
     if (e != cudaSuccess) return ember_fail("attention_decode_mma: %s", cudaGetErrorString(e));
     configured = true;
   }
-  // EMBER_DECODE_CLUSTER=0 in the environment merges through global scratch and a ticket (for measurements)
-  static const bool cluster_allowed = [] {
-    const char* v = getenv("EMBER_DECODE_CLUSTER");
-    return !(v && v[0] == '0');
-  }();
+  // the option EMBER_OPT_DECODE_CLUSTER switched off merges through global scratch and a ticket (for measurements)
+  const bool cluster_allowed = g_ember_options[EMBER_OPT_DECODE_CLUSTER] != 0;
   const bool cluster = cluster_allowed && n_heads == kv_heads && n_chunks >= 2 && n_chunks <= kMaxCluster;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_chunks, kv_heads, T);

@@ -13,14 +13,15 @@
 // page pages[seq][j / 64] at row j % 64.
 #include "common.cuh"
 
-// One block per token; 16 bytes (4 float32 or 8 bfloat16 values, never across a head since head
-// sizes are multiples of 16) per thread and trip, all of a thread's loads before its stores.
-template <typename T>
+// One block per token; 16 bytes (4 float32 or 8 bfloat16 values, never across a head: VEC is taken
+// only when a head's row is a multiple of 16 bytes) or one value per thread and trip, all of a
+// thread's loads before its stores.
+template <typename T, bool VEC>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                                 const int* __restrict__ positions, const int* __restrict__ token_seq,
                                 const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks,
                                 int q_width, int kv_heads, int hd) {
-  constexpr int kVec = 16 / (int)sizeof(T);
+  constexpr int kVec = VEC ? 16 / (int)sizeof(T) : 1;
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -34,10 +35,16 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T
   for (int i = threadIdx.x * kVec; i < kv_width; i += blockDim.x * kVec) {
     const int h = i / hd, d = i % hd;
     const size_t dst = (((size_t)page * kv_heads + h) * kPage + (p % kPage)) * hd + d;
-    const uint4 k = __ldcg(reinterpret_cast<const uint4*>(src + i));
-    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + kv_width + i));
-    *reinterpret_cast<uint4*>(kc + dst) = k;
-    *reinterpret_cast<uint4*>(vc + dst) = v;
+    if constexpr (VEC) {
+      const uint4 k = __ldcg(reinterpret_cast<const uint4*>(src + i));
+      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + kv_width + i));
+      *reinterpret_cast<uint4*>(kc + dst) = k;
+      *reinterpret_cast<uint4*>(vc + dst) = v;
+    } else {
+      const T k = __ldcg(src + i), v = __ldcg(src + kv_width + i);
+      kc[dst] = k;
+      vc[dst] = v;
+    }
   }
 }
 
@@ -45,18 +52,21 @@ EMBER_API int ember_kv_store(const void* qkv, void* kc, void* vc, const int* pos
                              const int* seq_slot, const int* pages, int max_blocks, int T, int n_heads, int kv_heads,
                              int hd, int dtype, cudaStream_t stream) {
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && hd > 0 && max_blocks > 0, "kv_store: bad sizes");
-  EMBER_CHECK(hd % 16 == 0, "kv_store: head size %d is not a multiple of 16", hd);
+  EMBER_CHECK(dtype == EMBER_F32 || dtype == EMBER_BF16, "kv_store: element type %d", dtype);
   const int qw = n_heads * hd;
+  // 16-byte copies where every head's row, and so every row of the activations, is a multiple of 16 bytes
+  const bool vec = hd * (dtype == EMBER_F32 ? 4 : 2) % 16 == 0;
   cudaError_t e;
-  if (dtype == EMBER_F32)
-    e = launch_pdl(kv_store_kernel<float>, dim3(T), dim3(128), 0, stream, (const float*)qkv, (float*)kc, (float*)vc,
-                   positions, token_seq, seq_slot, pages, max_blocks, qw, kv_heads, hd);
-  else if (dtype == EMBER_BF16)
-    e = launch_pdl(kv_store_kernel<__nv_bfloat16>, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)qkv,
-                   (__nv_bfloat16*)kc, (__nv_bfloat16*)vc, positions, token_seq, seq_slot, pages, max_blocks, qw,
-                   kv_heads, hd);
-  else
-    return ember_fail("kv_store: element type %d", dtype);
+#define EMBER_KV_STORE(T, VEC)                                                                                           \
+  e = launch_pdl(kv_store_kernel<T, VEC>, dim3(T_tokens), dim3(128), 0, stream, (const T*)qkv, (T*)kc, (T*)vc, positions, \
+                 token_seq, seq_slot, pages, max_blocks, qw, kv_heads, hd)
+  const int T_tokens = T;
+  if (dtype == EMBER_F32) {
+    if (vec) EMBER_KV_STORE(float, true); else EMBER_KV_STORE(float, false);
+  } else {
+    if (vec) EMBER_KV_STORE(__nv_bfloat16, true); else EMBER_KV_STORE(__nv_bfloat16, false);
+  }
+#undef EMBER_KV_STORE
   if (e != cudaSuccess) return ember_fail("kv_store: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -69,25 +79,34 @@ EMBER_API int ember_kv_store(const void* qkv, void* kc, void* vc, const int* pos
 // multiplies a probability of zero with those rows.  ember.cpp's kernel tests fill their caches
 // with NaN to catch such reads (tools/window_attention_cuda_test.cu:57-86).
 // grid (sequences, tensors); tails[i] = (page, first row) or (-1, 0).
+template <typename U>  // the unit of a store: 16 bytes where rows are multiples of it, else 4 or 2
 __global__ void clear_tails_kernel(void* const* __restrict__ tensors, const int* __restrict__ tails, int kv_heads,
                                    int row_bytes) {
   const int page = tails[2 * blockIdx.x], row0 = tails[2 * blockIdx.x + 1];
   if (page < 0 || row0 >= kPage) return;
   char* base = static_cast<char*>(tensors[blockIdx.y]);
-  const int vecs = (kPage - row0) * row_bytes / 16;  // a row is a multiple of 16 bytes
+  const int units = (kPage - row0) * row_bytes / (int)sizeof(U);
+  U zero;
+  memset(&zero, 0, sizeof(U));
   for (int h = 0; h < kv_heads; ++h) {
-    uint4* dst = reinterpret_cast<uint4*>(base + (((size_t)page * kv_heads + h) * kPage + row0) * row_bytes);
-    for (int i = threadIdx.x; i < vecs; i += blockDim.x) dst[i] = make_uint4(0, 0, 0, 0);
+    U* dst = reinterpret_cast<U*>(base + (((size_t)page * kv_heads + h) * kPage + row0) * row_bytes);
+    for (int i = threadIdx.x; i < units; i += blockDim.x) dst[i] = zero;
   }
 }
 
 EMBER_API int ember_clear_tails(void* const* tensors, int n_tensors, const int* tails, int n, int kv_heads, int hd,
                                 int elem_bytes, cudaStream_t stream) {
   EMBER_CHECK(n_tensors > 0 && n > 0 && kv_heads > 0 && hd > 0, "clear_tails: bad sizes");
-  EMBER_CHECK((elem_bytes == 2 || elem_bytes == 4) && hd * elem_bytes % 16 == 0, "clear_tails: rows of %d x %d bytes", hd,
-              elem_bytes);
-  EMBER_CHECK(n <= 65535 * 32 && n_tensors <= 65535, "clear_tails: %d sequences x %d tensors exceed one launch", n, n_tensors);
-  clear_tails_kernel<<<dim3(n, n_tensors), 128, 0, stream>>>(tensors, tails, kv_heads, hd * elem_bytes);
+  EMBER_CHECK(elem_bytes == 2 || elem_bytes == 4, "clear_tails: elements of %d bytes", elem_bytes);
+  EMBER_CHECK(n_tensors <= 65535, "clear_tails: %d tensors exceed one launch", n_tensors);
+  const int row_bytes = hd * elem_bytes;
+  const dim3 grid(n, n_tensors);
+  if (row_bytes % 16 == 0)
+    clear_tails_kernel<uint4><<<grid, 128, 0, stream>>>(tensors, tails, kv_heads, row_bytes);
+  else if (row_bytes % 4 == 0)
+    clear_tails_kernel<unsigned><<<grid, 128, 0, stream>>>(tensors, tails, kv_heads, row_bytes);
+  else
+    clear_tails_kernel<unsigned short><<<grid, 128, 0, stream>>>(tensors, tails, kv_heads, row_bytes);
   EMBER_LAUNCH_OK("clear_tails");
   return 0;
 }
@@ -173,8 +192,7 @@ EMBER_API int ember_attention_plain(const void* qkv, const void* kc, const void*
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
-  EMBER_CHECK(hd % 16 == 0 && hd >= 16 && hd <= kMaxHeadDim,
-              "attention: head size %d is not a multiple of 16 in [16, %d]", hd, kMaxHeadDim);
+  EMBER_CHECK(hd >= 1 && hd <= kMaxHeadDim, "attention: head size %d is not in [1, %d]", hd, kMaxHeadDim);
   EMBER_CHECK(window >= 0, "attention: window %d", window);
   const long long items = (long long)T * n_heads;
   const int grid = (int)((items + 3) / 4);

@@ -161,13 +161,27 @@ inline int read(void* dst, unsigned cap) {
 #define EMBER_TIMELINE_READER(file)
 #endif
 
-// EMBER_PDL=0 in the environment launches these kernels the ordinary way (for measurements).
-inline int pdl_allowed() {
-  static const int on = [] {
-    const char* v = getenv("EMBER_PDL");
-    return (v && v[0] == '0') ? 0 : 1;
-  }();
-  return on;
+// Switches that the kernels' launch code reads; `ember_set_option(which, value)` sets them (the
+// Python side does, from its RuntimeOptions).  Process-wide; all on by default.
+//   EMBER_OPT_PDL             programmatic dependent launch between the kernels of a step (0: ordinary launches)
+//   EMBER_OPT_DECODE_BULK     the CUDA-core decode attention brings pages in by bulk copies (0: by loads)
+//   EMBER_OPT_DECODE_CLUSTER  the tensor-core decode attention merges its chunks in a cluster (0: scratch and a ticket)
+enum : int { EMBER_OPT_PDL = 0, EMBER_OPT_DECODE_BULK = 1, EMBER_OPT_DECODE_CLUSTER = 2, EMBER_OPT_COUNT = 3 };
+extern int g_ember_options[EMBER_OPT_COUNT];  // elementwise.cu
+inline int pdl_allowed() { return g_ember_options[EMBER_OPT_PDL]; }
+
+// The number of SMs of the current device (asked once per device; launch heuristics size grids by it).
+inline int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!cached[dev]) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    cached[dev] = n;
+  }
+  return cached[dev];
 }
 
 template <typename... KArgs, typename... Args>

@@ -20,6 +20,14 @@ int ember_fail(const char* fmt, ...) {
 
 EMBER_API const char* ember_last_error() { return g_error; }
 
+int g_ember_options[EMBER_OPT_COUNT] = {1, 1, 1};
+
+EMBER_API int ember_set_option(int which, int value) {
+  EMBER_CHECK(which >= 0 && which < EMBER_OPT_COUNT, "set_option: there is no option %d", which);
+  g_ember_options[which] = value != 0;
+  return 0;
+}
+
 // ---------------------------------------------------------------------------- embedding
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
@@ -149,7 +157,7 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
 EMBER_API int ember_layernorm(const float* x, const float* w, const float* b, void* out, int rows, int d, float eps,
                               int out_dtype, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && d > 0, "layernorm: rows = %d, width = %d", rows, d);
-  const int warps = rows <= 148 ? 1 : 4;  // a decode step's rows: a block each, so that they run on different SMs
+  const int warps = rows <= sm_count() ? 1 : 4;  // a decode step's rows: a block each, so that they run on different SMs
   const int grid = (rows + warps - 1) / warps;
   cudaError_t e;
   const bool early = rows <= 512;  // a decode step's rows: the gain and bias come from DRAM, once per layer

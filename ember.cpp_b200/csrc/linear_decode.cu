@@ -504,7 +504,7 @@ int launch(const void* xin, const float* gamma, const float* beta, float eps, co
   // the blocks still fit the chip at once and keep at least two slices per warp.
   int k_split = 1;
   while (k_split < 4 && all_steps / k_split > 54) k_split *= 2;
-  while (k_split < 4 && tiles * k_split * 2 <= 3 * 148 && all_steps / (k_split * 2) >= 2 * kWarps) k_split *= 2;
+  while (k_split < 4 && tiles * k_split * 2 <= 3 * sm_count() && all_steps / (k_split * 2) >= 2 * kWarps) k_split *= 2;
   const int per_block = (all_steps + k_split - 1) / k_split;
   const size_t smem = (size_t)16 * tile_stride(per_block) * sizeof(__nv_bfloat16) +
                       (size_t)(kWarps + k_split) * 16 * 8 * MT * sizeof(float) + 2 * 16 * sizeof(float) +

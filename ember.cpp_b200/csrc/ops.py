@@ -12,7 +12,6 @@ bfloat16 operands take the tensor-core kernels.
 from __future__ import annotations
 
 import ctypes
-import os
 
 import torch
 
@@ -102,6 +101,10 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = _c_int
+    lib.ember_wait_probe.argtypes = [_c_u64, _c_void]
+    lib.ember_wait_probe.restype = _c_int
+    lib.ember_set_option.argtypes = [_c_int, _c_int]
+    lib.ember_set_option.restype = _c_int
     lib.ember_attention_decode_partials.argtypes = [_c_int] * 5
     lib.ember_attention_decode_partials.restype = _c_size
     for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status",
@@ -115,58 +118,61 @@ def load_library() -> ctypes.CDLL:
 class CudaOps:
     name = "cuda-sm100a"
 
-    def __init__(self):
+    def __init__(self, options=None):
+        """`options`: a RuntimeOptions; None takes the defaults with the EMBER_* variables laid on top."""
+        from ..options import RuntimeOptions
+        self.options = options = options if options is not None else RuntimeOptions.from_env()
         self.lib = load_library()
         self._workspace = None
-        self._bias16: dict[int, torch.Tensor] = {}
         self._partials = None          # scratch of the decode attention: partial results ...
         self._counters = None          # ... and its per-(token, head) counters, zero between calls
         self._retired = []             # outgrown scratch stays alive: captured graphs may still name it
         self.launches = 0
-        self.decode_slots = 6 * torch.cuda.get_device_properties(0).multi_processor_count  # ... that are resident at once
-        # Run a layer norm inside the following product's kernel when it can be.  Off: measured on
-        # GPT-2 XL's shapes a separate norm kernel, overlapped with the product's weight fetch by
-        # programmatic dependent launch, is faster (a step of 12 layers at 8 rows 0.586 against 0.683 ms
-        # with the norm's gain and bias staged beside the weights): every block of the product reads and
-        # norms all the rows again, 300 to 400 times the norm kernel's traffic from L2.
-        self.fuse_norm = os.environ.get("EMBER_FUSE_NORM", "0") == "1"
-        # A decode attention asks the next layer's rows of the cache into L2 (see `attention`).  Off: with
-        # the kernel that loads keys into registers the step's time did not change (0.5822 against 0.5820 ms
-        # of 12 layers); with the tensor-core kernel it grew (0.538 against 0.516 ms; at a context of 900 to
-        # 1,024, 0.605 against 0.551): a layer's rows and weights together do not stay in L2 that long, and
-        # the rows are then fetched twice.
-        self.cache_ahead = os.environ.get("EMBER_CACHE_AHEAD", "0") == "1"
-        # Decode attention on the tensor cores where that kernel has an instantiation (head size 64 or 128,
-        # up to 8 query heads to a key/value head); EMBER_DECODE_MMA=0 takes the other kernel (for measurements).
-        self.decode_mma = os.environ.get("EMBER_DECODE_MMA", "1") == "1"
-        # The norm that follows a sum into the residual stream can run in the tail of that sum's product
-        # (few rows in bfloat16): `expect_norm` announces it, `layernorm` then finds its result ready.
-        # Off: measured on GPT-2 XL's shape at batch 8 it changes nothing (0.780 against 0.782 ms a step
-        # of 12 layers): the separate norm kernels already hide behind the next product's weight fetch.
-        self.tail_norm = os.environ.get("EMBER_TAIL_NORM", "0") == "1"
+        self.sms = torch.cuda.get_device_properties(0).multi_processor_count
+        self.decode_slots = 6 * self.sms   # blocks of the decode attention that are resident at once
+        # What the switches are and why their defaults are what they are (all measured on GPT-2 XL's shapes):
+        # fuse_norm: a layer norm inside the following product's kernel.  Off: a separate norm kernel, overlapped
+        #   with the product's weight fetch by programmatic dependent launch, is faster (a step of 12 layers at 8
+        #   rows 0.586 against 0.683 ms with the norm's gain and bias staged beside the weights): every block of
+        #   the product reads and norms all the rows again, 300 to 400 times the norm kernel's traffic from L2.
+        self.fuse_norm = options.fuse_norm
+        # cache_ahead: a decode attention asks the next layer's rows of the cache into L2.  Off: with the kernel
+        #   that loads keys into registers the step's time did not change (0.5822 against 0.5820 ms of 12 layers);
+        #   with the tensor-core kernel it grew (0.538 against 0.516 ms): a layer's rows and weights together do
+        #   not stay in L2 that long, and the rows are then fetched twice.
+        self.cache_ahead = options.cache_ahead
+        # decode_mma: decode attention on the tensor cores where that kernel has an instantiation (head size 64
+        #   or 128, up to 8 query heads to a key/value head); off takes the other kernel.
+        self.decode_mma = options.decode_mma
+        # tail_norm: the norm that follows a sum into the residual stream runs in the tail of that sum's product
+        #   (`expect_norm` announces it, `layernorm` then finds its result ready).  Off: at batch 8 it changes
+        #   nothing (0.780 against 0.782 ms a step of 12 layers): the separate norm kernels already hide behind
+        #   the next product's weight fetch.
+        self.tail_norm = options.tail_norm
         self._expected = None          # (gain, bias, eps, dtype) announced for the next sum
         self._warm = None              # tensor announced by `warm` for the next product
-        # The second product of a feed-forward has its weights landed about a microsecond earlier with it
-        # (its blocks cannot be resident beside the first product's); a step of 12 layers 0.519 against
-        # 0.521 ms.  Warming the next block's first weights during that second product as well gained nothing.
-        self.warm_ahead = os.environ.get("EMBER_WARM", "1") == "1"
+        # warm: the second product of a feed-forward has its weights landed about a microsecond earlier with it
+        #   (its blocks cannot be resident beside the first product's); a step of 12 layers 0.519 against 0.521 ms.
+        self.warm_ahead = options.warm
         self._normed = None            # (stream ptr, gain ptr, bias ptr, eps, dtype, result) of the last tail norm
         self._tail_counter = None
-        # Products of more than SMALL_M rows go to cuBLASLt ("lt"), as ember.cpp's own go to cuBLAS, or
-        # with EMBER_GEMM=tc in the environment, above TC_MIN_M rows, to this library's tcgen05 kernel.
-        # Measured on GPT-2 XL's four products the library is ahead: at 2,048 rows 133 against 205
-        # microseconds a layer, at 16,384 rows the tcgen05 kernel reaches 87 % of it on the QKV product.
-        self.gemm = os.environ.get("EMBER_GEMM", "lt")
-        # Products of SMALL_M + 1 to STREAM_M rows stream the weights through this library's tcgen05 kernel with
-        # the operands swapped (linear_stream.cu); EMBER_LINEAR_STREAM=0 sends them to cuBLASLt (for measurements).
-        self.linear_stream_on = os.environ.get("EMBER_LINEAR_STREAM", "1") == "1"
-        self.lt_tune = os.environ.get("EMBER_LT_TUNE", "1") != "0"
+        # gemm: products of more than STREAM_M rows go to cuBLASLt ("lt"), as ember.cpp's own go to cuBLAS, or
+        #   ("tc"), above TC_MIN_M rows, to this library's tcgen05 kernel.  On GPT-2 XL's four products the
+        #   library is ahead at 2,048 rows; at 16,384 rows the tcgen05 kernel reaches 95 % of it on the QKV product.
+        self.gemm = options.gemm
+        # lt_tune: the first product of a shape times the library's candidate algorithms; `deterministic` turns
+        #   it off, so that the choice does not depend on a timing
+        self.lt_tune = options.lt_tune
         self._lt_tuned = set()
-        # Prefill attention with head size 64 runs on the tcgen05 kernel; EMBER_ATTENTION=mma keeps it
-        # on the mma.sync kernel (which takes every other head size anyway).
-        self.attention_tc = os.environ.get("EMBER_ATTENTION", "tc") != "mma"
-        if self.gemm not in ("tc", "lt"):
-            raise KernelError(f"EMBER_GEMM={self.gemm!r}: 'tc' (this library's tcgen05 kernel) or 'lt' (cuBLASLt)")
+        # linear_stream: products of SMALL_M + 1 to STREAM_M rows stream the weights through this library's tcgen05
+        #   kernel with the operands swapped (linear_stream.cu); off sends them to cuBLASLt.
+        self.linear_stream_on = options.linear_stream
+        # attention: prefill attention with head size 64 on the tcgen05 kernel, or ("mma") on the mma.sync kernel
+        #   (which takes every other head size anyway)
+        self.attention_tc = options.attention == "tc"
+        # the three switches that the kernels' launch code reads (process-wide)
+        for which, value in ((0, options.pdl), (1, options.decode_bulk), (2, options.decode_cluster)):
+            self.lib.ember_set_option(which, 1 if value else 0)
 
     # ------------------------------------------------------------------ helpers
     def _call(self, name: str, *args, allow=()) -> int:
@@ -202,12 +208,16 @@ class CudaOps:
             self._workspace = torch.empty(_LT_WORKSPACE, dtype=torch.uint8, device="cuda")
         return self._workspace
 
-    def _bias_bf16(self, bias: torch.Tensor) -> torch.Tensor:
-        key = bias.data_ptr()
-        cached = self._bias16.get(key)
-        if cached is None or cached.shape != bias.shape:
-            cached = self._bias16[key] = bias.to(torch.bfloat16)
-        return cached
+    @staticmethod
+    def _bias_bf16(bias: torch.Tensor) -> torch.Tensor:
+        """The bfloat16 copy of a bias that cuBLASLt's epilogue reads.  It is kept on the bias tensor itself
+        (made once, dies with it): a cache keyed by address would hand a freed model's copy to a new model
+        whose bias landed on the same address."""
+        copy = getattr(bias, "_ember_bf16", None)
+        if copy is None or copy.shape != bias.shape or copy.device != bias.device:
+            copy = bias.to(torch.bfloat16)
+            bias._ember_bf16 = copy
+        return copy
 
     # ------------------------------------------------------------------ rows
     def embed(self, tokens, positions, table, pos_table):
@@ -390,6 +400,12 @@ class CudaOps:
                    M, w.shape[0], K, _ACT[act], _code(out.dtype), int(k_split), int(stages))
         return out
 
+    def wait_probe(self, limit_ns: int = 1_000_000) -> None:
+        """Launches the kernel whose only wait nothing ends (wait_probe.cu): it gives up after `limit_ns`
+        and leaves code 31 in the status word, which the next `check()` raises for.  For tests of the
+        kernels' bounded waits; nothing faults or hangs."""
+        self._call("ember_wait_probe", int(limit_ns))
+
     def check(self) -> None:
         """Raises if a kernel with bounded waits gave up since the last call.  The caller has
         synchronized with the device (it has just read a step's results)."""
@@ -399,8 +415,9 @@ class CudaOps:
             raise KernelError("attention_decode: a block gave up waiting for its copies of keys and values; the results of that launch are not valid")
         code = self.lib.ember_tc_status()
         if code:
-            kernel = "linear_tc" if code < 10 else ("attention_prefill_tc" if code < 20 else "linear_stream")
-            role = {1: "the TMA producer", 2: "the product issuer", 3: "the epilogue", 4: "copies in flight",
+            kernel = "linear_tc" if code < 10 else ("attention_prefill_tc" if code < 20 else
+                                                    ("linear_stream" if code < 30 else "wait_probe"))
+            role = {31: "the probe's wait, as it is meant to",1: "the TMA producer", 2: "the product issuer", 3: "the epilogue", 4: "copies in flight",
                     11: "the TMA loader", 12: "the product issuer", 13: "the softmax warps",
                     21: "the TMA producer", 22: "the product issuer", 23: "the epilogue", 24: "copies in flight"}.get(code, code)
             raise KernelError(f"{kernel}: a wait ran out ({role}); the results of that launch are not valid")

@@ -44,7 +44,7 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
 // loop is one function for the whole kernel, not a copy at every wait: these kernels run their code
 // once, straight through, and a kernel of 96 KB (what inlined, unrolled polling loops made of the
 // weight-streaming product) waits on its instruction fetches.
-static __device__ __noinline__ bool mbar_wait_poll(unsigned bar, unsigned parity) {
+static __device__ __noinline__ bool mbar_wait_poll(unsigned bar, unsigned parity, unsigned long long limit_ns) {
   unsigned long long t0, t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
   for (;;) {
@@ -52,12 +52,13 @@ static __device__ __noinline__ bool mbar_wait_poll(unsigned bar, unsigned parity
     for (int i = 0; i < 256; ++i)
       if (mbar_try(bar, parity)) return true;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    if (t - t0 > kWaitNs) return false;
+    if (t - t0 > limit_ns) return false;
   }
 }
-__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+// (the limit is a parameter so that a test can make a wait run out in a millisecond: wait_probe.cu)
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, unsigned long long limit_ns = kWaitNs) {
   if (mbar_try(bar, parity)) return true;
-  return mbar_wait_poll(bar, parity);
+  return mbar_wait_poll(bar, parity, limit_ns);
 }
 
 // One box of a tensor map into this block's shared memory; completion counted on `bar`.  No

@@ -18,6 +18,7 @@ import torch
 
 from ..cache.sequence_cache import CacheError, SequenceCache
 from ..config.base import ModelConfig, get_architecture, load_config
+from ..options import RuntimeOptions
 from ..parts.model import DecoderModel
 from ..parts.spec import ModelSpec
 from ..weights.loader import check_tensors, load_checked
@@ -100,26 +101,40 @@ class Engine:
         self.counters = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0}
 
     # ------------------------------------------------------------------ construction
-    @classmethod
-    def from_folder(cls, folder: str, dtype="bfloat16", max_tokens: int = 4096, device="cuda", ops=None,
-                    max_slots: int | None = None, cuda_graphs: bool = True) -> "Engine":
-        """Config, model class and weights from `<folder>/config.json` and `model.safetensors`."""
-        config = load_config(folder)
-        spec = get_architecture(config.architecture).build_spec(config)
-        model = DecoderModel(spec)
-        runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
-        tensors = load_checked(folder, model.weight_specs(), spec.ignored_tensors)
-        model.load(tensors, runtime)
-        return cls(model, runtime, max_tokens, max_slots, config, cuda_graphs)
+    @staticmethod
+    def _options(options, dtype, max_tokens, max_slots, cuda_graphs) -> RuntimeOptions:
+        """The options an engine runs with: `options` (default: the defaults with the EMBER_*
+        variables laid on top), with the arguments that were given in their own right on top."""
+        base = options if options is not None else RuntimeOptions.from_env()
+        return base.replace(dtype=dtype, max_tokens=max_tokens, max_slots=max_slots, cuda_graphs=cuda_graphs)
 
     @classmethod
-    def from_spec(cls, spec: ModelSpec, tensors: dict, dtype="bfloat16", max_tokens: int = 4096, device="cuda",
-                  ops=None, max_slots: int | None = None, cuda_graphs: bool = True) -> "Engine":
-        """A model given as data, with its tensors by name (how tests build toy models)."""
+    def from_folder(cls, folder: str, dtype=None, max_tokens: int | None = None, device="cuda", ops=None,
+                    max_slots: int | None = None, cuda_graphs: bool | None = None,
+                    options: RuntimeOptions | None = None) -> "Engine":
+        """Config, model class and weights from `<folder>/config.json` and `model.safetensors`.
+        `options`: a RuntimeOptions (compute type, cache size, kernel switches); dtype, max_tokens,
+        max_slots and cuda_graphs given here override its fields."""
+        opt = cls._options(options, dtype, max_tokens, max_slots, cuda_graphs)
+        config = load_config(folder)
+        config.check_dtype(opt.dtype)
+        spec = get_architecture(config.architecture).build_spec(config)
         model = DecoderModel(spec)
-        runtime = Runtime(dtype, device, ops if ops is not None else _cuda_ops())
-        model.load(check_tensors("tensors", tensors, model.weight_specs(), spec.ignored_tensors), runtime)
-        return cls(model, runtime, max_tokens, max_slots, None, cuda_graphs)
+        runtime = Runtime(opt.dtype, device, ops if ops is not None else _cuda_ops(opt))
+        tensors = load_checked(folder, model.weight_specs(), spec.ignored_tensors, spec.strip_prefixes)
+        model.load(tensors, runtime)
+        return cls(model, runtime, opt.max_tokens, opt.max_slots, config, opt.cuda_graphs)
+
+    @classmethod
+    def from_spec(cls, spec: ModelSpec, tensors: dict, dtype=None, max_tokens: int | None = None, device="cuda",
+                  ops=None, max_slots: int | None = None, cuda_graphs: bool | None = None,
+                  options: RuntimeOptions | None = None) -> "Engine":
+        """A model given as data, with its tensors by name (how tests build toy models)."""
+        opt = cls._options(options, dtype, max_tokens, max_slots, cuda_graphs)
+        model = DecoderModel(spec)
+        runtime = Runtime(opt.dtype, device, ops if ops is not None else _cuda_ops(opt))
+        model.load(check_tensors("tensors", tensors, model.weight_specs(), spec.ignored_tensors, spec.strip_prefixes), runtime)
+        return cls(model, runtime, opt.max_tokens, opt.max_slots, None, opt.cuda_graphs)
 
     # ------------------------------------------------------------------ sequences
     def open(self) -> int:
@@ -335,6 +350,6 @@ class _DecodeGraph:
             engine.ops.launches += self.launches
 
 
-def _cuda_ops():
+def _cuda_ops(options=None):
     from ..csrc.ops import CudaOps
-    return CudaOps()
+    return CudaOps(options)

@@ -1,0 +1,113 @@
+"""Every switch of the runtime in one typed place.
+
+ember.cpp reads its switches from environment variables, each once, and documents them in one
+table (docs/USAGE.md:242-271); `EMBER_DETERMINISTIC` pins the algorithms its libraries may
+otherwise choose between (determinism.h:17-35).  Here the switches are the fields of
+`RuntimeOptions`.  An engine, a session and the kernels take one; the environment variables of the
+same meaning are overrides that `RuntimeOptions.from_env()` applies on top of the defaults (or of
+options given in code), so a measurement can flip a switch without touching the program.
+
+  field            variable               meaning
+  dtype            EMBER_DTYPE            compute type: bfloat16 (the fast kernels) or float32 (everything in true 32-bit)
+  max_tokens       EMBER_MAX_TOKENS       positions the cache holds over all live sequences, each rounded up to 64
+  max_slots        EMBER_MAX_SLOTS        most live sequences (default: as many as the cache has pages)
+  cuda_graphs      EMBER_CUDA_GRAPHS      one-token steps replay a captured graph (0: launch by launch)
+  deterministic    EMBER_DETERMINISTIC    no choice is made by timing: the library products take the heuristic's first
+                                          algorithm, so two processes give the same bits (it implies lt_tune = False)
+  gemm             EMBER_GEMM             products of more than 64 rows: "lt" cuBLASLt (as ember.cpp's go to cuBLAS), "tc" this
+                                          library's tcgen05 kernel
+  lt_tune          EMBER_LT_TUNE          time cuBLASLt's candidate algorithms once per shape and keep the fastest
+  linear_stream    EMBER_LINEAR_STREAM    products of 17 to 64 rows on the tcgen05 weight-streaming kernel (0: cuBLASLt)
+  attention        EMBER_ATTENTION        bfloat16 prefill attention at head size 64: "tc" tcgen05, "mma" the mma.sync kernel
+  decode_mma       EMBER_DECODE_MMA       bfloat16 decode attention on the tensor cores where it has an instantiation
+  decode_cluster   EMBER_DECODE_CLUSTER   its chunks merge in a thread-block cluster (0: through scratch and a ticket)
+  decode_bulk      EMBER_DECODE_BULK      the CUDA-core decode attention brings pages in by bulk copies (0: by loads)
+  pdl              EMBER_PDL              programmatic dependent launch between the kernels of a step
+  fuse_norm        EMBER_FUSE_NORM        a layer norm runs in the prologue of the product after it (few rows)
+  tail_norm        EMBER_TAIL_NORM        a layer norm runs in the tail of the product before it (few rows)
+  cache_ahead      EMBER_CACHE_AHEAD      a decode attention asks the next layer's rows of the cache into L2
+  warm             EMBER_WARM             a small product asks the next product's weights into L2
+
+The kernel switches are measurement switches: the defaults are what measured fastest, and every
+combination computes the same function.  The three that the launch code of the kernels reads
+(pdl, decode_cluster, decode_bulk) are process-wide: the options of the `CudaOps` made last win.
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+
+
+class OptionError(ValueError):
+    pass
+
+
+def _flag(text: str, name: str) -> bool:
+    if text.strip().lower() in ("1", "true", "yes", "on"):
+        return True
+    if text.strip().lower() in ("0", "false", "no", "off"):
+        return False
+    raise OptionError(f"{name}={text!r}: expected 0 or 1")
+
+
+@dataclasses.dataclass(frozen=True)
+class RuntimeOptions:
+    dtype: str = "bfloat16"
+    max_tokens: int = 4096
+    max_slots: int | None = None
+    cuda_graphs: bool = True
+    deterministic: bool = False
+    gemm: str = "lt"
+    lt_tune: bool = True
+    linear_stream: bool = True
+    attention: str = "tc"
+    decode_mma: bool = True
+    decode_cluster: bool = True
+    decode_bulk: bool = True
+    pdl: bool = True
+    fuse_norm: bool = False
+    tail_norm: bool = False
+    cache_ahead: bool = False
+    warm: bool = True
+
+    def __post_init__(self):
+        if self.dtype not in ("bfloat16", "bf16", "float32", "fp32"):
+            raise OptionError(f"dtype = {self.dtype!r}: 'bfloat16' or 'float32'")
+        if self.gemm not in ("lt", "tc"):
+            raise OptionError(f"gemm = {self.gemm!r}: 'tc' (this library's tcgen05 kernel) or 'lt' (cuBLASLt)")
+        if self.attention not in ("tc", "mma"):
+            raise OptionError(f"attention = {self.attention!r}: 'tc' (tcgen05) or 'mma' (mma.sync)")
+        if self.max_tokens <= 0 or (self.max_slots is not None and self.max_slots <= 0):
+            raise OptionError(f"max_tokens = {self.max_tokens}, max_slots = {self.max_slots}: both positive")
+        if self.deterministic and self.lt_tune:
+            object.__setattr__(self, "lt_tune", False)      # a choice by timing is not reproducible
+
+    @staticmethod
+    def variable(field: str) -> str:
+        return "EMBER_" + field.upper()
+
+    @classmethod
+    def from_env(cls, base: "RuntimeOptions | None" = None, environ=None) -> "RuntimeOptions":
+        """`base` (default: the defaults) with every EMBER_* variable that is set laid on top."""
+        environ = os.environ if environ is None else environ
+        values = dataclasses.asdict(base) if base is not None else {}
+        for f in dataclasses.fields(cls):
+            name = cls.variable(f.name)
+            text = environ.get(name)
+            if text is None:
+                continue
+            if f.type in ("bool", bool):
+                values[f.name] = _flag(text, name)
+            elif f.name in ("max_tokens", "max_slots"):
+                try:
+                    values[f.name] = int(text)
+                except ValueError:
+                    raise OptionError(f"{name}={text!r}: expected a whole number") from None
+            else:
+                values[f.name] = text
+        if values.get("deterministic"):
+            values["lt_tune"] = False
+        return cls(**values)
+
+    def replace(self, **changes) -> "RuntimeOptions":
+        return dataclasses.replace(self, **{k: v for k, v in changes.items() if v is not None})

@@ -23,8 +23,8 @@ class CausalAttention(Mixer):
         super().__init__(prefix)
         if n_heads % kv_heads:
             raise ValueError(f"attention {prefix!r}: {n_heads} heads are not a multiple of {kv_heads} key/value heads")
-        if head_dim % 16 or not 16 <= head_dim <= 256:
-            raise ValueError(f"attention {prefix!r}: head size {head_dim} is not a multiple of 16 in [16, 256]")
+        if not 1 <= head_dim <= 256:
+            raise ValueError(f"attention {prefix!r}: head size {head_dim} is not in [1, 256]")
         if stored not in ("in_out", "out_in"):
             raise ValueError(f"attention {prefix!r}: stored = {stored!r}")
         self.width, self.n_heads, self.kv_heads, self.head_dim = int(width), int(n_heads), int(kv_heads), int(head_dim)
@@ -47,6 +47,12 @@ class CausalAttention(Mixer):
         return specs
 
     def load(self, get, runtime):
+        import torch
+        if runtime.dtype == torch.bfloat16 and (self.head_dim % 16 or self.width % 8):
+            # (the true 32-bit path takes every head size up to 256 and every width)
+            raise ValueError(f"attention {self.prefix!r}: the bfloat16 kernels take head sizes that are multiples of 16 "
+                             f"and widths that are multiples of 8 (here {self.head_dim} and {self.width}); "
+                             "the float32 path takes this model")
         t = self.stored == "in_out"
         self.w_qkv = runtime.matrix(get(self.qkv_name + ".weight"), transpose=t)
         self.w_out = runtime.matrix(get(self.out_name + ".weight"), transpose=t)

@@ -40,6 +40,10 @@ class DenseFeedForward(FeedForward):
         return specs
 
     def load(self, get, runtime):
+        import torch
+        if runtime.dtype == torch.bfloat16 and (self.inner % 8 or self.width % 8):
+            raise ValueError(f"feed-forward {self.prefix!r}: the bfloat16 kernels take widths that are multiples of 8 "
+                             f"(rows of 16 bytes; here width {self.width}, inner {self.inner}); the float32 path takes this model")
         t = self.stored == "in_out"
         self.w_up = runtime.matrix(get(self.up_name + ".weight"), transpose=t)
         self.w_down = runtime.matrix(get(self.down_name + ".weight"), transpose=t)

@@ -57,6 +57,9 @@ class ModelSpec:
     stop_token_ids: tuple[int, ...] = ()
     # tensors that a checkpoint may hold and the model does not use (regular expressions)
     ignored_tensors: tuple[str, ...] = ()
+    # prefixes that a checkpoint's tensor names may carry in front of the names the parts use (a
+    # wrapper module's name); a detail of the architecture's checkpoints, so it stands here
+    strip_prefixes: tuple[str, ...] = ()
 
     def check(self) -> None:
         if not self.layers:

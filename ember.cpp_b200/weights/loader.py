@@ -13,7 +13,7 @@ import re
 import torch
 
 from ..parts.base import WeightSpec
-from .safetensors_io import read_folder
+from .safetensors_io import UnreadTensor, read_folder
 
 
 class WeightError(ValueError):
@@ -42,8 +42,10 @@ def _strip(name: str, prefixes) -> str:
 
 
 def check_tensors(where: str, tensors: dict[str, torch.Tensor], specs: list[WeightSpec], ignored=(),
-                  strip_prefixes=("transformer.",)) -> dict[str, torch.Tensor]:
-    """Returns name -> tensor for exactly the wanted names, or raises one WeightError."""
+                  strip_prefixes=()) -> dict[str, torch.Tensor]:
+    """Returns name -> tensor for exactly the wanted names, or raises one WeightError.  `ignored`
+    and `strip_prefixes` come from the architecture's ModelSpec.  A tensor whose stored type the
+    reader does not know (`UnreadTensor`) is an error only if the model wants it."""
     have = {_strip(k, strip_prefixes): v for k, v in tensors.items()}
     want = {s.name: s for s in specs}
     missing = [n for n in want if n not in have]
@@ -53,7 +55,9 @@ def check_tensors(where: str, tensors: dict[str, torch.Tensor], specs: list[Weig
                    if n in have and tuple(have[n].shape) != tuple(want[n].shape)]
     wrong_type = []
     for n, s in want.items():
-        if n in have:
+        if n in have and isinstance(have[n], UnreadTensor):
+            wrong_type.append((n, f"stored as {have[n].dtype_name}, which this library does not read"))
+        elif n in have:
             is_int = not have[n].dtype.is_floating_point
             if is_int != s.integer:
                 wrong_type.append((n, f"{have[n].dtype}, expected {'an integer' if s.integer else 'a floating'} type"))
@@ -62,5 +66,5 @@ def check_tensors(where: str, tensors: dict[str, torch.Tensor], specs: list[Weig
     return {n: have[n] for n in want}
 
 
-def load_checked(folder: str, specs: list[WeightSpec], ignored=()) -> dict[str, torch.Tensor]:
-    return check_tensors(folder, read_folder(folder), specs, ignored)
+def load_checked(folder: str, specs: list[WeightSpec], ignored=(), strip_prefixes=()) -> dict[str, torch.Tensor]:
+    return check_tensors(folder, read_folder(folder), specs, ignored, strip_prefixes)

@@ -27,6 +27,16 @@ class SafetensorsError(ValueError):
     pass
 
 
+class UnreadTensor:
+    """A tensor of the file whose stored type this library does not read (BOOL, U8, F64, ...): its
+    name, shape and type are known, its values are not fetched.  Checkpoints carry such tensors as
+    buffers that no model wants (GPT-2's causal mask is saved as BOOL or U8 by some writers); the
+    loader complains only if a model asks for one."""
+
+    def __init__(self, dtype_name: str, shape):
+        self.dtype_name, self.shape = dtype_name, tuple(shape)
+
+
 def read_header(path: str) -> tuple[dict, int]:
     size = os.path.getsize(path)
     with open(path, "rb") as f:
@@ -58,10 +68,11 @@ def read_file(path: str) -> dict[str, torch.Tensor]:
         if name == "__metadata__":
             continue
         dt = str(meta.get("dtype", "")).upper()
-        if dt not in _DTYPES:
-            raise SafetensorsError(f"{path}: tensor {name!r} has unsupported dtype {meta.get('dtype')!r}")
-        tdt, width = _DTYPES[dt]
         shape = [int(s) for s in meta["shape"]]
+        if dt not in _DTYPES:
+            out[name] = UnreadTensor(str(meta.get("dtype")), shape)
+            continue
+        tdt, width = _DTYPES[dt]
         begin, end = (int(v) for v in meta["data_offsets"])
         numel = 1
         for s in shape:

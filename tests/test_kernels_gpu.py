@@ -570,9 +570,19 @@ def test_attention_window_edge(ops, dtype):
 
 def test_attention_refuses_sizes_it_cannot_run(ops):
     from ember_cpp_b200.csrc.ops import KernelError
-    for heads, kv, hd in [(4, 4, 24), (4, 3, 32), (2, 2, 512)]:
+    for heads, kv, hd in [(4, 3, 32), (2, 2, 512)]:
         with pytest.raises((KernelError, ValueError)):
             run_attention(ops, [(0, 4)], heads, kv, hd, "float32")
+    with pytest.raises(KernelError, match="head size"):        # one token each in bfloat16: the decode kernels want 16s
+        run_attention(ops, [(3, 1)], 2, 2, 24, "bfloat16")
+
+
+@pytest.mark.parametrize("hd", [12, 24, 1, 250])
+def test_attention_in_32_bit_takes_every_head_size(ops, hd):
+    """The plain kernels of the 32-bit path (scalar copies where a head's row is no multiple of 16 bytes):
+    prompts, tokens on top of a cache, one token each, NaN in every row that no query may see."""
+    got, want = run_attention(ops, [(0, 70), (65, 3), (130, 1), (0, 1)], 3, 3, hd, "float32", seed=hd, poison=NAN)
+    assert (got - want).abs().max().item() < ATOL["float32"]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -679,6 +689,32 @@ def test_decode_attention_window_edge_and_own_key(hd, mma, p):
                                   poison=NAN, store_apart=apart)
         assert (got - rounded(p / 8)).abs().max().item() < 5e-2, ("own", apart)
     ops.check()
+
+
+# ------------------------------------------------------------------------------ bounded waits
+def test_a_wait_that_runs_out_is_reported_and_harms_nothing(ops):
+    """The kernels' waits on mbarriers give up after a time limit and say so in a status word instead of
+    hanging.  A kernel whose only wait nothing ever ends (wait_probe.cu, the same tc::mbar_wait with a limit
+    of a millisecond) returns; `check()` raises and names it, once; the launches after it work."""
+    import time
+    from ember_cpp_b200.csrc.ops import KernelError
+    torch.cuda.synchronize()
+    ops.check()
+    t0 = time.perf_counter()
+    ops.wait_probe(1_000_000)
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 1.0                 # it gave up after its millisecond, not after the kernels' two seconds
+    with pytest.raises(KernelError, match="wait_probe"):
+        ops.check()
+    ops.check()                                           # the word is cleared by reading it
+    a, w = gen((40, 256), 70, torch.bfloat16), gen((300, 256), 71, torch.bfloat16, 0.1)
+    got = ops.linear(a, w, None, out_dtype=torch.float32)  # a tcgen05 kernel right after: the context is fine
+    torch.cuda.synchronize()
+    ops.check()
+    want = a.double() @ w.double().t()
+    assert (got.double() - want).abs().max().item() / want.abs().max().item() < 2e-4
+    with pytest.raises(KernelError, match="limit"):
+        ops.wait_probe(10)
 
 
 # ------------------------------------------------------------------------------ sampling

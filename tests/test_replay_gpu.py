@@ -142,3 +142,107 @@ def test_replay_writes_nothing_where_nothing_is_wanted(tiny_folders, plains, tmp
     got = rp.step([("x", [ids[11]], [0]), ("y", [ids[1]], [])], end=["y"]).reshape(1, -1)
     rp.close()
     assert rel_error(got, plain.logits(ids[:12])[11:]) < TOL["float32"]
+
+
+# ------------------------------------------------------------------------------ GPT-2 XL's layer sizes
+XL_LAYERS = dict(vocab_size=50257, n_positions=1024, n_embd=1600, n_layer=2, n_head=25, n_inner=6400,
+                 activation_function="gelu_new", layer_norm_epsilon=1e-5, tie_word_embeddings=True)
+XL_LENGTHS = (700, 520, 130, 64)          # two of them hold more than 8 pages: the decode attention is cut into chunks
+XL_BATCHES = [[0, 2], [1, 3]]
+
+
+@pytest.fixture(scope="module")
+def xl_folder(tmp_path_factory):
+    """A model folder with the layer sizes of GPT-2 XL (width 1,600, 25 heads of 64, inner 6,400, vocabulary
+    50,257) and two layers, random weights."""
+    import ember_cpp_b200 as E
+    folder = str(tmp_path_factory.mktemp("xl_layers"))
+    E.write_random_model(folder, E.GPT2Config.from_dict(XL_LAYERS), seed=2)
+    return folder
+
+
+def kept(n):
+    """The positions of a request of n tokens whose rows are compared: the first ones, page edges, one in 61, the last 40."""
+    return sorted({p for p in (0, 1, 2, 63, 64, 65, 127, 128) if p < n} | set(range(0, n, 61)) | set(range(max(0, n - 40), n)))
+
+
+def replay_kept(rp, seqs, vocab, way):
+    """Feeds the requests in one of the three ways and returns, per request, {position: row} for kept(n)."""
+    out = [dict() for _ in seqs]
+
+    def feed(entries, end=()):
+        """entries: (request, first position, count); wants the kept positions among them."""
+        wants = [[p - a for p in kept(len(seqs[i])) if a <= p < a + n] for i, a, n in entries]
+        flat = rp.step([(f"{way}{i}", seqs[i][a:a + n], w) for (i, a, n), w in zip(entries, wants)], end=[f"{way}{i}" for i in end])
+        if flat is None:
+            return
+        flat = flat.reshape(-1, vocab)
+        at = 0
+        for (i, a, n), w in zip(entries, wants):
+            for r in w:
+                out[i][a + r] = flat[at]
+                at += 1
+
+    if way == "w":
+        for i, ids in enumerate(seqs):
+            feed([(i, 0, len(ids))], end=[i])
+    elif way == "t":
+        for i, ids in enumerate(seqs):
+            head = max(1, len(ids) - 32)
+            feed([(i, 0, head)], end=[i] if head == len(ids) else [])
+            for t in range(head, len(ids)):
+                feed([(i, t, 1)], end=[i] if t == len(ids) - 1 else [])
+    else:
+        for batch in XL_BATCHES:
+            fed = {i: max(1, len(seqs[i]) // 2) for i in batch}
+            feed([(i, 0, fed[i]) for i in batch])
+            live = list(batch)
+            while live:
+                feed([(i, fed[i], 1) for i in live], end=[i for i in live if fed[i] + 1 == len(seqs[i])])
+                for i in live:
+                    fed[i] += 1
+                live = [i for i in live if fed[i] < len(seqs[i])]
+    return out
+
+
+def test_replay_three_ways_at_gpt2_xl_layer_sizes(xl_folder, tmp_path):
+    """The benchmark's layer sizes through bin/trace_run in all three cuts: the tensor-core decode attention with
+    its chunk merges, the tcgen05 prefill attention, the weight-streaming products at their real shapes, several
+    buckets of lengths.  32-bit: the three cuts give the same bits, and rows within 1e-5 of the plain implementation
+    with its top-1.  bfloat16: every cut within 8e-3 of the 32-bit rows, and the same top-1 wherever the 32-bit
+    row's margin is wider than that."""
+    import plain_gpt2
+    plain = plain_gpt2.PlainGPT2(xl_folder)
+    V = plain.vocab
+    seqs = [random_ids(900 + i, V, n) for i, n in enumerate(XL_LENGTHS)]
+    need = max(sum(-(-len(seqs[i]) // 64) * 64 for i in b) for b in XL_BATCHES)
+    rows = {}
+    for dtype in ("float32", "bfloat16"):
+        out = tmp_path / dtype
+        rp = Replay(xl_folder, dtype, out, need)
+        rows[dtype] = {way: replay_kept(rp, seqs, V, way) for way in ("w", "t", "b")}
+        rp.close()
+    exact = rows["float32"]
+    for i, ids in enumerate(seqs):
+        ref = plain.logits(ids)
+        assert sorted(exact["w"][i]) == kept(len(ids))
+        for way in ("w", "t", "b"):
+            assert sorted(exact[way][i]) == kept(len(ids)), (way, i)
+            for p in kept(len(ids)):
+                assert np.array_equal(exact[way][i][p], exact["w"][i][p]), (way, i, p)      # the cut changes no bit
+        got = np.stack([exact["w"][i][p] for p in kept(len(ids))])
+        want = ref[kept(len(ids))]
+        assert rel_error(got, want) < TOL["float32"], (i, rel_error(got, want))
+        assert (got.argmax(-1) == want.argmax(-1)).all(), i
+    wide = 0
+    for way in ("w", "t", "b"):
+        for i, ids in enumerate(seqs):
+            got = np.stack([rows["bfloat16"][way][i][p] for p in kept(len(ids))])
+            want = np.stack([exact["w"][i][p] for p in kept(len(ids))])
+            assert rel_error(got, want) < TOL["bfloat16"], (way, i, rel_error(got, want))
+            top2 = np.sort(want, axis=-1)[:, -2:]
+            margin = (top2[:, 1] - top2[:, 0]) / (want.max(-1) - want.min(-1))
+            sure = margin > 2 * TOL["bfloat16"]
+            wide += int(sure.sum())
+            assert (got.argmax(-1)[sure] == want.argmax(-1)[sure]).all(), (way, i)
+    assert wide > 0            # some rows did have a margin wider than the tolerance: the top-1 check ran

@@ -9,8 +9,8 @@ import torch
 import ember_cpp_b200 as E
 from ember_cpp_b200.config import get_architecture
 from ember_cpp_b200.parts import DecoderModel
-from ember_cpp_b200.weights import (SafetensorsError, WeightError, check_tensors, load_checked, random_tensors, read_file,
-                                    read_folder, write_file)
+from ember_cpp_b200.weights import (SafetensorsError, UnreadTensor, WeightError, check_tensors, load_checked, random_tensors,
+                                    read_file, read_folder, read_header, write_file)
 
 from conftest import TINY
 
@@ -59,8 +59,8 @@ def test_container_errors(tmp_path):
         read_file(str(p))
     head = json.dumps({"w": {"dtype": "F8_E4M3", "shape": [4], "data_offsets": [0, 4]}}).encode()
     p.write_bytes(struct.pack("<Q", len(head)) + head + b"\0" * 4)
-    with pytest.raises(SafetensorsError, match="unsupported dtype"):
-        read_file(str(p))
+    got = read_file(str(p))["w"]                  # a type the reader does not know: named, not fetched
+    assert isinstance(got, UnreadTensor) and got.dtype_name == "F8_E4M3" and got.shape == (4,)
     with pytest.raises(SafetensorsError, match="no model.safetensors"):
         read_folder(str(tmp_path / "nowhere"))
 
@@ -82,7 +82,7 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes():
     tensors["transformer.h.9.ln_1.weight"] = torch.zeros(64)
     tensors["h.0.attn.bias"] = torch.ones(1, 1, 8, 8)         # a buffer of GPT-2 checkpoints: ignored
     with pytest.raises(WeightError) as e:
-        check_tensors("here", tensors, model.weight_specs(), spec.ignored_tensors)
+        check_tensors("here", tensors, model.weight_specs(), spec.ignored_tensors, spec.strip_prefixes)
     err = e.value
     assert err.missing == ["h.1.ln_2.bias", "wpe.weight"]
     assert err.unexpected == ["h.0.mlp.extra", "h.9.ln_1.weight"]
@@ -97,13 +97,40 @@ def test_prefix_tied_duplicate_and_untied_head():
     _, spec, model = _model("tiny_a")
     tensors = {"transformer." + k: v for k, v in random_tensors(model.weight_specs(), 0).items()}
     tensors["lm_head.weight"] = tensors["transformer.wte.weight"]      # tied checkpoints may repeat it
-    got = check_tensors("here", tensors, model.weight_specs(), spec.ignored_tensors)
+    got = check_tensors("here", tensors, model.weight_specs(), spec.ignored_tensors, spec.strip_prefixes)
     assert "wte.weight" in got and "lm_head.weight" not in got
+    assert spec.strip_prefixes == ("transformer.",)                    # the architecture's own detail, not the loader's
+    with pytest.raises(WeightError, match="unexpected"):               # without it the names do not fit
+        check_tensors("here", tensors, model.weight_specs(), spec.ignored_tensors)
     _, spec_b, model_b = _model("tiny_b")
     tensors = random_tensors(model_b.weight_specs(), 0)
     del tensors["lm_head.weight"]
     with pytest.raises(WeightError, match="lm_head.weight"):
         check_tensors("here", tensors, model_b.weight_specs(), spec_b.ignored_tensors)
+
+
+def test_a_buffer_of_a_type_the_reader_does_not_know_is_ignored_unless_wanted(tmp_path):
+    """GPT-2 checkpoints of some writers store the causal mask `h.N.attn.bias` as BOOL or U8: the
+    folder loads (the spec ignores those names); a wanted tensor of such a type is one clear error."""
+    cfg, spec, model = _model("tiny_a")
+    folder = str(tmp_path / "m")
+    E.write_random_model(folder, cfg, seed=3)
+    path = os.path.join(folder, "model.safetensors")
+    header, base = read_header(path)
+    data = open(path, "rb").read()[base:]
+    n = cfg.n_positions
+    header["h.0.attn.bias"] = {"dtype": "BOOL", "shape": [1, 1, n, n], "data_offsets": [len(data), len(data) + n * n]}
+    raw = json.dumps(header).encode()
+    raw += b" " * (-len(raw) % 8)
+    open(path, "wb").write(struct.pack("<Q", len(raw)) + raw + data + b"\1" * (n * n))
+    t = load_checked(folder, model.weight_specs(), spec.ignored_tensors, spec.strip_prefixes)
+    assert "h.0.attn.bias" not in t and "wte.weight" in t
+    header["ln_f.bias"]["dtype"] = "U8"          # a wanted tensor in a type that is not read
+    raw = json.dumps(header).encode()
+    raw += b" " * (-len(raw) % 8)
+    open(path, "wb").write(struct.pack("<Q", len(raw)) + raw + data + b"\1" * (n * n))
+    with pytest.raises(WeightError, match="ln_f.bias is stored as U8"):
+        load_checked(folder, model.weight_specs(), spec.ignored_tensors, spec.strip_prefixes)
 
 
 def test_integer_where_float_is_wanted():
