@@ -112,16 +112,41 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm() -> int:
-    """ember.cpp does not install offline: its scikit-build/CMake build downloads nlohmann_json
-    and cpp-httplib with FetchContent, and there is no network here."""
-    ref = os.path.join(ROOT, "baseline", "_ref")
-    installed = os.path.isdir(ref) and any(n.startswith("tinyllama") for n in os.listdir(ref))
-    why = ("baseline/_ref holds an ember.cpp build, but its GPT-2 path has no sm_100 target and no batch API to time"
-           if installed else
-           "ember.cpp does not install offline: pip's build of it fails in CMake FetchContent (nlohmann_json from "
-           "github.com, no network); nothing under baseline/_ref")
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+def reference_arm(args) -> int:
+    """ember.cpp's own GPT-2 path (its graph interpreter on its CUDA path, float32, unmodified) on the
+    same model shape and workload, through baseline/_ref/ref_bench.  The package does not install with
+    pip offline (its CMake configure downloads two libraries); its interpreter is built by hand from its
+    sources instead (baseline/build_reference.py), where those sources are mounted."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    import build_reference
+    import reference_arm as arm
+    exe = build_reference.binary()
+    if not os.path.isfile(exe):
+        src = os.environ.get("EMBER_REFERENCE", "/root/reference")
+        try:
+            exe = build_reference.build(src)
+        except (RuntimeError, OSError) as e:
+            why = " ".join(str(e).split())[:300]
+            print(json.dumps({"impl": "reference", "unavailable": f"baseline/_ref/ref_bench is not built and cannot be built here: {why}"}))
+            return 0
+    cfg = dict(xl_config())
+    if args.layers:
+        cfg["n_layer"] = args.layers
+    W = max(3, args.warmup)
+    K = args.steps if args.steps is not None else cfg["n_positions"] - args.prompt_len - W
+    K = max(1, min(K, cfg["n_positions"] - args.prompt_len - W))
+    clocks = ClockSampler()
+    clocks.start()
+    t0 = time.time()
+    try:
+        line = arm.run(exe, cfg, args.batch, args.prompt_len, W, K, PREFILL)
+    except (RuntimeError, OSError, subprocess.SubprocessError, ValueError) as e:
+        clocks.stop()
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(str(e).split())[:300]}))
+        return 0
+    clocks.stop()
+    line["clocks"] = clocks.summary([(t0, time.time())])
+    print(json.dumps(line))
     return 0
 
 
@@ -137,7 +162,7 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each prompt before decoding starts")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py measures one GPU: this library runs a model on a single GPU (asked for {args.gpus})")
         return 2
@@ -163,74 +188,108 @@ def main() -> int:
     K = max(1, min(K, ctx - prompt_len - W))
     pk = peaks()
 
-    t0 = time.time()
-    spec = get_architecture(cfg.architecture).build_spec(cfg)
-    tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=0, dtype=torch.bfloat16, device="cuda")
-    log(f"random weights: {sum(t.numel() for t in tensors.values()) / 1e9:.3f} G parameters in {time.time() - t0:.1f} s")
+    def build_engine(config, max_tokens):
+        t0 = time.time()
+        spec = get_architecture(config.architecture).build_spec(config)
+        tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=0, dtype=torch.bfloat16, device="cuda")
+        log(f"random weights: {sum(t.numel() for t in tensors.values()) / 1e9:.3f} G parameters in {time.time() - t0:.1f} s")
+        eng = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=max_tokens)
+        eng.config = config
+        return eng
+
+    def step_bytes(config):
+        """(bytes of weights a decode step reads once, bytes of cache per held position)."""
+        d, L, F, V = config.n_embd, config.n_layer, config.inner, config.vocab_size
+        weights = L * (3 * d * d + d * d + 2 * d * F) * 2 + V * d * 2 + L * (3 * d + d + F + d + 4 * d) * 4 + 2 * d * 4
+        return weights, L * 2 * d * 2
+
     biggest = max(args.batch, 1 if args.no_points else 64)
-    engine = Engine.from_spec(spec, tensors, dtype="bfloat16", max_tokens=max(biggest, PREFILL[0]) * ctx)
-    engine.config = cfg
-    del tensors
+    engine = build_engine(cfg, max(biggest, PREFILL[0]) * ctx)
     sampler = E.Sampler(engine.ops)
     params = E.SamplingParams()  # ember.cpp's defaults: temperature 0.1, top_k 40, top_p 0.9
     rng = np.random.default_rng(0)
     d, L, F, V = cfg.n_embd, cfg.n_layer, cfg.inner, cfg.vocab_size
-    weight_bytes = L * (3 * d * d + d * d + 2 * d * F) * 2 + V * d * 2 + L * (3 * d + d + F + d + 4 * d) * 4 + 2 * d * 4
-    kv_bytes_per_pos = L * 2 * d * 2
     clocks = ClockSampler()
     clocks.start()
     windows = []
 
-    def decode_run(B: int, warm: int, steps: int):
-        """Prefill B prompts of prompt_len, then warm + steps decode steps; times the last `steps`."""
-        engine.capture_decode(B)   # the step's graphs for every bucket of lengths, before anything is timed
-        slots = [engine.open() for _ in range(B)]
-        prompts = [rng.integers(0, V, prompt_len).tolist() for _ in range(B)]
-        logits = engine.step([(s, p, [prompt_len - 1]) for s, p in zip(slots, prompts)])
+    def decode_run(eng, lengths, warm: int, steps: int | None):
+        """Prefills prompts of the given lengths in one step, then decodes: `warm` untimed steps and then `steps`
+        timed ones, or (steps None) until every sequence has reached the context's end, sequences leaving as
+        they do.  As Generator does, a step takes its tokens from the sampler's output on the device and is
+        queued before the host reads those ids."""
+        config = eng.config
+        weight_bytes, kv_bytes_per_pos = step_bytes(config)
+        smp = sampler if eng is engine else E.Sampler(eng.ops)
+        B = len(lengths)
+        # the step's graphs for every bucket of lengths (and, where the batch shrinks, of batch sizes), before anything is timed
+        for b in ([B] if steps is not None else [1 << k for k in range(B.bit_length()) if (1 << k) <= B] + [B]):
+            eng.capture_decode(b)
+        slots = [eng.open() for _ in range(B)]
+        prompts = [rng.integers(0, config.vocab_size, n).tolist() for n in lengths]
+        logits = eng.step([(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
         streams = torch.arange(B, dtype=torch.int32, device="cuda")
         counters = torch.zeros(B, dtype=torch.int32, device="cuda")
-        ids = sampler.sample(logits, params, streams, counters)
-        on_the_way = sampler.fetch(ids)
+        ids = smp.sample(logits, params, streams, counters)
+        on_the_way = smp.fetch(ids)
+        live = list(range(B))
         rows = list(range(B))
-        generated = []
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        cache_bytes = 0
-        launches0 = 0
-        for i in range(warm + steps):
+        cache_bytes = tokens = timed_steps = launches0 = 0
+        i = 0
+        w0 = time.time()
+        while live and (steps is None or i < warm + steps):
             if i == warm:
                 torch.cuda.synchronize()
-                launches0 = engine.ops.launches
+                launches0 = eng.ops.launches
                 w0 = time.time()
                 start.record()
             if i >= warm:
-                cache_bytes += sum(engine.length(s) + 1 for s in slots) * kv_bytes_per_pos
-            # as Generator does: the step takes its tokens from the sampler's output on the device and is
-            # queued before the host reads those ids
-            logits = engine.step([(s, [0], [0]) for s in slots], borrow=True, device_tokens=(ids, rows))
-            counters += 1
-            following = sampler.sample(logits, params, streams, counters)
-            fetched = sampler.fetch(following)
-            generated.append(on_the_way.tolist())
+                cache_bytes += sum(eng.length(slots[j]) + 1 for j in live) * kv_bytes_per_pos
+                tokens += len(live)
+                timed_steps += 1
+            logits = eng.step([(slots[j], [0], [0]) for j in live], borrow=True, device_tokens=(ids, rows))
+            counters[:len(live)] += 1
+            following = smp.sample(logits, params, streams[:len(live)], counters[:len(live)])
+            fetched = smp.fetch(following)
+            on_the_way.tolist()
             ids, on_the_way = following, fetched
-        generated.append(on_the_way.tolist())
+            i += 1
+            if steps is None:      # sequences that have reached the context's end leave; the others keep their rows' order
+                staying = [k for k, j in enumerate(live) if eng.length(slots[j]) < config.n_positions]
+                for k, j in enumerate(live):
+                    if k not in staying:
+                        eng.close(slots[j])
+                live = [live[k] for k in staying]
+                rows = staying
+            else:
+                rows = list(range(len(live)))
+        on_the_way.tolist()
         stop.record()
         torch.cuda.synchronize()
         windows.append((w0, time.time()))
         ms = start.elapsed_time(stop)
-        launches = engine.ops.launches - launches0
-        for s in slots:
-            engine.close(s)
-        return {"tok_s": B * steps / (ms / 1e3), "ms_per_step": ms / steps, "launches": launches,
-                "bytes_per_step": weight_bytes + cache_bytes / steps}
+        launches = eng.ops.launches - launches0
+        for j in live:
+            eng.close(slots[j])
+        per_step = weight_bytes + cache_bytes / max(1, timed_steps)
+        gbs = per_step / (ms / max(1, timed_steps) / 1e3) / 1e9
+        return {"tok_s": tokens / (ms / 1e3), "ms_per_step": ms / max(1, timed_steps), "launches": launches, "steps": timed_steps,
+                "bytes_per_step": per_step, "gbs": gbs, "frac": gbs / pk["hbm_gbs"]}
+
+    def roof(r):
+        return {"bytes_per_step": int(r["bytes_per_step"]), "gbs": round(r["gbs"], 1), "frac": round(r["frac"], 4),
+                "ms_per_step": round(r["ms_per_step"], 4)}
 
     log("main decode run ...")
-    main_run = decode_run(args.batch, W, K)
+    main_run = decode_run(engine, [prompt_len] * args.batch, W, K)
     log(main_run)
-    points = {}
+    points, point_roofs = {}, {}
     if not args.no_points:
-        for B in (1, 64):
-            r = decode_run(B, W, ctx - prompt_len - W)
+        for B in (1, 8, 64):       # the whole sweep from the prompt to the context's end, whatever --steps says
+            r = decode_run(engine, [PROMPT_LEN] * B, W, ctx - PROMPT_LEN - W)
             points[f"decode_b{B}"] = round(r["tok_s"], 1)
+            point_roofs[f"decode_b{B}"] = roof(r)
             log(f"batch {B}: {r}")
 
     # prefill of 2,048 tokens: 2 prompts x 1,024, the last row's logits wanted
@@ -272,6 +331,25 @@ def main() -> int:
     from ember_cpp_b200.engine import StepLayout
     bucket = 1 << (args.batch - 1).bit_length()
     h2d = StepLayout(bucket, bucket, bucket, engine.cache.max_blocks, len(engine.cache.groups)).size * 4
+
+    # BASELINE.json's two other workloads at their full depth: GPT-2 large's shape (16 ragged prompts of 1 to 512
+    # tokens, then 256 decode steps) and GPT-2 medium's (64 ragged prompts of 8 to 960 tokens, each decoded to the
+    # context's end; sequences leave as they get there)
+    if not args.no_points:
+        del session
+        engine = sampler = None
+        torch.cuda.empty_cache()
+        for name, sizes, lengths, steps in (
+                ("large_b16", dict(n_layer=36, n_embd=1280, n_head=20, n_inner=5120), rng.integers(1, 513, 16).tolist(), 256),
+                ("medium_b64", dict(n_layer=24, n_embd=1024, n_head=16, n_inner=4096), rng.integers(8, 961, 64).tolist(), None)):
+            c = E.GPT2Config.from_dict({**XL, **sizes, "architectures": ["GPT2LMHeadModel"]})
+            eng = build_engine(c, len(lengths) * c.n_positions)
+            r = decode_run(eng, [int(n) for n in lengths], W if steps else 0, steps)
+            points[name] = round(r["tok_s"], 1)
+            point_roofs[name] = roof(r)
+            log(f"{name}: {r}")
+            del eng
+            torch.cuda.empty_cache()
     clocks.stop()
 
     achieved = main_run["bytes_per_step"] / (main_run["ms_per_step"] / 1e3) / 1e9
@@ -292,6 +370,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "points_roofline": point_roofs,
         "clocks": clocks.summary(windows),
     }
     print(json.dumps(line))
