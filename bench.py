@@ -3,6 +3,7 @@ weights (batch 8 by default, 128-token prompts decoded towards the 1,024-token c
 2,048-token prefill, the decode step's memory roofline and batch 1 / 64 beside it.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+    python bench.py --linear M N K [--act gelu_tanh] [--residual]      (one product, every kernel that takes it)
 
 Prints ONE JSON line on stdout (everything else goes to stderr).  A "step" is one decode step of
 the whole batch.  `value` times K steps of the engine's own loop (step function + device sampler,
@@ -150,6 +151,70 @@ def reference_arm(args) -> int:
     return 0
 
 
+def linear_mode(args) -> int:
+    """Times one bfloat16 product Y[M,N] = X[M,K] W[N,K]^T (+ bias, activation, float32 residual) on every
+    kernel that takes its shape: cuBLASLt (`lt`), this library's tcgen05 kernel (`tc`, more than 64 rows), the
+    tcgen05 weight-streaming kernel (`stream`, up to 64 rows) and the mma.sync weight-streaming kernel
+    (`decode`, up to 16 rows).  As in a model's step, the launches follow one another in a captured graph,
+    each with a weight matrix of its own (so many that they exceed L2 together: weights come from DRAM
+    every time); the time is the graph's CUDA-event time divided by its launches, the median of 7 replays."""
+    import torch
+
+    from ember_cpp_b200.csrc.ops import CudaOps
+    M, N, K = args.linear
+    ops = CudaOps()
+    copies = max(4, -(-(400 << 20) // (N * K * 2)))
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    ws = [(torch.randn(N, K, device="cuda") * 0.02).bfloat16() for _ in range(copies)]
+    bias = torch.randn(N, device="cuda")
+    res = torch.randn(M, N, device="cuda") if args.residual else None
+    out = res if res is not None else torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+
+    def timed(fn):
+        for w in ws[:2]:
+            fn(w)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for w in ws:
+                fn(w)
+        graph.replay()
+        times = []
+        for _ in range(7):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            graph.replay()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3 / len(ws))
+        ops.check()
+        return statistics.median(times)
+
+    def lt(w):
+        ops.gemm, ops.linear_stream_on = "lt", False
+        ops.linear(x, w, bias, act=args.act, residual=res, out_dtype=out.dtype)
+
+    kernels = {}
+    if M > 16:
+        kernels["lt"] = lt
+    if M > 64:
+        kernels["tc"] = lambda w: ops.linear_tc(x, w, bias, args.act, res, out)
+    if M <= 64:
+        kernels["stream"] = lambda w: ops.linear_stream(x, w, bias, args.act, res, out)
+    if M <= 16:
+        def decode(w):
+            ops.linear_stream_on = False
+            ops.linear(x, w, bias, act=args.act, residual=res, out_dtype=out.dtype)
+        kernels["decode"] = decode
+    ideal = N * K * 2 / (peaks()["hbm_gbs"] * 1e3)
+    for name, fn in kernels.items():
+        us = timed(fn)
+        print(f"{name:7s} M={M} N={N} K={K} act={args.act} residual={args.residual}: {us:7.1f} us a launch, "
+              f"{2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s, weights at {N * K * 2 / us / 1e3:6.0f} GB/s "
+              f"(streaming W alone: {ideal:.1f} us)")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -160,7 +225,13 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each prompt before decoding starts")
+    ap.add_argument("--linear", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
+                    help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
+    ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
+    ap.add_argument("--residual", action="store_true", help="with --linear: add a float32 residual (the output is float32 then)")
     args = ap.parse_args()
+    if args.linear:
+        return linear_mode(args)
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:

@@ -26,15 +26,20 @@
 //                 through distributed shared memory: the sequences are dealt out in groups of four
 //                 among the blocks, every block sends each other block that block's columns and
 //                 sums what it receives in block order (no atomics: a result does not depend on
-//                 timing), then applies bias, activation and residual to its own columns and stores
-//                 them; stores of a warp cover 32 consecutive features of one sequence.
+//                 timing).  The stores into a partner's shared memory count their bytes on the
+//                 partner's mbarrier as they land (st.async), so nobody meets at a barrier after
+//                 the exchange.  Then all eight warps apply bias, activation and residual to the
+//                 block's own columns and store them; stores of a warp cover 32 consecutive
+//                 features of one sequence.
 //
 // Nothing is written to global memory before the dependency wait, and what the kernel in front
 // wrote (X, the residual) is read by TMA or `__ldcg`, never through the read-only data path.
 //
 // Every wait on an mbarrier has a time limit; a role whose wait runs out records a code in the
-// host-visible status word, the block still meets its cluster at both cluster barriers (nobody is
-// left waiting), frees its tensor memory and returns.  `ember_tc_status` reports it.
+// host-visible status word, the block still meets its cluster at the cluster's one barrier (nobody
+// is left waiting there), frees its tensor memory and returns.  `ember_tc_status` reports it.
+// A block leaves only after everything its partners send it has landed (it needs it), and it sends
+// to a partner only what that partner waits for: no block's shared memory is written after it left.
 #include <mutex>
 
 #include "tc_common.cuh"
@@ -58,13 +63,14 @@ struct StreamArgs {
   int M, N, K;
   int mp;        // M rounded up to a multiple of 16: columns of the accumulator
   int stages, act, out_f32, k_split;
+  const char* warm;            // constants that a kernel soon after this one streams (the next product's weights), or null:
+  unsigned long long warm_bytes;  // a multiple of 16; this launch's blocks ask them into L2, a share each
   int res_by_tma;  // the residual's tile comes as one TMA box (its rows are 16-byte aligned)
   int* status;
 };
 
 enum : int { ST_PRODUCER = 21, ST_MMA = 22, ST_EPILOGUE = 23, ST_DRAIN = 24 };
 
-__device__ __forceinline__ void cluster_arrive_relaxed() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ unsigned map_to_rank(unsigned addr, unsigned rank) {
@@ -72,8 +78,12 @@ __device__ __forceinline__ unsigned map_to_rank(unsigned addr, unsigned rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void st_cluster_f4(unsigned addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};\n" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+// Four floats into a partner's shared memory; when they have landed there, 16 bytes are counted on
+// the partner's mbarrier: the data's arrival is its own signal, no barrier of the cluster follows.
+__device__ __forceinline__ void st_async_f4(unsigned addr, unsigned a, unsigned b, unsigned c, unsigned d, unsigned remote_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];\n" ::"r"(addr),
+               "r"(a), "r"(b), "r"(c), "r"(d), "r"(remote_bar)
+               : "memory");
 }
 
 // The columns of the accumulator in groups of four ("quads"); block r of a cluster of `split` owns
@@ -97,7 +107,7 @@ __global__ void __launch_bounds__(kThreads, 2)
                          const __grid_constant__ CUtensorMap map_r, const StreamArgs p) {
   EMBER_MARK_START(kLinearStream);
   extern __shared__ unsigned char smem_raw[];
-  __shared__ unsigned long long bars[2 * kMaxStages + 2];  // full[stages], empty[stages], done, residual
+  __shared__ unsigned long long bars[2 * kMaxStages + 3];  // full[stages], empty[stages], done, residual, partial sums
   __shared__ unsigned s_tmem;
   __shared__ unsigned char s_owner[kMaxRows / 4], s_local[kMaxRows / 4];
   __shared__ int s_failed;  // a wait of this block ran out: nothing is stored
@@ -116,7 +126,8 @@ __global__ void __launch_bounds__(kThreads, 2)
   const int q_most = quads_most(quads, split);
   const unsigned recv = base + p.stages * stage_bytes;          // [source block][quad of mine][row 0..127] float4
   const unsigned res_s = recv + split * q_most * (BM * 16);     // [column of mine][row 0..127] float
-  const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * p.stages, done = empty0 + 8 * p.stages, res_bar = done + 8;
+  const unsigned full0 = smem_u32(bars), empty0 = full0 + 8 * p.stages, done = empty0 + 8 * p.stages, res_bar = done + 8,
+                 recv_bar = res_bar + 8;
   const unsigned tmem_cols = p.mp <= 32 ? 32u : 64u;
 
   if (threadIdx.x == 0) {
@@ -126,6 +137,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     }
     mbar_init(done, 1);
     mbar_init(res_bar, 1);
+    mbar_init(recv_bar, 1);
+    if (split > 1)  // what the partners will send: every other block's partial sums of this block's quads
+      mbar_expect_tx(recv_bar, (unsigned)((split - 1) * (quad_lo(quads, split, rank + 1) - quad_lo(quads, split, rank)) * BM * 16));
     mbar_init_fence();
     s_failed = 0;
     // The weights of the ring's first turn are asked for at once: before the other warps are met,
@@ -158,9 +172,9 @@ __global__ void __launch_bounds__(kThreads, 2)
   __syncthreads();
   fence_after();
   const unsigned tmem = s_tmem;
-  // every block of the cluster says that it runs (its shared memory exists) long before a partner
-  // writes into it; the wait for this phase comes just before the first such write
-  if (split > 1) cluster_arrive_relaxed();
+  // every block of the cluster says that it runs (its shared memory and its barriers exist) long
+  // before a partner writes into it; the wait for this phase comes just before the first such write
+  if (split > 1) cluster_arrive();
   pdl_trigger();
 
   // the bias of the row this thread finishes at the end: a constant of the model, asked for now (in a
@@ -220,7 +234,22 @@ __global__ void __launch_bounds__(kThreads, 2)
       if (it == n_kb - 1) umma_commit_1cta_elect(done);
     }
     if (!ok && lane == 0) atomicCAS(p.status, 0, ST_MMA), s_failed = 1;
-  } else if (warp < 6) {
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------------ the next product's weights, into L2
+    // A product's ring holds three or four boxes of K; the boxes after those are asked for only as the ring
+    // turns, and from DRAM each turn costs a microsecond and a half on the step's chain of dependent waits.
+    // Asked into L2 one kernel early (by this launch, whose own weights were asked for by the launch before
+    // it), they come from there.  Two warps, this block's share of the tensor, 8 KB a request.
+    if (p.warm) {
+      constexpr unsigned kPiece = 8192;
+      const unsigned long long share = ((p.warm_bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+      const unsigned long long lo = share * blockIdx.x, hi = min(p.warm_bytes, lo + share);
+      for (unsigned long long at = lo + (unsigned long long)(threadIdx.x - 6 * 32) * kPiece; at < hi; at += 64ull * kPiece) {
+        const unsigned n = (unsigned)min((unsigned long long)kPiece, hi - at);
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p.warm + at), "r"(n) : "memory");
+      }
+    }
+  } else {
     // ------------------------------------------------------------------ the accumulator leaves tensor memory
     const int quarter = warp & 3;              // the 32 lanes of tensor memory this warp may read
     const int row = quarter * 32 + lane;       // row of the tile = output feature n0 + row
@@ -229,8 +258,9 @@ __global__ void __launch_bounds__(kThreads, 2)
     if (warp == 2) STREAM_MARK(kPhaseB);  // accumulator complete
     if (!ok && lane == 0) atomicCAS(p.status, 0, ST_EPILOGUE), s_failed = 1;
     if (split > 1) cluster_wait();  // every block of the cluster runs: its shared memory may be written
-    // Every quad of columns goes to the block that owns it, this block's own quads into its own
-    // shared memory by the same path: 16 columns of the accumulator at a time.
+    // Every quad of columns goes to the block that owns it: this block's own quads into its own shared
+    // memory, the others into their owners' with a store that counts its bytes on the owner's barrier
+    // when it lands.  16 columns of the accumulator at a time.
     if (ok) {
       const unsigned taddr = tmem + ((unsigned)(quarter * 32) << 16);
       const unsigned mine = recv + (unsigned)((rank * q_most * BM + row) * 16);
@@ -241,24 +271,22 @@ __global__ void __launch_bounds__(kThreads, 2)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const int q = (c >> 2) + j;
-          const unsigned at = map_to_rank(mine + (unsigned)(s_local[q] * (BM * 16)), (unsigned)s_owner[q]);
-          st_cluster_f4(at, __uint_as_float(a[4 * j]), __uint_as_float(a[4 * j + 1]), __uint_as_float(a[4 * j + 2]),
-                        __uint_as_float(a[4 * j + 3]));
+          const unsigned owner = s_owner[q], at = mine + (unsigned)(s_local[q] * (BM * 16));
+          if ((int)owner == rank)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(at), "r"(a[4 * j]), "r"(a[4 * j + 1]), "r"(a[4 * j + 2]),
+                         "r"(a[4 * j + 3])
+                         : "memory");
+          else
+            st_async_f4(map_to_rank(at, owner), a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3], map_to_rank(recv_bar, owner));
         }
       }
     }
     if (warp == 2) STREAM_MARK(kMerged);  // (timeline only) partial sums sent
-    if (split > 1) {
-      cluster_arrive();
-      cluster_wait();  // what the partners sent has arrived
-    }
   }
-  if ((warp < 2 || warp >= 6) && split > 1) {  // the other warps meet the cluster where those four do
-    cluster_wait();
-    cluster_arrive();
-    cluster_wait();
-  }
-  if (split == 1) __syncthreads();  // (with a cluster its second barrier has done this)
+  if ((warp < 2 || warp >= 6) && split > 1) cluster_wait();  // (every thread that arrived at the start also waits)
+  __syncthreads();  // this block's own quads are in its shared memory
+  bool landed = true;
+  if (split > 1) landed = mbar_wait(recv_bar, 0);  // the partners' have landed
   if (warp == 2) STREAM_MARK(kPhaseC);  // partial sums exchanged
   // ------------------------------------------------------------------ all warps: sums, epilogue, stores
   // An item is a quad of this block's columns for one row: its partial sums are added in block order
@@ -280,7 +308,8 @@ __global__ void __launch_bounds__(kThreads, 2)
     // One short loop, not unrolled and not specialised: this code runs once per block, and what it
     // costs is fetching it (unrolled twice, in a copy for every activation and every combination of
     // residual and output type, it was 49 KB of the kernel's 79 KB).
-    if (fine && n_ok && !*reinterpret_cast<volatile int*>(&s_failed)) {
+    if (!landed && threadIdx.x == 0) atomicCAS(p.status, 0, ST_EPILOGUE);
+    if (fine && landed && n_ok && !*reinterpret_cast<volatile int*>(&s_failed)) {
       const int act = p.act;
       const bool with_res = p.residual != nullptr, out_f32 = p.out_f32 != 0;
 #pragma unroll 1
@@ -354,8 +383,11 @@ int pick_split(int tiles, int kb_all, int sms) {
 // bias: float32 [N] or null.  residual: float32 [M,N] or null (the output is float32 then and may
 // be the same buffer).  act: an EMBER_ACT code.  k_split: 0 lets the library choose how many
 // blocks share a tile, else 1 to 8.  stages: 0 lets it choose the depth of the ring, else 2 to 10.
+// warm, warm_bytes: null and 0, or constants that a kernel soon after this one reads (the next
+// product's weight matrix; 16-byte aligned, a multiple of 16 bytes): this launch asks them into L2.
 EMBER_API int ember_linear_stream(const void* X, const void* W, const float* bias, const float* residual, void* out, int M,
-                                  int N, int K, int act, int out_dtype, int k_split, int stages, cudaStream_t stream) {
+                                  int N, int K, int act, int out_dtype, int k_split, int stages, const void* warm,
+                                  size_t warm_bytes, cudaStream_t stream) {
   EMBER_CHECK(M > 0 && M <= kMaxRows && N > 0 && K > 0, "linear_stream: M = %d (at most %d), N = %d, K = %d", M, kMaxRows, N, K);
   EMBER_CHECK(K % 8 == 0, "linear_stream: K = %d is not a multiple of 8 (rows of 16 bytes)", K);
   EMBER_CHECK(((uintptr_t)X | (uintptr_t)W) % 16 == 0, "linear_stream: operands are not 16-byte aligned");
@@ -364,6 +396,8 @@ EMBER_API int ember_linear_stream(const void* X, const void* W, const float* bia
   EMBER_CHECK(!residual || out_dtype == EMBER_F32, "linear_stream: a residual sum needs a float32 output");
   EMBER_CHECK(k_split >= 0 && k_split <= kMaxSplit, "linear_stream: k_split = %d (0 to %d)", k_split, kMaxSplit);
   EMBER_CHECK(stages == 0 || (stages >= 2 && stages <= kMaxStages), "linear_stream: stages = %d (0, or 2 to %d)", stages, kMaxStages);
+  EMBER_CHECK(warm_bytes % 16 == 0 && (reinterpret_cast<size_t>(warm) & 15) == 0,
+              "linear_stream: what is to be warmed is 16-byte aligned and a multiple of 16 bytes");
   const int tiles = (N + BM - 1) / BM, kb_all = (K + BK - 1) / BK;
   CUtensorMap map_w, map_x, map_r;
   StreamArgs p;
@@ -398,6 +432,8 @@ EMBER_API int ember_linear_stream(const void* X, const void* W, const float* bia
   p.bias = bias, p.residual = residual, p.out = out;
   p.M = M, p.N = N, p.K = K, p.act = act, p.out_f32 = out_dtype == EMBER_F32;
   p.status = tc::status().device;
+  p.warm = warm_bytes ? static_cast<const char*>(warm) : nullptr;
+  p.warm_bytes = warm_bytes;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * p.k_split);
   cfg.blockDim = dim3(kThreads);

@@ -34,7 +34,7 @@ _SIGNATURES = {
                           _c_void, _c_size, _c_void, _c_void],
     "ember_linear_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_stream": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                            _c_void],
+                            _c_void, _c_size, _c_void],
     "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_size, _c_void],
     "ember_clear_tails": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
@@ -151,6 +151,7 @@ class CudaOps:
         self.tail_norm = options.tail_norm
         self._expected = None          # (gain, bias, eps, dtype) announced for the next sum
         self._warm = None              # tensor announced by `warm` for the next product
+        self._coming = []              # weight matrices announced by `announce_weights`, in the order their products run
         # warm: the second product of a feed-forward has its weights landed about a microsecond earlier with it
         #   (its blocks cannot be resident beside the first product's); a step of 12 layers 0.519 against 0.521 ms.
         self.warm_ahead = options.warm
@@ -241,6 +242,22 @@ class CudaOps:
         after it).  A hint: a small product's kernel asks them into L2 while it waits for its own input."""
         fits = tensor is not None and tensor.numel() * tensor.element_size() <= self.AHEAD_BYTES
         self._warm = tensor if self.warm_ahead and fits else None
+
+    def announce_weights(self, weights) -> None:
+        """Announces the weight matrices of the products to come, in the order they run (a block announces
+        its own and the first of what follows it).  A hint: a product of 17 to 64 rows asks the matrix after
+        its own into L2, so that the next product's ring refills from there and not from DRAM."""
+        self._coming = [w for w in weights if w is not None]
+
+    def _after(self, w):
+        """The announced matrix that follows `w`, if it is worth asking into L2 (it fits there with room to spare)."""
+        if not self.warm_ahead:
+            return None
+        for i, c in enumerate(self._coming[:-1]):
+            if c.data_ptr() == w.data_ptr():
+                nxt = self._coming[i + 1]
+                return nxt if nxt.numel() * nxt.element_size() <= self.AHEAD_BYTES else None
+        return None
 
     def layernorm(self, x, w, b, eps, out_dtype, lazy=False):
         """Layer norm of float32 rows.  With `lazy` the caller promises to hand the result to
@@ -363,7 +380,7 @@ class CudaOps:
         if norm is not None:
             a = norm.materialize()
         if self.linear_stream_on and M <= STREAM_M and K % 8 == 0:
-            return self.linear_stream(a, w, bias, act, residual, out)
+            return self.linear_stream(a, w, bias, act, residual, out, warm=warm if warm is not None else self._after(w))
         # an output width that is no multiple of 8 (a vocabulary of 50,257) leaves the library only unaligned,
         # slow kernels (167 against 50 microseconds for the head at 64 rows): those products take the tcgen05 kernel
         if K % 8 == 0 and ((self.gemm == "tc" and M > TC_MIN_M) or N % 8 != 0):
@@ -392,12 +409,14 @@ class CudaOps:
                    M, w.shape[0], K, _ACT[act], _code(out.dtype), tile_n)
         return out
 
-    def linear_stream(self, a, w, bias, act, residual, out, k_split: int = 0, stages: int = 0):
+    def linear_stream(self, a, w, bias, act, residual, out, k_split: int = 0, stages: int = 0, warm=None):
         """The tcgen05 weight-streaming product for up to 64 rows with its epilogue into `out`; `k_split` and
-        `stages` 0 let the kernel choose how many blocks share a tile and how deep its ring is."""
+        `stages` 0 let the kernel choose how many blocks share a tile and how deep its ring is; `warm`: a tensor
+        that the launch asks into L2 (the next product's weights)."""
         M, K = a.shape
         self._call("ember_linear_stream", a.data_ptr(), w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(),
-                   M, w.shape[0], K, _ACT[act], _code(out.dtype), int(k_split), int(stages))
+                   M, w.shape[0], K, _ACT[act], _code(out.dtype), int(k_split), int(stages),
+                   None if warm is None else warm.data_ptr(), 0 if warm is None else warm.numel() * warm.element_size() // 16 * 16)
         return out
 
     def wait_probe(self, limit_ns: int = 1_000_000) -> None:

@@ -60,6 +60,9 @@ class CausalAttention(Mixer):
             self.b_qkv = runtime.vector(get(self.qkv_name + ".bias"))
             self.b_out = runtime.vector(get(self.out_name + ".bias"))
 
+    def stream_weights(self):
+        return [self.w_qkv, self.w_out]
+
     def cache_need(self):
         return CacheNeed("window" if self.window > 0 else "full", self.kv_heads, self.head_dim, self.window)
 

@@ -64,6 +64,12 @@ class Part:
     def weight_specs(self) -> list[WeightSpec]:
         return []
 
+    def stream_weights(self) -> list:
+        """The weight matrices that this part's forward streams through `ops.linear`, in that order
+        (as prepared by load()).  A hint for the kernels: a block announces them so that one product's
+        launch can ask the next product's weights into L2.  The default names none."""
+        return []
+
     def load(self, get: Callable[[str], Any], runtime) -> None:
         """Fetch the tensors named in weight_specs() with `get(name)` (as stored, on the
         runtime's device) and keep them in the form the kernels want."""

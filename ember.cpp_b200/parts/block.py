@@ -15,6 +15,9 @@ from .base import Block, register_part
 class PreNormBlock(Block):
 
     def forward(self, ctx, x, app):
+        announce = getattr(ctx.ops, "announce_weights", None)
+        if announce is not None:    # a hint: this block's matrices in the order they are streamed, then what follows
+            announce(self.mixer.stream_weights() + self.ffn.stream_weights() + list(getattr(ctx, "next_weights", ())))
         h = self.norm1.forward(ctx, x, ctx.dtype, lazy=self.mixer.takes_lazy_norm)
         self.norm2.announce(ctx, ctx.dtype)         # what follows the mixer's sum into the stream
         x = self.mixer.forward(ctx, h, x, app)

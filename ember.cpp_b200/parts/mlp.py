@@ -51,6 +51,9 @@ class DenseFeedForward(FeedForward):
             self.b_up = runtime.vector(get(self.up_name + ".bias"))
             self.b_down = runtime.vector(get(self.down_name + ".bias"))
 
+    def stream_weights(self):
+        return [self.w_up, self.w_down]
+
     def forward(self, ctx, h, residual):
         warm = getattr(ctx.ops, "warm", None)
         if warm is not None:

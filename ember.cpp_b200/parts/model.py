@@ -79,8 +79,10 @@ class DecoderModel:
         for i, app in enumerate(ctx.apps):
             if i + 1 < len(ctx.apps):
                 ctx.next_norm = self.blocks[ctx.apps[i + 1].layer].norm1
+                ctx.next_weights = self.blocks[ctx.apps[i + 1].layer].mixer.stream_weights()[:1]
             else:  # the final norm reads the stream itself only if no rows are picked out first
                 ctx.next_norm = self.final_norm if plan.n_want and plan.wants_every_row else None
+                ctx.next_weights = ()
             x = self.blocks[app.layer].forward(ctx, x, app)
         ctx.next_norm = None
         if plan.n_want == 0:
