@@ -225,6 +225,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each prompt before decoding starts")
+    ap.add_argument("--only", default=None, choices=["prefill"],
+                    help="run only the 2,048-token prefill (a few repeats; prints its line and no benchmark record): for profiling")
     ap.add_argument("--linear", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
     ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
@@ -352,11 +354,12 @@ def main() -> int:
         return {"bytes_per_step": int(r["bytes_per_step"]), "gbs": round(r["gbs"], 1), "frac": round(r["frac"], 4),
                 "ms_per_step": round(r["ms_per_step"], 4)}
 
-    log("main decode run ...")
-    main_run = decode_run(engine, [prompt_len] * args.batch, W, K)
-    log(main_run)
     points, point_roofs = {}, {}
-    if not args.no_points:
+    if args.only != "prefill":
+        log("main decode run ...")
+        main_run = decode_run(engine, [prompt_len] * args.batch, W, K)
+        log(main_run)
+    if not args.no_points and args.only != "prefill":
         for B in (1, 8, 64):       # the whole sweep from the prompt to the context's end, whatever --steps says
             r = decode_run(engine, [PROMPT_LEN] * B, W, ctx - PROMPT_LEN - W)
             points[f"decode_b{B}"] = round(r["tok_s"], 1)
@@ -387,6 +390,11 @@ def main() -> int:
     pre_flops = 2 * T * L * (3 * d * d + d * d + 2 * d * F) + n_seq * 2 * d * plen * (plen + 1) * L + 2 * n_seq * d * V
     prefill = {"value": round(T / (pre_ms / 1e3), 1), "tokens": T, "ms": round(pre_ms, 3),
                "frac": round(pre_flops / (pre_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    if args.only == "prefill":
+        clocks.stop()
+        print(json.dumps({"prefill": prefill, "n_layer": L, "times_ms": [round(t, 3) for t in times]}))
+        return 0
 
     # the same decode through the Python entry point: host ids in, host ids out
     session = E.Session.from_engine(engine, max_batch_size=args.batch, seed=0)
