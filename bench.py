@@ -393,7 +393,10 @@ def main() -> int:
 
     if args.only == "prefill":
         clocks.stop()
-        print(json.dumps({"prefill": prefill, "n_layer": L, "times_ms": [round(t, 3) for t in times]}))
+        line = {"prefill": prefill, "n_layer": L, "times_ms": [round(t, 3) for t in times]}
+        if engine.ops.op_timing:     # EMBER_OP_TIMING=1: the time per kernel entry point over the repeats (launches do not overlap then)
+            line["op_ms_per_prefill"] = {k: round(ms / len(times + [0, 0]), 4) for k, (n, ms) in sorted(engine.ops.op_times().items())}
+        print(json.dumps(line))
         return 0
 
     # the same decode through the Python entry point: host ids in, host ids out

@@ -171,19 +171,46 @@ class CudaOps:
         # attention: prefill attention with head size 64 on the tcgen05 kernel, or ("mma") on the mma.sync kernel
         #   (which takes every other head size anyway)
         self.attention_tc = options.attention == "tc"
+        # op_timing, nvtx: per-launch CUDA events and NVTX ranges (see options.py); both off by default
+        self.op_timing, self.nvtx = options.op_timing, options.nvtx
+        self._timed = []
         # the three switches that the kernels' launch code reads (process-wide)
         for which, value in ((0, options.pdl), (1, options.decode_bulk), (2, options.decode_cluster)):
             self.lib.ember_set_option(which, 1 if value else 0)
 
     # ------------------------------------------------------------------ helpers
     def _call(self, name: str, *args, allow=()) -> int:
+        timed = self.op_timing and not torch.cuda.is_current_stream_capturing()
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(name)
+        if timed:
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
         rc = getattr(self.lib, name)(*args, torch.cuda.current_stream().cuda_stream)
+        if timed:
+            end.record()
+            self._timed.append((name, begin, end))
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
         if rc in allow:
             return rc
         self.launches += 1
         if rc != 0:
             raise KernelError(self.lib.ember_last_error().decode())
         return 0
+
+    def op_times(self, reset: bool = True) -> dict:
+        """With the `op_timing` option: {entry point: (launches, milliseconds)} since the last call, from CUDA
+        events around every launch (an event between two launches keeps them from overlapping, so the sum is
+        more than a step takes: read the shares).  Synchronizes with the device."""
+        torch.cuda.synchronize()
+        out: dict = {}
+        for name, begin, end in self._timed:
+            n, ms = out.get(name, (0, 0.0))
+            out[name] = (n + 1, ms + begin.elapsed_time(end))
+        if reset:
+            self._timed = []
+        return out
 
     def _decode_scratch(self, n_partials: int, n_counters: int):
         if self._partials is None or self._partials.numel() < n_partials:

@@ -97,7 +97,9 @@ class Engine:
         self._graphs: dict[int, "_DecodeGraph"] = {}
         # a part whose forward does work on the host (reads a value back, loops over tokens in
         # Python) cannot be replayed from a captured graph; it says so with graph_safe = False
+        # (per-launch timing needs an event between launches, which a captured graph does not carry)
         self.cuda_graphs = (bool(cuda_graphs) and runtime.device.type == "cuda"
+                            and not getattr(self.ops, "op_timing", False)
                             and all(getattr(p, "graph_safe", True) for p in model.all_parts()))
         self.counters = {"steps": 0, "prompt_tokens": 0, "decode_tokens": 0}
 
@@ -230,6 +232,12 @@ class Engine:
 
     def run(self, plan: StepPlan):
         ctx = StepContext(self.ops, self.runtime.dtype, plan, self.apps, self.model.position)
+        if getattr(self.ops, "nvtx", False):
+            torch.cuda.nvtx.range_push(f"step {'decode' if plan.all_single else 'prefill'} T={plan.T} n={plan.n}")
+            try:
+                return self.model.forward(ctx)
+            finally:
+                torch.cuda.nvtx.range_pop()
         return self.model.forward(ctx)
 
     # ------------------------------------------------------------------ one token each, as a replayed graph

@@ -27,6 +27,11 @@ options given in code), so a measurement can flip a switch without touching the 
   tail_norm        EMBER_TAIL_NORM        a layer norm runs in the tail of the product before it (few rows)
   cache_ahead      EMBER_CACHE_AHEAD      a decode attention asks the next layer's rows of the cache into L2
   warm             EMBER_WARM             a small product asks the next product's weights into L2
+  op_timing        EMBER_OP_TIMING        every launch is bracketed by CUDA events; `CudaOps.op_times()` gives the time per
+                                          kernel entry point (ember.cpp: EMBER_OP_TIMING=1, model.h:465-467).  Steps then run
+                                          launch by launch (no graph) and without overlap between kernels: read the shares
+  nvtx             EMBER_NVTX             every launch is an NVTX range named after its entry point, and every step a range
+                                          around them (ember.cpp names its prefill range for nsys, api.cpp:32, 1043-1045)
 
 The kernel switches are measurement switches: the defaults are what measured fastest, and every
 combination computes the same function.  The three that the launch code of the kernels reads
@@ -69,6 +74,8 @@ class RuntimeOptions:
     tail_norm: bool = False
     cache_ahead: bool = False
     warm: bool = True
+    op_timing: bool = False
+    nvtx: bool = False
 
     def __post_init__(self):
         if self.dtype not in ("bfloat16", "bf16", "float32", "fp32"):

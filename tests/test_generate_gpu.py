@@ -355,6 +355,26 @@ def test_two_processes_give_the_same_bits_when_deterministic(tiny_folders, tmp_p
     assert np.array_equal(outs[0], outs[1])
 
 
+def test_per_launch_timing_and_ranges(tiny_folders, plains):
+    """With the op_timing option every launch of a prompt step and of decode steps is timed by name (the
+    step then runs launch by launch, no graph), with NVTX ranges around launches and steps; the logits are
+    the same as without."""
+    plain = plains["tiny_b"]
+    seqs = [random_ids(480 + i, plain.vocab, n) for i, n in enumerate((70, 9))]
+    timed = Engine.from_folder(tiny_folders["tiny_b"], dtype="bfloat16", max_tokens=512,
+                               options=E.RuntimeOptions(op_timing=True, nvtx=True))
+    assert not timed.cuda_graphs
+    rows, _ = run_batch(timed, seqs, (60, 5))
+    times = timed.ops.op_times()
+    assert {"ember_embed", "ember_layernorm", "ember_attention_prefill", "ember_linear_decode", "ember_kv_store"} <= set(times)
+    assert all(n > 0 and ms > 0 for n, ms in times.values())
+    assert times["ember_layernorm"][0] == (2 * 3 + 1) * 11          # 3 layers and the final norm, 1 prompt step and 10 decode steps
+    assert timed.ops.op_times() == {}                                # read and reset
+    usual = run_batch(Engine.from_folder(tiny_folders["tiny_b"], dtype="bfloat16", max_tokens=512), seqs, (60, 5))[0]
+    for a, b in zip(rows, usual):
+        assert rel_error(a, b) < 1e-6
+
+
 def test_graph_replay_equals_launch_by_launch(tiny_folders, plains):
     plain = plains["tiny_a"]
     seqs = [random_ids(400 + i, plain.vocab, 50) for i in range(3)]
