@@ -149,8 +149,14 @@ class SequenceCache:
                 self.views[i] = self.views[src]
                 self.writes[i] = False
         self.state_needs = [s for _, s in needs]
-        self.states = [None if s is None else
-                       torch.full((self.n_slots, *s.shape), s.init, dtype=torch.float32, device=device)
+
+        def make(need: StateNeed):
+            if need.dtype not in ("float32", "int32"):
+                raise CacheError(f"per-sequence state of type {need.dtype!r}: float32 or int32")
+            return torch.full((self.n_slots, *need.shape), need.init, dtype=getattr(torch, need.dtype), device=device)
+
+        # per application: None, one tensor [slots, *shape], or (a mixer with several) a dict of them by name
+        self.states = [None if s is None else ({k: make(v) for k, v in s.items()} if isinstance(s, dict) else make(s))
                        for s in self.state_needs]
 
     # ------------------------------------------------------------------ slots
@@ -161,7 +167,10 @@ class SequenceCache:
             raise CacheError(str(e)) from None
         self.lengths[slot] = 0
         for need, state in zip(self.state_needs, self.states):
-            if state is not None:
+            if isinstance(state, dict):
+                for name, t in state.items():
+                    t[slot].fill_(need[name].init)
+            elif state is not None:
                 state[slot].fill_(need.init)
         return slot
 

@@ -236,4 +236,20 @@ EMBER_API int ember_act_inplace(void* y, size_t n, int act, int dtype, cudaStrea
   return 0;
 }
 
+// y <- scale * y, then (cap > 0) cap * tanh(y / cap): a factor on the embedded rows, a cap on the logits.
+__global__ void scale_cap_kernel(float* __restrict__ y, size_t n, float scale, float cap) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float v = y[i] * scale;
+  if (cap > 0.f) v = cap * tanhf(v / cap);
+  y[i] = v;
+}
+
+EMBER_API int ember_scale_cap_inplace(float* y, size_t n, float scale, float cap, cudaStream_t stream) {
+  EMBER_CHECK(n > 0 && cap >= 0.f, "scale_cap: %zu values, cap %g", n, (double)cap);
+  scale_cap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(y, n, scale, cap);
+  EMBER_LAUNCH_OK("scale_cap");
+  return 0;
+}
+
 EMBER_TIMELINE_READER(elementwise)

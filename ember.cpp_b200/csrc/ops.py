@@ -29,6 +29,7 @@ _SIGNATURES = {
     "ember_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ember_take_tokens": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
     "ember_act_inplace": [_c_void, _c_size, _c_int, _c_int, _c_void],
+    "ember_scale_cap_inplace": [_c_void, _c_size, _c_float, _c_float, _c_void],
     "ember_gemm_f32": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_bf16": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_void, _c_size, _c_void, _c_void],
@@ -336,6 +337,15 @@ class CudaOps:
         out.sort()
         return out
 
+    def scale_cap(self, x, scale: float = 1.0, cap: float | None = None):
+        """x <- scale * x, then (with a cap) cap * tanh(x / cap), in place on float32 values: a factor on
+        the embedded rows, a cap on the logits."""
+        if x.dtype != torch.float32:
+            raise KernelError("scale_cap: float32 values (the residual stream, the logits)")
+        self._call("ember_scale_cap_inplace", self._dense(x, "values").data_ptr(), x.numel(), float(scale),
+                   0.0 if cap is None else float(cap))
+        return x
+
     def take_tokens(self, tokens, token_src, ids, vocab_size: int) -> None:
         """tokens[i] = ids[token_src[i]] where token_src[i] >= 0: a step's tokens taken from an earlier
         step's sampled ids on the device."""
@@ -507,6 +517,8 @@ class CudaOps:
         out = torch.empty((plan.T, n_heads * head_dim), dtype=out_dtype, device=qkv.device)
         pages = plan.pages[cache.group_index]
         if qkv.dtype == torch.bfloat16 and plan.all_single:
+            if plan.T != plan.n:      # the decode kernels take token t for sequence t of the step
+                raise KernelError("attention: a step of one token each has as many tokens as sequences")
             blocks = min(plan.max_blocks, max(1, -(-plan.max_end // 64)))
             # The context is cut into chunks for separate blocks so that the launch fills the chip once: as
             # many chunks as resident blocks per (token, head) pair allow, at least two pages each (a block's

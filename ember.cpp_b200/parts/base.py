@@ -7,7 +7,7 @@ Roles and what each must provide:
 
   norm      forward(ctx, x, out_dtype, lazy=False) -> tensor         (x: fp32 residual stream)
   mixer     forward(ctx, h, residual, app) -> new residual stream    (h: normed input)
-            cache_need() -> CacheNeed | None, state_need() -> StateNeed | None
+            cache_need() -> CacheNeed | None, state_need() -> StateNeed | {name: StateNeed} | None
   ffn       forward(ctx, h, residual) -> new residual stream
   position  embedding_table() -> tensor | None, max_positions() -> int | None,
             apply_qk(ctx, qkv, n_heads, kv_heads, head_dim) (in place; default: nothing)
@@ -46,10 +46,12 @@ class CacheNeed:
 
 @dataclasses.dataclass(frozen=True)
 class StateNeed:
-    """Per-sequence state of fixed size: `shape` float32 values per sequence, set to `init` when a
-    sequence starts."""
+    """Per-sequence state of fixed size: `shape` values of `dtype` ("float32" or "int32") per
+    sequence, set to `init` when a sequence starts.  A mixer that keeps several tensors returns a
+    dict of these by name from `state_need()`, and finds a dict of tensors in `app.state`."""
     shape: tuple[int, ...]
     init: float = 0.0
+    dtype: str = "float32"
 
 
 class Part:
@@ -96,7 +98,7 @@ class Mixer(Part):
     def cache_need(self) -> CacheNeed | None:
         return None
 
-    def state_need(self) -> StateNeed | None:
+    def state_need(self) -> "StateNeed | dict[str, StateNeed] | None":
         return None
 
     def forward(self, ctx, h, residual, app):
@@ -127,12 +129,13 @@ class Position(Part):
 class Block(Part):
     role = "block"
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
+    def __init__(self, norm1: "Norm | None", mixer: Mixer, norm2: "Norm | None", ffn: FeedForward, **more_norms: Norm):
         super().__init__("")
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+        self.more_norms = dict(more_norms)     # the arrangement's further norms, by the names the spec gives them
 
     def parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.ffn]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, *self.more_norms.values()) if p is not None]
 
     def forward(self, ctx, x, app):
         raise NotImplementedError
@@ -143,7 +146,8 @@ _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {r: {} for r in ("norm", 
 
 def register_part(role: str, kind: str, factory: Callable[..., Part]) -> None:
     """Makes `kind` available to specs for `role`.  `factory(prefix=..., **params)` builds the
-    part (for a block: `factory(norm1, mixer, norm2, ffn)`)."""
+    part (for a block: `factory(norm1, mixer, norm2, ffn, **more_norms)`; a norm the spec leaves
+    out arrives as None)."""
     if role not in _REGISTRY:
         raise ValueError(f"unknown role {role!r}; roles: {sorted(_REGISTRY)}")
     _REGISTRY[role][kind] = factory
@@ -160,8 +164,8 @@ def build_part(role: str, spec: PartSpec) -> Part:
     return kinds[spec.kind](prefix=spec.prefix, **spec.params)
 
 
-def build_block(kind: str, norm1, mixer, norm2, ffn) -> Block:
+def build_block(kind: str, norm1, mixer, norm2, ffn, more_norms=None) -> Block:
     kinds = _REGISTRY["block"]
     if kind not in kinds:
         raise ValueError(f"no block arrangement {kind!r} is registered; registered: {registered('block')}")
-    return kinds[kind](norm1, mixer, norm2, ffn)
+    return kinds[kind](norm1, mixer, norm2, ffn, **(more_norms or {}))

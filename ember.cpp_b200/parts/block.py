@@ -13,6 +13,11 @@ from .base import Block, register_part
 
 
 class PreNormBlock(Block):
+    def __init__(self, norm1, mixer, norm2, ffn, **more_norms):
+        if norm1 is None or norm2 is None or more_norms:
+            raise ValueError("block 'pre_norm' has exactly two norms: one before the mixer, one before the feed-forward")
+        super().__init__(norm1, mixer, norm2, ffn)
+
 
     def forward(self, ctx, x, app):
         announce = getattr(ctx.ops, "announce_weights", None)

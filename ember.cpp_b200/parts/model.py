@@ -4,7 +4,9 @@ order, final norm, head.
 The order is ember.cpp's for every decoder it runs: embed nodes, the block nodes once per
 layer, then the head nodes on the wanted rows only (graph_ir.cpp:3010-3066; rows trimmed before
 the head :3049-3061): `h = norm(x_rows)`, `logits = h Whead^T` without bias, Whead being the
-token table when the head is tied (graph_ir.cpp:624-628, 757-762).
+token table when the head is tied (graph_ir.cpp:624-628, 757-762).  What other decoders put
+around that order is data of the spec, not code of a model: a factor on the embedded rows, a bias
+on the logits, a cap on them (cap * tanh(logits / cap)); GPT-2 uses none of the three.
 """
 from __future__ import annotations
 
@@ -21,11 +23,13 @@ class DecoderModel:
         self.position = build_part("position", spec.position)
         self.blocks = []
         for layer in spec.layers:
-            self.blocks.append(build_block(layer.block, build_part("norm", layer.norm1), build_part("mixer", layer.mixer),
-                                           build_part("norm", layer.norm2), build_part("ffn", layer.ffn)))
+            norm = lambda part: None if part is None else build_part("norm", part)  # noqa: E731
+            self.blocks.append(build_block(layer.block, norm(layer.norm1), build_part("mixer", layer.mixer), norm(layer.norm2),
+                                           build_part("ffn", layer.ffn), {name: norm(part) for name, part in layer.more_norms}))
         self.final_norm = build_part("norm", spec.final_norm)
         self.table = None
         self.head = None
+        self.head_bias = None
 
     # ------------------------------------------------------------------ tensors
     def all_parts(self):
@@ -39,6 +43,8 @@ class DecoderModel:
         specs = [WeightSpec(s.token_table, (s.vocab_size, s.width), std=s.table_init_std)]
         if s.head is not None:
             specs.append(WeightSpec(s.head, (s.vocab_size, s.width), std=s.table_init_std))
+        if s.head_bias is not None:
+            specs.append(WeightSpec(s.head_bias, (s.vocab_size,), std=s.table_init_std))
         for p in self.all_parts():
             specs += p.weight_specs()
         seen: dict[str, WeightSpec] = {}
@@ -53,6 +59,7 @@ class DecoderModel:
         get = tensors.__getitem__
         self.table = runtime.table(get(self.spec.token_table))
         self.head = self.table if self.spec.head is None else runtime.table(get(self.spec.head))
+        self.head_bias = None if self.spec.head_bias is None else runtime.vector(get(self.spec.head_bias))
         for p in self.all_parts():
             p.load(get, runtime)
 
@@ -76,6 +83,8 @@ class DecoderModel:
         logits [wanted rows, vocab] (None if no row is wanted)."""
         plan, ops = ctx.plan, ctx.ops
         x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table())
+        if self.spec.embedding_scale != 1.0:
+            x = ops.scale_cap(x, scale=self.spec.embedding_scale)
         for i, app in enumerate(ctx.apps):
             if i + 1 < len(ctx.apps):
                 ctx.next_norm = self.blocks[ctx.apps[i + 1].layer].norm1
@@ -89,4 +98,7 @@ class DecoderModel:
             return None
         rows = x if plan.wants_every_row else ops.gather_rows(x, plan.want_rows, plan.n_want)
         h = self.final_norm.forward(ctx, rows, ctx.dtype, lazy=True)
-        return ops.linear(h, self.head, None, out_dtype=torch.float32)
+        logits = ops.linear(h, self.head, self.head_bias, out_dtype=torch.float32)
+        if self.spec.logit_cap is not None:
+            logits = ops.scale_cap(logits, cap=self.spec.logit_cap)
+        return logits

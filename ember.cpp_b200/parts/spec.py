@@ -26,12 +26,15 @@ class PartSpec:
 @dataclasses.dataclass(frozen=True)
 class LayerSpec:
     """One layer's parts.  `block` names the arrangement (how norms, mixer, feed-forward and
-    the residual stream are wired)."""
+    the residual stream are wired).  An arrangement with one shared norm leaves `norm2` None; one
+    with more norms than two (norms after the mixer and after the feed-forward as well) names the
+    others in `more_norms`, and its block receives them as keyword arguments of those names."""
     block: str
-    norm1: PartSpec
+    norm1: PartSpec | None
     mixer: PartSpec
-    norm2: PartSpec
+    norm2: PartSpec | None
     ffn: PartSpec
+    more_norms: tuple[tuple[str, PartSpec], ...] = ()
 
 
 @dataclasses.dataclass(frozen=True)
@@ -53,6 +56,9 @@ class ModelSpec:
     schedule: tuple[Application, ...]
     final_norm: PartSpec
     head: str | None                 # tensor name of the [vocab, width] head; None: tied to the token table
+    embedding_scale: float = 1.0     # the embedded rows are multiplied by this (a model that scales by sqrt(width))
+    head_bias: str | None = None     # tensor name of a [vocab] bias added to the logits
+    logit_cap: float | None = None   # logits become cap * tanh(logits / cap)
     table_init_std: float = 0.02     # random-weights mode: std of the token table and the head
     stop_token_ids: tuple[int, ...] = ()
     # tensors that a checkpoint may hold and the model does not use (regular expressions)

@@ -87,6 +87,12 @@ class CpuOps:
                 out[t, h * head_dim:(h + 1) * head_dim] = pr @ v[:, h // rep, :]
         return out.to(out_dtype)
 
+    def scale_cap(self, x, scale=1.0, cap=None):
+        x.mul_(scale)
+        if cap is not None:
+            x.copy_(cap * torch.tanh(x / cap))
+        return x
+
     def take_tokens(self, tokens, token_src, ids, vocab_size):
         take = token_src >= 0
         tokens[take] = ids[token_src[take].long()].to(tokens.dtype)

@@ -13,7 +13,7 @@ from conftest import TOL, random_ids, rel_error, run_batch
 from ember_cpp_b200.cache import SequenceCache
 from ember_cpp_b200.engine import Engine, Runtime, StepContext, StepPlan, build_step
 from ember_cpp_b200.engine.engine import AppHandle
-from ember_cpp_b200.parts import (Application, DecoderModel, FeedForward, LayerSpec, Mixer, ModelSpec, PartSpec, Position,
+from ember_cpp_b200.parts import (Application, Block, DecoderModel, FeedForward, LayerSpec, Mixer, ModelSpec, PartSpec, Position,
                                   StateNeed, build_block,
                                   build_part, register_part)
 from ember_cpp_b200.weights import random_tensors
@@ -377,3 +377,133 @@ def test_toy_models_step_like_whole_sequences(ops, dtype, toy):
         eng.cache.check()
         assert eng.cache.slots.held == 0
         assert all(g.pages.free == g.pages.size for g in eng.cache.groups)
+
+
+# ------------------------------------------------------------------------------ other arrangements, model-level options
+class ToySandwich(Block):
+    """Norms before and after the mixer and the feed-forward: x + post1(mixer(norm1(x))), then the same
+    around the feed-forward.  The spec names the two further norms in `more_norms`."""
+
+    def __init__(self, norm1, mixer, norm2, ffn, post1, post2):
+        super().__init__(norm1, mixer, norm2, ffn, post1=post1, post2=post2)
+
+    def forward(self, ctx, x, app):
+        zero = torch.zeros_like(x)
+        a = self.mixer.forward(ctx, self.norm1.forward(ctx, x, ctx.dtype), zero, app)
+        x = x + self.more_norms["post1"].forward(ctx, a, torch.float32)
+        f = self.ffn.forward(ctx, self.norm2.forward(ctx, x, ctx.dtype), torch.zeros_like(x))
+        return x + self.more_norms["post2"].forward(ctx, f, torch.float32)
+
+
+class ToyParallel(Block):
+    """One norm shared by the mixer and the feed-forward, both branches added to the stream at once."""
+
+    def __init__(self, norm1, mixer, norm2, ffn):
+        assert norm2 is None
+        super().__init__(norm1, mixer, None, ffn)
+
+    def forward(self, ctx, x, app):
+        h = self.norm1.forward(ctx, x, ctx.dtype)
+        a = self.mixer.forward(ctx, h, torch.zeros_like(x), app)
+        f = self.ffn.forward(ctx, h, torch.zeros_like(x))
+        return x + a + f
+
+
+class ToyCounter(Mixer):
+    """A mixer with two state tensors of different types: a float32 running sum `s` <- decay * s + h W^T
+    and an int32 count of the sequence's tokens; its output is s + 0.01 * count."""
+    graph_safe = False
+
+    def __init__(self, prefix, width, decay):
+        super().__init__(prefix)
+        self.width, self.decay = width, decay
+
+    def weight_specs(self):
+        from ember_cpp_b200.parts import WeightSpec
+        return [WeightSpec(self.prefix + "mix.weight", (self.width, self.width), std=0.05)]
+
+    def load(self, get, runtime):
+        self.w = runtime.matrix(get(self.prefix + "mix.weight"))
+
+    def state_need(self):
+        return {"s": StateNeed((self.width,), init=0.5), "count": StateNeed((1,), init=0, dtype="int32")}
+
+    def forward(self, ctx, h, residual, app):
+        u = ctx.ops.linear(h, self.w, None, out_dtype=ctx.dtype).float()
+        slots, cu = ctx.plan.seq_slot.tolist(), ctx.plan.cu_new.tolist()
+        out = torch.empty_like(u)
+        for i, slot in enumerate(slots):
+            if slot < 0:
+                continue
+            s, n = app.state["s"][slot], int(app.state["count"][slot])
+            for t in range(cu[i], cu[i + 1]):
+                s, n = self.decay * s + u[t], n + 1
+                out[t] = s + 0.01 * n
+            app.state["s"][slot] = s
+            app.state["count"][slot] = n
+        return residual + out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_other_arrangements_states_and_model_options(ops, dtype):
+    """What a model needs beyond GPT-2's shape is data of the spec and parts registered from outside: a layer with
+    four norms (before and after each branch), a layer with one shared norm and parallel branches, a mixer that
+    keeps two state tensors of different types, a factor on the embedded rows, a bias on the logits and a cap on
+    them.  Stepped in unequal batches one after another, like whole sequences in the plain restatement below."""
+    register_part("block", "toy_sandwich", ToySandwich)
+    register_part("block", "toy_parallel", ToyParallel)
+    register_part("mixer", "toy_counter", ToyCounter)
+    width, vocab, eps, cap = 64, 210, 1e-5, 5.0
+    ln = lambda prefix: PartSpec("layernorm", prefix, {"width": width, "eps": eps})  # noqa: E731
+    dense = lambda prefix: PartSpec("dense", prefix, {"width": width, "inner": 136, "activation": "gelu_tanh", "up": "up",  # noqa: E731
+                                                      "down": "down", "stored": "out_in", "init_std": 0.08, "down_init_std": 0.08})
+    attn = PartSpec("causal_attention", "l0.attn.", {"width": width, "n_heads": 4, "kv_heads": 2, "head_dim": 16, "scale": 0.25,
+                                                     "qkv": "qkv", "out": "o", "stored": "out_in", "init_std": 0.08,
+                                                     "out_init_std": 0.08})
+    layers = (LayerSpec("toy_sandwich", ln("l0.n1."), attn, ln("l0.n2."), dense("l0.ffn."),
+                        more_norms=(("post1", ln("l0.p1.")), ("post2", ln("l0.p2.")))),
+              LayerSpec("toy_parallel", ln("l1.n1."), PartSpec("toy_counter", "l1.cnt.", {"width": width, "decay": 0.7}), None,
+                        dense("l1.ffn.")))
+    spec = ModelSpec(width=width, vocab_size=vocab, token_table="embed.weight",
+                     position=PartSpec("learned_absolute", "pos.", {"width": width, "n_positions": 160}),
+                     layers=layers, schedule=(Application(0), Application(1)), final_norm=ln("norm."), head="head.weight",
+                     table_init_std=0.3, embedding_scale=math.sqrt(width), head_bias="head.bias", logit_cap=cap)
+    tensors = random_tensors(DecoderModel(spec).weight_specs(), 9, torch.bfloat16)
+    w = {k: f64(v) for k, v in tensors.items()}
+    eng = Engine.from_spec(spec, tensors, dtype=dtype, max_tokens=1024, ops=ops)
+    assert isinstance(eng.apps[1].state, dict) and eng.apps[1].state["count"].dtype == torch.int32
+    assert len(eng.model.blocks[0].parts()) == 6 and len(eng.model.blocks[1].parts()) == 3
+
+    def plain(ids):
+        P = plain_gpt2
+        norm = lambda x, p: P.layer_norm(x, w[p + "weight"], w[p + "bias"], eps)  # noqa: E731
+        mlp = lambda h, p: P.mlp(h, w[p + "up.weight"], w[p + "up.bias"], w[p + "down.weight"], w[p + "down.bias"], "tanh")  # noqa: E731
+        x = P.position_embedding(P.token_embedding(w["embed.weight"], ids), w["pos.weight"]) * math.sqrt(width)
+        # (the factor applies to the embedded rows as a whole, positions included: it follows the embedding kernel)
+        q, k, v = P.split_qkv(P.linear(norm(x, "l0.n1."), w["l0.attn.qkv.weight"], w["l0.attn.qkv.bias"]), 4, 2, 16)
+        a = P.linear(P.attention(q, k, v, 4, 2, 16, 0.25), w["l0.attn.o.weight"], w["l0.attn.o.bias"])
+        x = x + norm(a, "l0.p1.")
+        x = x + norm(mlp(norm(x, "l0.n2."), "l0.ffn."), "l0.p2.")
+        h = norm(x, "l1.n1.")
+        u = h @ w["l1.cnt.mix.weight"].T
+        s, out = np.full(width, 0.5), np.zeros_like(u)
+        for t in range(len(ids)):
+            s = 0.7 * s + u[t]
+            out[t] = s + 0.01 * (t + 1)
+        x = x + out + mlp(h, "l1.ffn.")
+        logits = norm(x, "norm.") @ w["head.weight"].T + w["head.bias"]
+        return cap * np.tanh(logits / cap)
+
+    seqs = [random_ids(40 + i, vocab, n) for i, n in enumerate((150, 33, 70))]
+    tol = 1e-5 if dtype == "float32" else 2e-2
+    for batch in ((40, 1, 70), (100, 20, 5)):
+        rows, _ = run_batch(eng, seqs, batch)
+        for ids, got in zip(seqs, rows):
+            assert np.abs(got).max() <= cap
+            assert rel_error(got, plain(ids)) < tol
+        eng.cache.check()
+        assert eng.cache.slots.held == 0
+    with pytest.raises(ValueError, match="exactly two norms"):       # GPT-2's arrangement says what it needs
+        DecoderModel(ModelSpec(width=width, vocab_size=vocab, token_table="embed.weight", position=spec.position,
+                               layers=(LayerSpec("pre_norm", ln("a."), attn, None, dense("b.")),), schedule=(Application(0),),
+                               final_norm=ln("norm."), head=None))
