@@ -215,6 +215,25 @@ def linear_mode(args) -> int:
     return 0
 
 
+def umma_issue_mode() -> int:
+    """Cycles per tcgen05.mma by shape and by the way it is issued (see csrc/umma_probe.cu)."""
+    from ember_cpp_b200.csrc.ops import CudaOps
+    ops = CudaOps()
+    for m in (128, 64):
+        for n in (16, 64, 128, 256):
+            for elected in (False, True):
+                ops.umma_issue_probe(m, n, 64, elected)
+                issue, done = ops.umma_issue_probe(m, n, 512, elected)
+                print(f"M={m:3d} N={n:3d} {'elect.sync, whole warp ' if elected else 'if (thread == 0)       '}: {issue:6.1f} cycles to issue, "
+                      f"{done:6.1f} until complete, {2.0 * m * n * 16 / done:6.0f} flop a cycle")
+    for every in (1, 4, 8, 16):
+        for wait_too in (False, True):
+            issue, done = ops.umma_issue_probe(128, 64, 512, True, commit_every=every, wait_too=wait_too)
+            print(f"M=128 N= 64 elect.sync, a tcgen05.commit after every {every:2d}{', a satisfied wait and a fence before' if wait_too else ''}: "
+                  f"{issue * every:6.1f} cycles a group, {issue:6.1f} a product")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -231,7 +250,10 @@ def main() -> int:
                     help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
     ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
     ap.add_argument("--residual", action="store_true", help="with --linear: add a float32 residual (the output is float32 then)")
+    ap.add_argument("--umma-issue", action="store_true", help="print what a tcgen05.mma costs to issue, by shape and way of issuing")
     args = ap.parse_args()
+    if args.umma_issue:
+        return umma_issue_mode()
     if args.linear:
         return linear_mode(args)
     if args.impl == "reference":

@@ -174,7 +174,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       if (!__all_sync(0xffffffffu, mbar_wait(kv_full + 8 * st, (it / kStages) & 1) && mbar_wait(s_free + 8 * b, ((it >> 1) & 1) ^ 1)))
         return false;
       fence_after();
-      // every lane holds the same operands and one elected lane issues (tc_common.cuh: that is the fast way)
+      // every lane holds the same operands and one elected lane issues (tc_common.cuh)
       const unsigned long long dk = smem_desc_sw128(sKV + st * 2 * kPageBytes);
 #pragma unroll
       for (int k = 0; k < HD / 16; ++k) umma_1cta_elect(tmem + 64 * b, dq + 2 * k, dk + 2 * k, idesc_s, k != 0);  // 32 bytes of a row a step

@@ -42,6 +42,21 @@ struct Plan {
 cublasLtHandle_t g_handle = nullptr;
 std::mutex g_mutex;
 std::unordered_map<PlanKey, Plan, PlanHash> g_plans;
+// The algorithm that timing chose, kept per bucket of M (M rounded up to a multiple of 128): every new
+// prompt-length mix is a new M, and timing eight candidates for each would put milliseconds into the
+// request path; a bucket is timed once and its choice is checked (not timed) for the other M of the bucket.
+std::unordered_map<PlanKey, cublasLtMatmulAlgo_t, PlanHash> g_tuned;
+constexpr size_t kMaxPlans = 512;  // descriptors kept; beyond that all are dropped and made again as they come
+
+void drop_plans() {
+  for (auto& kv : g_plans) {
+    cublasLtMatmulDescDestroy(kv.second.op);
+    cublasLtMatrixLayoutDestroy(kv.second.a);
+    cublasLtMatrixLayoutDestroy(kv.second.b);
+    cublasLtMatrixLayoutDestroy(kv.second.c);
+  }
+  g_plans.clear();
+}
 
 const char* lt_status(cublasStatus_t s) {
   switch (s) {
@@ -151,8 +166,9 @@ void tune_plan(Plan* plan, const cublasLtMatmulAlgo_t* more, int n_more, const v
 // where the library takes it with this output type, else the bfloat16 one.
 // residual: float32 [M,N] added to the product (out is float32 then, and may be the same buffer).
 // act: none or the tanh GELU (the erf form is not a library epilogue; the caller applies it).
-// tune_scratch: null, or a buffer as large as the output: the first call for a shape then times
-// the library's candidate algorithms there (synchronizing the stream) and keeps the fastest.
+// tune_scratch: null, or a buffer as large as the output: the first call for a shape whose bucket of
+// M (multiples of 128) has not been timed yet then times the library's candidate algorithms there
+// (synchronizing the stream) and keeps the fastest for the bucket.
 EMBER_API int ember_linear_bf16(const void* A, const void* W, const float* bias_f32, const void* bias_bf16,
                                 const float* residual, void* out, int M, int N, int K, int act, int out_dtype,
                                 void* workspace, size_t workspace_bytes, void* tune_scratch, cudaStream_t stream) {
@@ -164,31 +180,43 @@ EMBER_API int ember_linear_bf16(const void* A, const void* W, const float* bias_
   EMBER_CHECK(K % 8 == 0, "linear_bf16: K = %d is not a multiple of 8 (16-byte rows)", K);
   EMBER_CHECK((bias_f32 == nullptr) == (bias_bf16 == nullptr), "linear_bf16: give the bias in both types or not at all");
   const PlanKey key{M, N, K, act, bias_f32 != nullptr, residual != nullptr, out_dtype};
-  Plan plan;
-  {
-    std::lock_guard<std::mutex> lock(g_mutex);
-    if (!g_handle) LT_TRY(cublasLtCreate(&g_handle));
-    auto it = g_plans.find(key);
-    if (it == g_plans.end()) {
-      Plan fresh;
-      cublasLtMatmulAlgo_t more[kCandidates];
-      int n_more = 0;
-      int rc = make_plan(key, /*bias_bf16=*/false, workspace_bytes, &fresh, more, &n_more);
-      if (rc == 2 && key.bias) rc = make_plan(key, /*bias_bf16=*/true, workspace_bytes, &fresh, more, &n_more);
-      if (rc == 2) return ember_fail("linear_bf16: the library has no algorithm for M=%d N=%d K=%d", M, N, K);
-      if (rc != 0) return rc;
-      if (tune_scratch && n_more > 0) {
+  PlanKey bucket = key;
+  bucket.M = (M + 127) / 128 * 128;
+  // One lock from the look-up to the launch: a plan's descriptor is shared by all callers of its shape,
+  // and the bias pointer is set on it for this call (the launch itself only queues work).
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_handle) LT_TRY(cublasLtCreate(&g_handle));
+  auto it = g_plans.find(key);
+  if (it == g_plans.end()) {
+    if (g_plans.size() >= kMaxPlans) drop_plans();
+    Plan fresh;
+    cublasLtMatmulAlgo_t more[kCandidates];
+    int n_more = 0;
+    int rc = make_plan(key, /*bias_bf16=*/false, workspace_bytes, &fresh, more, &n_more);
+    if (rc == 2 && key.bias) rc = make_plan(key, /*bias_bf16=*/true, workspace_bytes, &fresh, more, &n_more);
+    if (rc == 2) return ember_fail("linear_bf16: the library has no algorithm for M=%d N=%d K=%d", M, N, K);
+    if (rc != 0) return rc;
+    if (tune_scratch) {
+      auto tuned = g_tuned.find(bucket);
+      cublasLtMatmulHeuristicResult_t check;
+      if (tuned != g_tuned.end()) {  // this bucket was timed before: its choice, if the library takes it for this M too
+        if (cublasLtMatmulAlgoCheck(g_handle, fresh.op, fresh.a, fresh.b, fresh.c, fresh.c, &tuned->second, &check) ==
+                CUBLAS_STATUS_SUCCESS &&
+            check.state == CUBLAS_STATUS_SUCCESS && check.workspaceSize <= workspace_bytes)
+          fresh.algo = tuned->second;
+      } else if (n_more > 0) {
         if (key.bias) {
           const void* bias = fresh.bias_is_bf16 ? bias_bf16 : (const void*)bias_f32;
           LT_TRY(cublasLtMatmulDescSetAttribute(fresh.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias)));
         }
         tune_plan(&fresh, more, n_more, A, W, residual, residual ? 1.0f : 0.0f, tune_scratch, workspace, workspace_bytes,
                   stream);
+        g_tuned.emplace(bucket, fresh.algo);
       }
-      it = g_plans.emplace(key, fresh).first;
     }
-    plan = it->second;
+    it = g_plans.emplace(key, fresh).first;
   }
+  const Plan& plan = it->second;
   if (key.bias) {
     const void* bias = plan.bias_is_bf16 ? bias_bf16 : (const void*)bias_f32;
     LT_TRY(cublasLtMatmulDescSetAttribute(plan.op, CUBLASLT_MATMUL_DESC_BIAS_POINTER, &bias, sizeof(bias)));

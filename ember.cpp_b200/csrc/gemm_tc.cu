@@ -79,8 +79,7 @@ __device__ __forceinline__ void load_2d(unsigned dst, const CUtensorMap* map, in
 }
 
 // Issued by a whole, converged warp whose lanes all hold the same operands; one elected lane
-// issues (tc_common.cuh says why: from a single thread's branch a product costs 156 cycles to issue
-// against 128 of arithmetic for N = 256).
+// issues (tc_common.cuh has the measured cost of an instruction by shape and way of issuing).
 template <int CTAS>
 __device__ __forceinline__ void umma(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
                                      unsigned accumulate) {

@@ -208,18 +208,14 @@ __global__ void __launch_bounds__(kThreads, 2)
       __syncwarp();
     }
     if (!ok && lane == 0) atomicCAS(p.status, 0, ST_PRODUCER), s_failed = 1;
-    // Copies in flight land in this block's shared memory: the block may not end before them.  In
-    // a launch that runs to its end the `done` barrier covers them (every stage was used); here
-    // the last turn's hand-backs are awaited as well, so that an error on the way still drains.
-    for (int j = max(0, it - p.stages); j < it; ++j)
-      if (!mbar_wait(empty0 + 8 * (j % p.stages), (j / p.stages) & 1)) {
-        if (lane == 0) atomicCAS(p.status, 0, ST_DRAIN);
-        break;
-      }
+    // Copies in flight land in this block's shared memory: the block may not end before them.  The
+    // `done` barrier covers them (the last product has read the last stage); on the way out after
+    // an error the wait simply runs out.
+    if (!mbar_wait(done, 0) && ok && lane == 0) atomicCAS(p.status, 0, ST_DRAIN);
   } else if (warp == 1) {
     // ------------------------------------------------------------------ products
     // The whole warp runs the loop with the same values in every lane and one elected lane issues
-    // (tc_common.cuh: issued from a single thread's branch a product costs 156 cycles, this way 67).
+    // (tc_common.cuh).  A product of N = 64 costs 48 cycles, a box of K four of them.
     const unsigned idesc = instr_desc_bf16(BM, p.mp, false);
     for (int it = 0; it < n_kb && ok; ++it) {
       const int s = it % p.stages;
@@ -230,7 +226,9 @@ __global__ void __launch_bounds__(kThreads, 2)
       const unsigned long long dw = smem_desc_sw128(base + s * stage_bytes), dx = smem_desc_sw128(base + s * stage_bytes + kWBox);
 #pragma unroll
       for (int k = 0; k < BK / 16; ++k) umma_1cta_elect(tmem, dw + 2 * k, dx + 2 * k, idesc, (it | k) != 0);  // 32 bytes a step
-      umma_commit_1cta_elect(empty0 + 8 * s);
+      // a stage is handed back only if it is filled again: a tcgen05.commit costs the issuing warp about
+      // 200 cycles (bench.py --umma-issue), as much as the stage's four products
+      if (it + p.stages < n_kb) umma_commit_1cta_elect(empty0 + 8 * s);
       if (it == n_kb - 1) umma_commit_1cta_elect(done);
     }
     if (!ok && lane == 0) atomicCAS(p.status, 0, ST_MMA), s_failed = 1;

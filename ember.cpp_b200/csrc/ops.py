@@ -102,6 +102,8 @@ def load_library() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = _c_int
+    lib.ember_umma_issue_probe.argtypes = [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void]
+    lib.ember_umma_issue_probe.restype = _c_int
     lib.ember_wait_probe.argtypes = [_c_u64, _c_void]
     lib.ember_wait_probe.restype = _c_int
     lib.ember_set_option.argtypes = [_c_int, _c_int]
@@ -462,6 +464,16 @@ class CudaOps:
                    M, w.shape[0], K, _ACT[act], _code(out.dtype), int(k_split), int(stages),
                    None if warm is None else warm.data_ptr(), 0 if warm is None else warm.numel() * warm.element_size() // 16 * 16)
         return out
+
+    def umma_issue_probe(self, m: int, n: int, iters: int = 512, elected: bool = True, commit_every: int = 0, wait_too: bool = False):
+        """(cycles to issue, cycles until complete) per `tcgen05.mma` of M = m, N = n, K = 16, issued from a single
+        thread's branch or by a converged warp with elect.sync (umma_probe.cu).  A measurement for the notes."""
+        out = torch.zeros(3, dtype=torch.int64, device="cuda")
+        self._call("ember_umma_issue_probe", int(m), int(n), int(iters), 1 if elected else 0, int(commit_every), 1 if wait_too else 0, out.data_ptr())
+        issue, done, ended = out.tolist()
+        if not ended:
+            raise KernelError("umma_issue_probe: the products did not complete within the wait's limit")
+        return issue / iters, done / iters
 
     def wait_probe(self, limit_ns: int = 1_000_000) -> None:
         """Launches the kernel whose only wait nothing ends (wait_probe.cu): it gives up after `limit_ns`

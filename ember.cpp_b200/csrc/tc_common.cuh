@@ -98,11 +98,12 @@ __device__ __forceinline__ void umma_1cta(unsigned tmem_d, unsigned long long a,
       : "memory");
 }
 // The same two instructions issued by a whole, converged warp whose lanes all hold the same
-// operands: one elected lane issues.  This is the fast way: operands that are the same in every
-// lane live in the warp's uniform registers, which is where the instruction reads them; issued
-// from inside `if (lane == 0)` every operand is first moved there from an ordinary register, and a
-// product costs 156 cycles to issue whatever its size, against 64 to 67 (measured; a product of
-// N = 256 needs 128 cycles of arithmetic, so the slow way caps a kernel at about 0.8 of the peak).
+// operands: one elected lane issues.  Operands that are the same in every lane can live in the
+// warp's uniform registers, which is where the instruction reads them.  Measured (`bench.py
+// --umma-issue`, umma_probe.cu): for M = 128 both ways cost the same, 46 to 48 cycles an
+// instruction up to N = 64, 64 at N = 128 and 128 at N = 256 (the arithmetic itself, so an
+// instruction narrower than N = 128 leaves the pipe idle part of the time); for M = 64 and N up
+// to 64 the elected form takes 24 to 33 cycles against 46.  The product loops use this form.
 __device__ __forceinline__ void umma_1cta_elect(unsigned tmem_d, unsigned long long a, unsigned long long b, unsigned idesc,
                                                 unsigned accumulate) {
   asm volatile(
