@@ -148,9 +148,11 @@ class CudaOps:
         #   or 128, up to 8 query heads to a key/value head); off takes the other kernel.
         self.decode_mma = options.decode_mma
         # tail_norm: the norm that follows a sum into the residual stream runs in the tail of that sum's product
-        #   (`expect_norm` announces it, `layernorm` then finds its result ready).  Off: at batch 8 it changes
-        #   nothing (0.780 against 0.782 ms a step of 12 layers): the separate norm kernels already hide behind
-        #   the next product's weight fetch.
+        #   (`expect_norm` announces it, `layernorm` then finds its result ready).  Off: at batch 8 a step of
+        #   GPT-2 XL takes 2.08 against 1.44 ms with it.  The separate norm kernel is not only hidden: while it
+        #   runs, every block of the next product is resident (nothing else holds shared memory) and has its
+        #   weights on the way; without it the next product's last blocks start when the sum's blocks leave and
+        #   wait for their weights then.
         self.tail_norm = options.tail_norm
         self._expected = None          # (gain, bias, eps, dtype) announced for the next sum
         self._warm = None              # tensor announced by `warm` for the next product
@@ -368,9 +370,10 @@ class CudaOps:
         sum is made in float32 into the residual's buffer, which is returned."""
         if act not in _ACT:
             raise KernelError(f"linear: activation {act!r}")
-        expected, self._expected = self._expected, None
+        expected = None
         warm, self._warm = self._warm, None
-        if residual is not None:
+        if residual is not None:       # the sum into the stream that an announced norm follows
+            expected, self._expected = self._expected, None
             self._normed = None        # the stream changes: an earlier norm of it is stale
         norm = None
         if isinstance(a, LazyNorm):
