@@ -13,6 +13,15 @@
 // the order of addition), 11 bits a pass, stopping as soon as the bucket holds one candidate.  The
 // row's p values are kept in shared memory when the vocabulary fits (up to about 51,000 entries);
 // otherwise they are recomputed from the logits in each pass.
+//
+// A small top_k (the usual case: 40 of 50,257) needs no selection over the whole row.  Each of the
+// block's 512 threads knows the largest p among its own entries; the top_k-th largest of those 512
+// values is a lower bound of the top_k-th largest p of the row (at least top_k entries reach it), so
+// every candidate of the top_k lies at or above it, and with entries dealt to threads in turn only a
+// few more do.  They are gathered into a short list and finished there; a row whose list would not
+// fit (thousands of equal values at the edge) takes the radix selection instead.  The row itself comes
+// into shared memory by 4-byte asynchronous copies, all in flight at once: one trip to L2, where the
+// product that wrote the logits left them.
 #include "common.cuh"
 
 namespace {
@@ -186,52 +195,12 @@ __device__ u64 radix_select(const Row& row, int V, bool by_mass, u64 need, unsig
 constexpr int kSmallK = 512;   // top_k up to which the candidates are finished as a short list
 constexpr int kListCap = 1024;  // entries of that list
 
-// The short way for a small top_k.  Radix passes by count run only until the candidates that can
-// still be among the top_k (those above the chosen bucket, fewer than top_k, and the bucket itself)
-// number at most kListCap; these are gathered into a list and finished there: each one's rank and
-// the mass above it by comparison with all others, the kept set (rank < top_k, and the mass above
-// it short of the top_p target: the same set as the two radix selections give), and the draw in
-// index order.  Integer masses make every sum independent of the list's order.  Returns false
-// (having written nothing) when the list would not fit, which takes a bucket of hundreds of
-// candidates with the same leading digits on every level.
-__device__ bool sample_small(const Row& row, int V, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
-                             unsigned* cnt, u64* list, u64* scratch, int* s_hit, u64* s_before, int* s_n) {
-  const int shifts[6] = {53, 42, 32, 21, 10, 0};
-  const int widths[6] = {11, 11, 10, 11, 11, 10};
-  u64 prefix = 0, need = (u64)top_k, above = 0;
-  bool fits = false;
-  for (int pass = 0; pass < 6 && !fits; ++pass) {
-    const int shift = shifts[pass];
-    if (pass >= 3 && ((u64)(V - 1) >> shift) == 0 && shift > 0) continue;
-    const u64 high_mask = pass == 0 ? 0ull : ~0ull << (shift + widths[pass]);
-    const unsigned digit_mask = (1u << widths[pass]) - 1;
-    for (int b = threadIdx.x; b < kBins; b += kThreads) cnt[b] = 0;
-    __syncthreads();
-    for (int i = threadIdx.x; i < V; i += kThreads) {
-      const u64 key = key_of(row.p(i), i);
-      if ((key & high_mask) == prefix) {
-        const int b = (int)((key >> shift) & digit_mask);
-        const unsigned peers = __match_any_sync(__activemask(), b);
-        if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[b], (unsigned)__popc(peers));
-      }
-    }
-    __syncthreads();
-    const Pick pick = find_bucket(cnt, nullptr, false, need, scratch, s_hit, s_before);
-    prefix |= (u64)pick.bin << shift;
-    if (pick.none) return false;  // fewer candidates than top_k: not this function's case
-    need -= pick.before;
-    above += pick.before;
-    fits = above + pick.count <= (u64)kListCap;
-  }
-  if (!fits) return false;
-  if (threadIdx.x == 0) *s_n = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < V; i += kThreads) {
-    const u64 key = key_of(row.p(i), i);
-    if (key >= prefix) list[atomicAdd(s_n, 1)] = key;
-  }
-  __syncthreads();
-  const int n = *s_n;
+// The end of both short ways: the candidates are in `list` (n <= kListCap keys, in any order; room for
+// kListCap masses behind them).  Each one's rank and the mass above it by comparison with all others, the
+// kept set (rank < top_k, and the mass above it short of the top_p target: the same set as the two radix
+// selections give), and the draw in index order.
+__device__ void finish_list(u64* list, int n, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
+                            u64* scratch, int* s_hit) {
   u64* kept_mass = list + kListCap;
   constexpr int kPer = kListCap / kThreads;
   u64 my_key[kPer], my_mass[kPer];
@@ -280,6 +249,89 @@ __device__ bool sample_small(const Row& row, int V, int top_k, bool use_p, u64 n
   }
   __syncthreads();
   if (threadIdx.x == 0) out[blockIdx.x] = *s_hit;
+}
+
+// The short way for a small top_k.  Radix passes by count run only until the candidates that can
+// still be among the top_k (those above the chosen bucket, fewer than top_k, and the bucket itself)
+// number at most kListCap; these are gathered into a list and finished there: each one's rank and
+// the mass above it by comparison with all others, the kept set (rank < top_k, and the mass above
+// it short of the top_p target: the same set as the two radix selections give), and the draw in
+// index order.  Integer masses make every sum independent of the list's order.  Returns false
+// (having written nothing) when the list would not fit, which takes a bucket of hundreds of
+// candidates with the same leading digits on every level.
+__device__ bool sample_small(const Row& row, int V, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
+                             unsigned* cnt, u64* list, u64* scratch, int* s_hit, u64* s_before, int* s_n) {
+  const int shifts[6] = {53, 42, 32, 21, 10, 0};
+  const int widths[6] = {11, 11, 10, 11, 11, 10};
+  u64 prefix = 0, need = (u64)top_k, above = 0;
+  bool fits = false;
+  for (int pass = 0; pass < 6 && !fits; ++pass) {
+    const int shift = shifts[pass];
+    if (pass >= 3 && ((u64)(V - 1) >> shift) == 0 && shift > 0) continue;
+    const u64 high_mask = pass == 0 ? 0ull : ~0ull << (shift + widths[pass]);
+    const unsigned digit_mask = (1u << widths[pass]) - 1;
+    for (int b = threadIdx.x; b < kBins; b += kThreads) cnt[b] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += kThreads) {
+      const u64 key = key_of(row.p(i), i);
+      if ((key & high_mask) == prefix) {
+        const int b = (int)((key >> shift) & digit_mask);
+        const unsigned peers = __match_any_sync(__activemask(), b);
+        if ((threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&cnt[b], (unsigned)__popc(peers));
+      }
+    }
+    __syncthreads();
+    const Pick pick = find_bucket(cnt, nullptr, false, need, scratch, s_hit, s_before);
+    prefix |= (u64)pick.bin << shift;
+    if (pick.none) return false;  // fewer candidates than top_k: not this function's case
+    need -= pick.before;
+    above += pick.before;
+    fits = above + pick.count <= (u64)kListCap;
+  }
+  if (!fits) return false;
+  if (threadIdx.x == 0) *s_n = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += kThreads) {
+    const u64 key = key_of(row.p(i), i);
+    if (key >= prefix) list[atomicAdd(s_n, 1)] = key;
+  }
+  __syncthreads();
+  finish_list(list, *s_n, top_k, use_p, need_p, u24, fallback, out, scratch, s_hit);
+  return true;
+}
+
+// The other way to the short list (see the head of the file): the threshold is the top_k-th largest of
+// the threads' own maxima.  lmax: kThreads floats of scratch.  Returns false (nothing written) if more
+// than kListCap entries reach the threshold.
+__device__ bool sample_by_thread_maxima(const float* s_p, int V, float my_max, int top_k, bool use_p, u64 need_p, u64 u24,
+                                        int fallback, int* out, float* lmax, u64* list, u64* scratch, int* s_hit, int* s_n) {
+  __shared__ float s_thr;
+  lmax[threadIdx.x] = my_max;  // -1 for a thread without entries
+  if (threadIdx.x == 0) {
+    *s_n = 0;
+    s_thr = -1.f;              // fewer threads with entries than top_k: everything is a candidate
+  }
+  __syncthreads();
+  int rank = 0;
+  for (int j = 0; j < kThreads; ++j) {
+    const float o = lmax[j];
+    rank += (o > my_max || (o == my_max && j < (int)threadIdx.x)) ? 1 : 0;
+  }
+  if (rank == top_k - 1 && my_max >= 0.f) s_thr = my_max;
+  __syncthreads();
+  const float thr = s_thr;
+  for (int i = threadIdx.x; i < V; i += kThreads) {
+    const float p = s_p[i];
+    if (p >= thr) {
+      const int at = atomicAdd(s_n, 1);
+      if (at < kListCap) list[at] = key_of(p, i);
+    }
+  }
+  __syncthreads();
+  const int n = *s_n;
+  __syncthreads();
+  if (n > kListCap) return false;
+  finish_list(list, n, top_k, use_p, need_p, u24, fallback, out, scratch, s_hit);
   return true;
 }
 
@@ -301,19 +353,38 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   const float* rowp = logits + (size_t)blockIdx.x * V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
+  // The row comes into shared memory first when it fits: a 4-byte asynchronous copy for every entry, all
+  // of a thread's in flight together (no registers wait for them), so the row costs one trip to L2.
+  if (CACHED) {
+    for (int i = threadIdx.x; i < V; i += kThreads)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(s_p + i)), "l"(rowp + i)
+                   : "memory");
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+    __syncthreads();
+  }
   // first maximal index; NaN never wins
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {  // eight loads in flight a thread
-    float l[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) l[j] = i0 + j * kThreads < V ? __ldg(rowp + i0 + j * kThreads) : -INFINITY;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int i = i0 + j * kThreads;
-      if (l[j] > best || (l[j] == best && i < best_i)) {  // indices ascend, so the first maximum stays
-        best = l[j];
+  if (CACHED) {
+    for (int i = threadIdx.x; i < V; i += kThreads) {
+      const float l = s_p[i];
+      if (l > best) {  // indices ascend, so the first maximum stays
+        best = l;
         best_i = i;
+      }
+    }
+  } else {
+    for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {  // eight loads in flight a thread
+      float l[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) l[j] = i0 + j * kThreads < V ? __ldg(rowp + i0 + j * kThreads) : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + j * kThreads;
+        if (l[j] > best || (l[j] == best && i < best_i)) {  // indices ascend, so the first maximum stays
+          best = l[j];
+          best_i = i;
+        }
       }
     }
   }
@@ -352,17 +423,24 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   if (top_k <= 0 || top_k > V) top_k = V;
 
   u64 z = 0;
-  for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {
-    float l[8];
+  float my_max = -1.f;  // the largest p among this thread's entries (CACHED)
+  if (CACHED) {
+    for (int i = threadIdx.x; i < V; i += kThreads) {
+      const float l = s_p[i];
+      const float p = (l == l) ? expf((l - row.mx) * row.inv_t) : 0.f;  // as Row::p
+      s_p[i] = p;  // (an entry is read and written by this thread alone)
+      my_max = fmaxf(my_max, p);
+      z += mass_of(p);
+    }
+  } else {
+    for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {
+      float l[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) l[j] = i0 + j * kThreads < V ? __ldg(rowp + i0 + j * kThreads) : 0.f;
+      for (int j = 0; j < 8; ++j) l[j] = i0 + j * kThreads < V ? __ldg(rowp + i0 + j * kThreads) : 0.f;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int i = i0 + j * kThreads;
-      if (i < V) {
-        const float p = (l[j] == l[j]) ? expf((l[j] - row.mx) * row.inv_t) : 0.f;  // as Row::p
-        if (CACHED) s_p[i] = p;
-        z += mass_of(p);
+      for (int j = 0; j < 8; ++j) {
+        const int i = i0 + j * kThreads;
+        if (i < V) z += mass_of((l[j] == l[j]) ? expf((l[j] - row.mx) * row.inv_t) : 0.f);  // as Row::p
       }
     }
   }
@@ -372,6 +450,9 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   if (top_k < V && top_k <= kSmallK) {
     const u64 u = splitmix_uniform24(seed, (u64)streams[blockIdx.x], (u64)counters[blockIdx.x]);
     const u64 need_p = (u64)ceil((double)fmaxf(top_p, 0.f) * (double)z);
+    if (CACHED && sample_by_thread_maxima(s_p, V, my_max, top_k, top_p < 1.0f, need_p, u, best_i, out,
+                                          reinterpret_cast<float*>(s_cnt), s_mass, s_u64, &s_hit, &s_n))
+      return;
     if (sample_small(row, V, top_k, top_p < 1.0f, need_p, u, best_i, out, s_cnt, s_mass, s_u64, &s_hit, &s_before, &s_n)) return;
   }
 
