@@ -323,9 +323,7 @@ def main() -> int:
         slots = [eng.open() for _ in range(B)]
         prompts = [rng.integers(0, config.vocab_size, n).tolist() for n in lengths]
         logits = eng.step([(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
-        streams = torch.arange(B, dtype=torch.int32, device="cuda")
-        counters = torch.zeros(B, dtype=torch.int32, device="cuda")
-        ids = smp.sample(logits, params, streams, counters)
+        ids = smp.sample(logits, params, list(range(B)), [0] * B, out=eng.sample_target(B))
         on_the_way = smp.fetch(ids)
         live = list(range(B))
         rows = list(range(B))
@@ -344,8 +342,7 @@ def main() -> int:
                 tokens += len(live)
                 timed_steps += 1
             logits = eng.step([(slots[j], [0], [0]) for j in live], borrow=True, device_tokens=(ids, rows))
-            counters[:len(live)] += 1
-            following = smp.sample(logits, params, streams[:len(live)], counters[:len(live)])
+            following = smp.sample(logits, params, live, [i + 1] * len(live), out=eng.sample_target(len(live)))
             fetched = smp.fetch(following)
             on_the_way.tolist()
             ids, on_the_way = following, fetched

@@ -29,29 +29,63 @@ EMBER_API int ember_set_option(int which, int value) {
 }
 
 // ---------------------------------------------------------------------------- embedding
+// x[t, :] = table[token_t, :] (+ pos_table[position_t, :]), in float32.  A token is tokens[t], or, where
+// src is given and src[t] >= 0, ids[src[t]]: an id that an earlier step's sampler left on the device
+// (clamped into the table: a sampler's id is always in range; nothing else may reach the table).  Rows
+// whose width is a multiple of 8 are read 16 bytes a thread.
 template <typename T>
-__global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
-                             const T* __restrict__ table, const T* __restrict__ pos_table, float* __restrict__ x,
-                             int d) {
+__global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ src, const int* ids, int n_ids,
+                             int vocab, const int* __restrict__ positions, const T* __restrict__ table,
+                             const T* __restrict__ pos_table, float* __restrict__ x, int d) {
   EMBER_MARK_START(kEmbed);
   const int t = blockIdx.x;
-  const T* row = table + (size_t)tokens[t] * d;
+  int tok = tokens[t];
+  if (src) {
+    const int r = src[t];
+    if (r >= 0 && r < n_ids) {
+      const int v = __ldcg(ids + r);
+      tok = (v >= 0 && v < vocab) ? v : 0;
+    }
+  }
+  const T* row = table + (size_t)tok * d;
   const T* prow = pos_table ? pos_table + (size_t)positions[t] * d : nullptr;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float v = to_float(row[i]);
-    if (prow) v += to_float(prow[i]);
-    x[(size_t)t * d + i] = v;
+  float* out = x + (size_t)t * d;
+  constexpr int kVec = 16 / (int)sizeof(T);  // values in 16 bytes
+  if (d % kVec == 0) {
+    for (int i = threadIdx.x * kVec; i < d; i += blockDim.x * kVec) {
+      const uint4 a = *reinterpret_cast<const uint4*>(row + i);
+      uint4 b = make_uint4(0, 0, 0, 0);
+      if (prow) b = *reinterpret_cast<const uint4*>(prow + i);
+      const T* av = reinterpret_cast<const T*>(&a);
+      const T* bv = reinterpret_cast<const T*>(&b);
+      float v[kVec];
+#pragma unroll
+      for (int j = 0; j < kVec; ++j) v[j] = prow ? to_float(av[j]) + to_float(bv[j]) : to_float(av[j]);
+#pragma unroll
+      for (int j = 0; j < kVec; j += 4) *reinterpret_cast<float4*>(out + i + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      float v = to_float(row[i]);
+      if (prow) v += to_float(prow[i]);
+      out[i] = v;
+    }
   }
   EMBER_MARK(kEmbed, kEnd);
 }
 
+// src, ids: both null, or the rows of `ids` (n_ids of them) that the tokens come from (see above).
 EMBER_API int ember_embed(const int* tokens, const int* positions, const void* table, const void* pos_table, float* x,
-                          int T, int d, int dtype, cudaStream_t stream) {
+                          int T, int d, int dtype, const int* src, const int* ids, int n_ids, int vocab,
+                          cudaStream_t stream) {
   EMBER_CHECK(T > 0 && d > 0, "embed: T = %d, width = %d", T, d);
+  EMBER_CHECK((src == nullptr) == (ids == nullptr) && (!ids || (n_ids > 0 && vocab > 0)),
+              "embed: tokens from the device need their rows and the ids (%d of them), and the vocabulary (%d)", n_ids, vocab);
   if (dtype == EMBER_F32)
-    embed_kernel<float><<<T, 128, 0, stream>>>(tokens, positions, (const float*)table, (const float*)pos_table, x, d);
+    embed_kernel<float><<<T, 128, 0, stream>>>(tokens, src, ids, n_ids, vocab, positions, (const float*)table,
+                                               (const float*)pos_table, x, d);
   else if (dtype == EMBER_BF16)
-    embed_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(tokens, positions, (const __nv_bfloat16*)table,
+    embed_kernel<__nv_bfloat16><<<T, 128, 0, stream>>>(tokens, src, ids, n_ids, vocab, positions, (const __nv_bfloat16*)table,
                                                        (const __nv_bfloat16*)pos_table, x, d);
   else
     return ember_fail("embed: element type %d", dtype);

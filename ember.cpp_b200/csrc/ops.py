@@ -24,7 +24,7 @@ _LT_WORKSPACE = 32 << 20
 _c_int, _c_float, _c_void, _c_size, _c_u64 = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint64
 
 _SIGNATURES = {
-    "ember_embed": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
+    "ember_embed": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ember_layernorm": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_void],
     "ember_take_tokens": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
@@ -55,7 +55,7 @@ _SIGNATURES = {
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_attention_prefill_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
-    "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_void],
+    "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_u64, _c_void],
 }
 
 
@@ -253,14 +253,22 @@ class CudaOps:
         return copy
 
     # ------------------------------------------------------------------ rows
-    def embed(self, tokens, positions, table, pos_table):
+    def embed(self, tokens, positions, table, pos_table, token_src=None, ids=None):
+        """Rows of the token table (plus rows of the position table) in float32.  With `token_src` and `ids`
+        (int32, on the device) token t is ids[token_src[t]] where token_src[t] >= 0: an id that an earlier
+        step's sampler left there."""
         T, d = tokens.shape[0], table.shape[1]
         if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != d):
             raise KernelError("embed: the position table must have the token table's type and width")
+        if (token_src is None) != (ids is None):
+            raise KernelError("embed: tokens from the device need both their rows and the ids")
+        if ids is not None and (ids.dtype != torch.int32 or not ids.is_cuda or not ids.is_contiguous()):
+            raise KernelError("embed: sampled ids are a contiguous int32 CUDA tensor")
         self._expected = self._normed = None
         x = torch.empty((T, d), dtype=torch.float32, device=table.device)
         self._call("ember_embed", tokens.data_ptr(), positions.data_ptr(), self._dense(table, "token table").data_ptr(),
-                   self._ptr(pos_table), x.data_ptr(), T, d, _code(table.dtype))
+                   self._ptr(pos_table), x.data_ptr(), T, d, _code(table.dtype), self._ptr(token_src), self._ptr(ids),
+                   0 if ids is None else ids.numel(), table.shape[0])
         return x
 
     def expect_norm(self, w, b, eps, out_dtype) -> None:
@@ -589,13 +597,20 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ sampling
-    def sample(self, logits, temperature, top_k, top_p, seed, streams, counters):
+    sample_takes_base = True
+
+    def sample(self, logits, temperature, top_k, top_p, seed, streams, counters, counter_base: int = 0, out=None):
         """One token per row of float32 logits.  `streams` and `counters` (int32, one per row) key
-        the uniform number of each row's draw."""
+        the uniform number of each row's draw; `counter_base` is added to every row's counter.  `out`:
+        where the ids go (int32, one per row; default: a new tensor)."""
         rows, V = logits.shape
         if logits.dtype != torch.float32:
             raise KernelError("sample: logits are float32")
-        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        if out is None:
+            out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        elif out.dtype != torch.int32 or out.shape != (rows,) or not out.is_contiguous() or out.device != logits.device:
+            raise KernelError("sample: the ids go into a contiguous int32 tensor with one entry per row, on the logits' device")
         self._call("ember_sample", self._dense(logits, "logits").data_ptr(), out.data_ptr(), rows, V, float(temperature),
-                   int(top_k), float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF, streams.data_ptr(), counters.data_ptr())
+                   int(top_k), float(top_p), int(seed) & 0xFFFFFFFFFFFFFFFF, streams.data_ptr(), counters.data_ptr(),
+                   int(counter_base))
         return out

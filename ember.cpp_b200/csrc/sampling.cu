@@ -338,7 +338,7 @@ __device__ bool sample_by_thread_maxima(const float* s_p, int V, float my_max, i
 template <bool CACHED>
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, float temperature, int top_k,
-              float top_p, u64 seed, const int* __restrict__ streams, const int* __restrict__ counters) {
+              float top_p, u64 seed, const int* __restrict__ streams, const int* __restrict__ counters, u64 counter_base) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   u64* s_mass = reinterpret_cast<u64*>(smem_raw);                 // [kBins]; also the segment sums at the end
   unsigned* s_cnt = reinterpret_cast<unsigned*>(s_mass + kBins);  // [kBins]
@@ -448,7 +448,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   if (CACHED) row.cached = s_p;
 
   if (top_k < V && top_k <= kSmallK) {
-    const u64 u = splitmix_uniform24(seed, (u64)streams[blockIdx.x], (u64)counters[blockIdx.x]);
+    const u64 u = splitmix_uniform24(seed, (u64)streams[blockIdx.x], (u64)counters[blockIdx.x] + counter_base);
     const u64 need_p = (u64)ceil((double)fmaxf(top_p, 0.f) * (double)z);
     if (CACHED && sample_by_thread_maxima(s_p, V, my_max, top_k, top_p < 1.0f, need_p, u, best_i, out,
                                           reinterpret_cast<float*>(s_cnt), s_mass, s_u64, &s_hit, &s_n))
@@ -483,7 +483,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
     if (t < (int)threadIdx.x) before += v;
     total += v;
   }
-  const u64 u24 = splitmix_uniform24(seed, (u64)streams[blockIdx.x], (u64)counters[blockIdx.x]);
+  const u64 u24 = splitmix_uniform24(seed, (u64)streams[blockIdx.x], (u64)counters[blockIdx.x] + counter_base);
   // target = floor(total * u24 / 2^24), exact in 128 bits
   const u64 target = (__umul64hi(total, u24) << 40) | ((total * u24) >> 24);
   if (total > 0 && before <= target && target < before + mine) {
@@ -506,7 +506,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
 }  // namespace
 
 EMBER_API int ember_sample(const float* logits, int* out, int rows, int V, float temperature, int top_k, float top_p,
-                           unsigned long long seed, const int* streams, const int* counters, cudaStream_t stream) {
+                           unsigned long long seed, const int* streams, const int* counters,
+                           unsigned long long counter_base, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && V > 0, "sample: rows = %d, vocabulary = %d", rows, V);
   EMBER_CHECK(temperature >= 0.f, "sample: temperature %g is negative", (double)temperature);
   const size_t bins = kBins * (sizeof(u64) + sizeof(unsigned));
@@ -520,10 +521,10 @@ EMBER_API int ember_sample(const float* logits, int* out, int rows, int V, float
       configured = true;
     }
     sample_kernel<true><<<rows, kThreads, cached, stream>>>(logits, out, V, temperature, top_k, top_p, seed, streams,
-                                                            counters);
+                                                            counters, counter_base);
   } else {
     sample_kernel<false><<<rows, kThreads, bins, stream>>>(logits, out, V, temperature, top_k, top_p, seed, streams,
-                                                           counters);
+                                                           counters, counter_base);
   }
   EMBER_LAUNCH_OK("sample");
   return 0;

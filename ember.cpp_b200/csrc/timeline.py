@@ -95,17 +95,15 @@ def main() -> int:
     slots = [engine.open() for _ in range(args.batch)]
     prompts = [rng.integers(0, cfg.vocab_size, args.context).tolist() for _ in range(args.batch)]
     logits = engine.step([(s, p, [args.context - 1]) for s, p in zip(slots, prompts)])
-    streams = torch.arange(args.batch, dtype=torch.int32, device="cuda")
-    counters = torch.zeros(args.batch, dtype=torch.int32, device="cuda")
-    ids = sampler.sample(logits, params, streams, counters)
+    streams = list(range(args.batch))
+    ids = sampler.sample(logits, params, streams, [0] * args.batch, out=engine.sample_target(args.batch))
     rows = list(range(args.batch))
     for i in range(12):
         if i == 11:                      # the last step alone
             torch.cuda.synchronize()
             engine.ops.timeline()
         logits = engine.step([(s, [0], [0]) for s in slots], borrow=True, device_tokens=(ids, rows))
-        counters += 1
-        ids = sampler.sample(logits, params, streams, counters)
+        ids = sampler.sample(logits, params, streams, [i + 1] * args.batch, out=engine.sample_target(args.batch))
     torch.cuda.synchronize()
     print(report(launches_of(engine.ops.timeline()), args.blocks))
     return 0

@@ -95,6 +95,11 @@ class Engine:
         self._device_buffer = None
         self._staging = _Staging(runtime.device)
         self._graphs: dict[int, "_DecodeGraph"] = {}
+        # Where a sampler leaves a step's ids for the next step (`sample_target`): two halves in turn, at an
+        # address that a captured step can name.  The step that reads one half is queued before the sampler
+        # that writes the other, and the host has read a half's ids before the half is written again.
+        self._ids_ring = None
+        self._ids_turn = 0
         # a part whose forward does work on the host (reads a value back, loops over tokens in
         # Python) cannot be replayed from a captured graph; it says so with graph_safe = False
         # (per-launch timing needs an event between launches, which a captured graph does not carry)
@@ -240,6 +245,39 @@ class Engine:
                 torch.cuda.nvtx.range_pop()
         return self.model.forward(ctx)
 
+    def sample_target(self, rows: int):
+        """An int32 tensor of `rows` entries for a sampler to write a step's ids into, from which the next
+        step can take its tokens without a launch of its own (`step(device_tokens=(that tensor, rows))`)."""
+        ring, cap = self._ring(), max(self.cache.n_slots, 1)
+        if rows > cap:
+            raise StepError(f"{rows} rows of sampled ids, but the cache has {cap} slots")
+        self._ids_turn ^= 1
+        return ring[self._ids_turn * cap: self._ids_turn * cap + rows]
+
+    def _ring(self):
+        if self._ids_ring is None:
+            self._ids_ring = torch.zeros(2 * max(self.cache.n_slots, 1), dtype=torch.int32, device=self.runtime.device)
+        return self._ids_ring
+
+    def _ring_rows(self, ids, rows):
+        """`rows` of `ids` as rows of the ring that captured steps read: `ids` is a piece of the ring (what
+        `sample_target` gave out), or is copied into the ring's next piece first."""
+        ring = self._ring()
+        ring_ptr = ring.data_ptr()
+        at = (ids.data_ptr() - ring_ptr) // 4
+        if not (ids.dtype == torch.int32 and ids.is_contiguous() and 0 <= at and at + ids.numel() <= ring.numel()
+                and (ids.data_ptr() - ring_ptr) % 4 == 0):
+            if ids.dtype != torch.int32 or ids.dim() != 1 or ids.device != ring.device:
+                raise StepError("tokens taken from the device: rows of a one-dimensional int32 tensor of sampled ids")
+            piece = self.sample_target(min(ids.shape[0], max(self.cache.n_slots, 1)))
+            if ids.shape[0] > piece.shape[0]:
+                raise StepError(f"tokens taken from the device: {ids.shape[0]} sampled ids, but the cache has {piece.shape[0]} slots")
+            piece.copy_(ids)
+            at = (piece.data_ptr() - ring_ptr) // 4
+            if any(not 0 <= int(r) < ids.shape[0] for r in rows):
+                raise StepError("tokens taken from the device: a row outside the sampled ids")
+        return ring, [at + int(r) for r in rows]
+
     # ------------------------------------------------------------------ one token each, as a replayed graph
     def _length_bucket(self, pages: int) -> int:
         """The pages of the longest sequence, rounded up to 4, 6, 8, 12, 16, 24, ... (or to all the cache
@@ -278,13 +316,14 @@ class Engine:
         bucket = 1
         while bucket < n_real:
             bucket *= 2
+        if device_tokens is not None:     # the captured step's embedding takes them from the ring itself
+            device_tokens = self._ring_rows(*device_tokens)
         host, shape = self.prepare(entries, pad_to=bucket, want_all=True, device_tokens=device_tokens)
-        ids = None if device_tokens is None else device_tokens[0]
         pages = self._length_bucket(-(-host.max_end // 64))
         g = self._graphs.get((bucket, pages))
         if g is None:
             g = self._graphs[(bucket, pages)] = _DecodeGraph(self, host, pages)
-        g.replay(self, host, ids)
+        g.replay(self, host)
         self._account(host, shape)
         rows = [i for i, (_, _, want) in enumerate(entries) for _ in want]
         if not rows:
@@ -329,6 +368,8 @@ class _DecodeGraph:
         # launches are sized for sequences of up to `pages` pages, lengths come from the buffer
         sized = dataclasses.replace(host, max_end=pages * 64)
         self.plan = StepPlan(sized, self.buffer)
+        if dev.type == "cuda":            # tokens that an earlier step's sampler left in the ring are taken by the embedding
+            self.plan.device_ids = engine._ring()
         engine._stage(self.staging, host, self.buffer)
         engine.clear_tails(self.plan)
         if dev.type != "cuda":
@@ -343,12 +384,10 @@ class _DecodeGraph:
             self.logits = engine.run(self.plan)
         self.launches = engine.ops.launches - before
 
-    def replay(self, engine: Engine, host, ids=None) -> None:
+    def replay(self, engine: Engine, host) -> None:
         if host.packed.shape[0] != self.size:
             raise StepError("the step's description changed size under a captured graph")
         engine._stage(self.staging, host, self.buffer)
-        if ids is not None:           # outside the graph: the ids' address changes from step to step
-            engine.ops.take_tokens(self.plan.tokens, self.plan.token_src, ids, engine.vocab_size)
         if host.has_tails:            # outside the graph as well: a step in 64 has any
             self.plan.has_tails = True
             engine.clear_tails(self.plan)

@@ -125,8 +125,10 @@ class Generator:
 
         def launch(active, entries, device_tokens):
             logits = eng.step(entries, borrow=device_tokens is not None, device_tokens=device_tokens)
+            target = getattr(eng, "sample_target", None)   # where the next step can take the ids from by itself
             ids = self.sampler.sample(logits, params.sampling, [first_stream + i for i in active],
-                                      [len(generated[i]) + (device_tokens is not None) for i in active])
+                                      [len(generated[i]) + (device_tokens is not None) for i in active],
+                                      out=None if target is None or not logits.is_cuda else target(len(active)))
             # (requests, their ids on the device and on the way to the host, positions in the cache after the step)
             return active, ids, self.sampler.fetch(ids), [eng.length(slots[i]) for i in active]
 

@@ -167,3 +167,4 @@ class StepPlan:
         self.pages = [view(p, lay.n * lay.max_blocks).view(lay.n, lay.max_blocks) for p in lay.pages]
         self.tails = [view(p, 2 * lay.n).view(lay.n, 2) for p in lay.tails]
         self.has_tails = host.has_tails
+        self.device_ids = None   # set by the engine: the sampled ids that `token_src` indexes (a replayed step)

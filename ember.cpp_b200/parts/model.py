@@ -82,7 +82,12 @@ class DecoderModel:
         """Runs the tokens of `ctx.plan` through every entry of the schedule and returns float32
         logits [wanted rows, vocab] (None if no row is wanted)."""
         plan, ops = ctx.plan, ctx.ops
-        x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table())
+        ids = getattr(plan, "device_ids", None)   # sampled ids on the device that this step's tokens are taken from
+        if ids is not None:
+            x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table(),
+                          token_src=plan.token_src, ids=ids)
+        else:
+            x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table())
         if self.spec.embedding_scale != 1.0:
             x = ops.scale_cap(x, scale=self.spec.embedding_scale)
         for i, app in enumerate(ctx.apps):

@@ -85,6 +85,7 @@ class Sampler:
         self._turn = 0
         self._hpinned = []                  # pinned staging for the per-row stream and counter numbers
         self._hturn = 0
+        self._kept = None                   # (stream numbers, their device tensor, zeros of the same length)
 
     def fetch(self, ids: torch.Tensor) -> IdsOnTheWay:
         """Starts copying sampled ids to the host without stopping the stream they were drawn on."""
@@ -100,12 +101,26 @@ class Sampler:
             self._pinned[self._turn] = torch.empty(n, dtype=torch.int32, pin_memory=True)
         return IdsOnTheWay(ids, self._stream, self._pinned[self._turn])
 
-    def sample(self, logits: torch.Tensor, params: SamplingParams, streams, counters) -> torch.Tensor:
+    def sample(self, logits: torch.Tensor, params: SamplingParams, streams, counters, out=None) -> torch.Tensor:
         """logits: float32 [rows, vocab] on the device.  streams, counters: one int per row (lists
-        or int32 tensors).  Returns int32 [rows] on the device."""
+        or int32 tensors).  Returns int32 [rows] on the device (`out`, if one is given)."""
+        more = {} if out is None else {"out": out}
+        base = 0
         if not torch.is_tensor(streams) or not torch.is_tensor(counters):
-            streams, counters = self._to_device(list(streams), list(counters), logits.device)
-        return self.ops.sample(logits, params.temperature, params.top_k, params.top_p, params.seed, streams, counters)
+            streams, counters = list(streams), list(counters)
+            if counters and min(counters) == max(counters) and hasattr(self.ops, "sample_takes_base"):
+                # the sequences of a batch start together, so one number counts for all rows: it goes as an
+                # argument, and the stream numbers stay on the device from step to step (no copy a step)
+                key = tuple(streams)
+                if self._kept is None or self._kept[0] != key:
+                    on_device, zeros = self._to_device(streams, [0] * len(streams), logits.device)
+                    self._kept = (key, on_device, zeros)
+                base, streams, counters = counters[0], self._kept[1], self._kept[2]
+            else:
+                streams, counters = self._to_device(streams, counters, logits.device)
+        if base:
+            more["counter_base"] = base
+        return self.ops.sample(logits, params.temperature, params.top_k, params.top_p, params.seed, streams, counters, **more)
 
     def _to_device(self, streams: list[int], counters: list[int], dev):
         """Two lists of ints -> two int32 device tensors with one copy from pinned memory.  (A copy
