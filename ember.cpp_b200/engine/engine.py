@@ -263,20 +263,18 @@ class Engine:
         """`rows` of `ids` as rows of the ring that captured steps read: `ids` is a piece of the ring (what
         `sample_target` gave out), or is copied into the ring's next piece first."""
         ring = self._ring()
-        ring_ptr = ring.data_ptr()
-        at = (ids.data_ptr() - ring_ptr) // 4
-        if not (ids.dtype == torch.int32 and ids.is_contiguous() and 0 <= at and at + ids.numel() <= ring.numel()
-                and (ids.data_ptr() - ring_ptr) % 4 == 0):
-            if ids.dtype != torch.int32 or ids.dim() != 1 or ids.device != ring.device:
-                raise StepError("tokens taken from the device: rows of a one-dimensional int32 tensor of sampled ids")
-            piece = self.sample_target(min(ids.shape[0], max(self.cache.n_slots, 1)))
-            if ids.shape[0] > piece.shape[0]:
-                raise StepError(f"tokens taken from the device: {ids.shape[0]} sampled ids, but the cache has {piece.shape[0]} slots")
+        if (not torch.is_tensor(ids) or ids.dtype != torch.int32 or ids.dim() != 1 or ids.device != ring.device
+                or not ids.is_contiguous() or any(not 0 <= int(r) < ids.shape[0] for r in rows)):
+            raise StepError("tokens taken from the device: rows of a one-dimensional int32 tensor of sampled ids")
+        off = ids.data_ptr() - ring.data_ptr()
+        if not (off >= 0 and off % 4 == 0 and off // 4 + ids.shape[0] <= ring.numel()):
+            if ids.shape[0] > max(self.cache.n_slots, 1):
+                raise StepError(f"tokens taken from the device: {ids.shape[0]} sampled ids, but the cache has "
+                                f"{self.cache.n_slots} slots")
+            piece = self.sample_target(ids.shape[0])
             piece.copy_(ids)
-            at = (piece.data_ptr() - ring_ptr) // 4
-            if any(not 0 <= int(r) < ids.shape[0] for r in rows):
-                raise StepError("tokens taken from the device: a row outside the sampled ids")
-        return ring, [at + int(r) for r in rows]
+            off = piece.data_ptr() - ring.data_ptr()
+        return ring, [off // 4 + int(r) for r in rows]
 
     # ------------------------------------------------------------------ one token each, as a replayed graph
     def _length_bucket(self, pages: int) -> int:

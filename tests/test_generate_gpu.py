@@ -445,6 +445,46 @@ def test_running_a_step_ahead_changes_no_token_on_the_gpu(tiny_folders, plains, 
     assert out[0] == out[1]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_replayed_step_takes_its_tokens_from_sampled_ids_wherever_they_lie(engines, dtype):
+    """A one-token step whose tokens are ids on the device: given in the tensor that `sample_target` handed out
+    (the captured step's embedding reads them there) or in any other tensor (copied there first), with rows in
+    any order, the logits are those of the same tokens given by the host."""
+    eng = engines[("tiny_a", dtype)]
+    V = eng.vocab_size
+    a, b, c = random_ids(900, V, 9), random_ids(901, V, 70), random_ids(902, V, 3)
+    want = None
+    for way in ("host", "ring", "elsewhere", "ring again"):
+        slots = [eng.open() for _ in range(3)]
+        eng.step([(s, p[:-1], []) for s, p in zip(slots, (a, b, c))])
+        last = [a[-1], b[-1], c[-1]]
+        if way == "host":
+            out = eng.step([(s, [t], [0]) for s, t in zip(slots, last)])
+        else:
+            given = torch.tensor([7, last[2], last[0], 5, last[1]], dtype=torch.int32).cuda()   # rows 2, 4, 1 are wanted
+            if way == "elsewhere":
+                ids = given
+            else:
+                ids = eng.sample_target(5)
+                ids.copy_(given)
+            out = eng.step([(s, [0], [0]) for s in slots], device_tokens=(ids, [2, 4, 1]))
+        out = out.clone()
+        for s in slots:
+            eng.close(s)
+        if want is None:
+            want = out
+        else:
+            assert torch.equal(out, want), way
+    s0 = eng.open()
+    with pytest.raises(E.StepError, match="taken from the device"):
+        eng.step([(s0, [1], [])], device_tokens=(torch.zeros(2, dtype=torch.int32).cuda(), [2]))
+    with pytest.raises(E.StepError, match="taken from the device"):
+        eng.step([(s0, [1], [])], device_tokens=(torch.zeros(2, dtype=torch.int64).cuda(), [0]))
+    assert eng.length(s0) == 0
+    eng.close(s0)
+    eng.ops.check()
+
+
 def test_temperature_generation_equals_plain(tiny_folders, plains):
     plain = plains["tiny_b"]
     prompts = [random_ids(600 + i, plain.vocab, n) for i, n in enumerate((1, 9, 40, 63))]

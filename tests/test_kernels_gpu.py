@@ -48,6 +48,24 @@ def test_embed(ops, dtype, d):
     assert torch.equal(ops.embed(tokens, positions, table, None), table[tokens.long()].float())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("d", [48, 1600, 100])
+def test_embed_takes_tokens_that_a_sampler_left_on_the_device(ops, dtype, d):
+    """With rows of sampled ids given, token t is ids[src[t]] where src[t] >= 0 and tokens[t] elsewhere (also where
+    the row does not exist); an id outside the table reads row 0, never beyond the table."""
+    table, pos = gen((301, d), 8, DT[dtype]), gen((77, d), 9, DT[dtype])
+    tokens = torch.tensor([300, 0, 17, 17, 255], dtype=torch.int32).cuda()
+    positions = torch.tensor([76, 0, 5, 6, 7], dtype=torch.int32).cuda()
+    src = torch.tensor([2, -1, 0, 9, 3], dtype=torch.int32).cuda()
+    ids = torch.tensor([40, 41, 42, 1000], dtype=torch.int32).cuda()
+    x = ops.embed(tokens, positions, table, pos, token_src=src, ids=ids)
+    taken = torch.tensor([42, 0, 40, 17, 0]).cuda()
+    assert torch.equal(x, table[taken].float() + pos[positions.long()].float())
+    assert tokens.tolist() == [300, 0, 17, 17, 255]                      # the step's own description is left as it is
+    with pytest.raises(Exception, match="both"):
+        ops.embed(tokens, positions, table, pos, token_src=src)
+
+
 @pytest.mark.parametrize("out", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rows, d, eps", [(1, 64, 1e-5), (7, 1600, 1e-6), (130, 100, 1e-3), (3, 24, 1e-5)])
 def test_layernorm(ops, out, rows, d, eps):
