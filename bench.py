@@ -389,7 +389,7 @@ def main() -> int:
     n_seq, plen = PREFILL
     plen = min(plen, ctx)
     T = n_seq * plen
-    times = []
+    times, host_times = [], []
     for rep in range(2 + 5):
         slots = [engine.open() for _ in range(n_seq)]
         prompts = [rng.integers(0, V, plen).tolist() for _ in range(n_seq)]
@@ -399,9 +399,11 @@ def main() -> int:
         a.record()
         engine.step([(s, p, [plen - 1]) for s, p in zip(slots, prompts)])
         b.record()
+        queued = time.time() - w0          # what the host took to queue the step's launches
         torch.cuda.synchronize()
         if rep >= 2:
             times.append(a.elapsed_time(b))
+            host_times.append(queued * 1e3)
             windows.append((w0, time.time()))
         for s in slots:
             engine.close(s)
@@ -412,7 +414,8 @@ def main() -> int:
 
     if args.only == "prefill":
         clocks.stop()
-        line = {"prefill": prefill, "n_layer": L, "times_ms": [round(t, 3) for t in times]}
+        line = {"prefill": prefill, "n_layer": L, "times_ms": [round(t, 3) for t in times],
+                "host_queue_ms": [round(t, 3) for t in host_times]}
         if engine.ops.op_timing:     # EMBER_OP_TIMING=1: the time per kernel entry point over the repeats (launches do not overlap then)
             line["op_ms_per_prefill"] = {k: round(ms / len(times + [0, 0]), 4) for k, (n, ms) in sorted(engine.ops.op_times().items())}
         print(json.dumps(line))

@@ -80,6 +80,15 @@ class LazyNorm:
         return self.ops.layernorm(self.x, self.w, self.b, self.eps, self.dtype)
 
 
+def _current_stream() -> int:
+    """The handle of torch's current stream on the current device.  Asked for at every launch, so by the shortest
+    way torch has (a launch costs the host a few microseconds in all, and a prompt's step is some 500 launches)."""
+    raw = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+    if raw is None:
+        return torch.cuda.current_stream().cuda_stream
+    return raw(torch.cuda.current_device())
+
+
 def _code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return _F32
@@ -191,7 +200,7 @@ class CudaOps:
         if timed:
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record()
-        rc = getattr(self.lib, name)(*args, torch.cuda.current_stream().cuda_stream)
+        rc = getattr(self.lib, name)(*args, _current_stream())
         if timed:
             end.record()
             self._timed.append((name, begin, end))

@@ -12,6 +12,8 @@ options given in code), so a measurement can flip a switch without touching the 
   max_tokens       EMBER_MAX_TOKENS       positions the cache holds over all live sequences, each rounded up to 64
   max_slots        EMBER_MAX_SLOTS        most live sequences (default: as many as the cache has pages)
   cuda_graphs      EMBER_CUDA_GRAPHS      one-token steps replay a captured graph (0: launch by launch)
+  prompt_graphs    EMBER_PROMPT_GRAPHS    steps that bring prompts replay a captured graph from the second time their shape
+                                          comes; this many shapes are kept (0: never)
   deterministic    EMBER_DETERMINISTIC    no choice is made by timing: the library products take the heuristic's first
                                           algorithm, so two processes give the same bits (it implies lt_tune = False)
   gemm             EMBER_GEMM             products of more than 64 rows: "lt" cuBLASLt (as ember.cpp's go to cuBLAS), "tc" this
@@ -61,6 +63,7 @@ class RuntimeOptions:
     max_tokens: int = 4096
     max_slots: int | None = None
     cuda_graphs: bool = True
+    prompt_graphs: int = 4
     deterministic: bool = False
     gemm: str = "lt"
     lt_tune: bool = True
@@ -86,6 +89,8 @@ class RuntimeOptions:
             raise OptionError(f"attention = {self.attention!r}: 'tc' (tcgen05) or 'mma' (mma.sync)")
         if self.max_tokens <= 0 or (self.max_slots is not None and self.max_slots <= 0):
             raise OptionError(f"max_tokens = {self.max_tokens}, max_slots = {self.max_slots}: both positive")
+        if self.prompt_graphs < 0:
+            raise OptionError(f"prompt_graphs = {self.prompt_graphs}: a number of shapes, or 0 for never")
         if self.deterministic and self.lt_tune:
             object.__setattr__(self, "lt_tune", False)      # a choice by timing is not reproducible
 
@@ -105,7 +110,7 @@ class RuntimeOptions:
                 continue
             if f.type in ("bool", bool):
                 values[f.name] = _flag(text, name)
-            elif f.name in ("max_tokens", "max_slots"):
+            elif f.name in ("max_tokens", "max_slots", "prompt_graphs"):
                 try:
                     values[f.name] = int(text)
                 except ValueError:

@@ -485,6 +485,43 @@ def test_a_replayed_step_takes_its_tokens_from_sampled_ids_wherever_they_lie(eng
     eng.ops.check()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_prompt_step_of_a_known_shape_replays_a_graph_and_changes_nothing(tiny_folders, dtype):
+    """A step of prompts whose shape has come before is captured and replayed; the logits are, bit for bit, those
+    of the same step launched from the host, for other tokens, other slots and other wanted rows of the same
+    count; only the last few shapes are kept."""
+    plain_way = Engine.from_folder(tiny_folders["tiny_b"], dtype=dtype, max_tokens=2048,
+                                   options=E.RuntimeOptions(prompt_graphs=0))
+    eng = Engine.from_folder(tiny_folders["tiny_b"], dtype=dtype, max_tokens=2048, options=E.RuntimeOptions(prompt_graphs=2))
+    V = eng.vocab_size
+
+    def both(lengths, wants, seed, hold=0):
+        got = []
+        for e in (plain_way, eng):
+            held = [e.open() for _ in range(hold)]            # other slots, other pages
+            slots = [e.open() for _ in lengths]
+            out = e.step([(s, random_ids(seed + i, V, n), w) for i, (s, n, w) in enumerate(zip(slots, lengths, wants))])
+            got.append(None if out is None else out.clone())
+            for s in slots + held:
+                e.close(s)
+        assert (got[0] is None and got[1] is None) or torch.equal(got[0], got[1])
+
+    both([70, 9, 33], [[69], [0, 8], [32]], 1000)
+    assert len(eng._prompt_graphs) == 0                       # a new shape: launched from the host
+    both([70, 9, 33], [[69], [0, 8], [32]], 1010)
+    assert len(eng._prompt_graphs) == 1                       # the second time: captured
+    both([70, 9, 33], [[1], [2, 3], [4]], 1020, hold=2)
+    both([9, 70, 33], [[8], [0, 69], [32]], 1030)             # same counts, same longest: the same shape
+    assert len(eng._prompt_graphs) == 1
+    for lengths in ([5, 5], [64], [5, 5], [64], [3], [3]):
+        both(lengths, [[n - 1] for n in lengths], 1040)
+    assert len(eng._prompt_graphs) == 2                       # three shapes were captured in all, two are kept
+    both([12], [[]], 1050)
+    both([12], [[]], 1051)                                    # nothing wanted: no logits either way
+    eng.ops.check()
+    assert eng.cache.slots.held == 0 and plain_way.cache.slots.held == 0
+
+
 def test_temperature_generation_equals_plain(tiny_folders, plains):
     plain = plains["tiny_b"]
     prompts = [random_ids(600 + i, plain.vocab, n) for i, n in enumerate((1, 9, 40, 63))]

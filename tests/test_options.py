@@ -12,7 +12,7 @@ def test_defaults_and_variable_names():
     assert o.dtype == "bfloat16" and o.cuda_graphs and o.gemm == "lt" and o.lt_tune and not o.deterministic
     assert RuntimeOptions.variable("decode_mma") == "EMBER_DECODE_MMA"
     assert {f.name for f in dataclasses.fields(RuntimeOptions)} >= {
-        "dtype", "max_tokens", "max_slots", "cuda_graphs", "deterministic", "gemm", "lt_tune", "linear_stream", "attention",
+        "dtype", "max_tokens", "max_slots", "cuda_graphs", "prompt_graphs", "deterministic", "gemm", "lt_tune", "linear_stream", "attention",
         "decode_mma", "decode_cluster", "decode_bulk", "pdl", "fuse_norm", "tail_norm", "cache_ahead", "warm", "op_timing", "nvtx"}
 
 
