@@ -7,6 +7,10 @@
 // and draws from it by inverse CDF in index order with a counter-based uniform (ember.cpp uses
 // std::mt19937, whose stream cannot be shared with other code; the distribution is the same).
 //
+// The kernel's code runs once per row, straight through, and a step of a large model has pushed it out of every
+// cache by then: what a row costs is, to a good part, fetching the code it runs.  So the ways that a row seldom
+// takes (the radix selections) are functions of their own, out of line, and the usual way is short.
+//
 // One block per row; nothing is sorted.  Each candidate has the 64-bit key (bits of p, index);
 // the k-th largest key and the key at which the running mass reaches top_p are found by radix
 // selection over counts and over masses held as integers (p * 2^40, so that sums do not depend on
@@ -81,7 +85,7 @@ struct Pick {
 // Walks the buckets from the highest down and finds the first non-empty one at which the running
 // weight (counts, or masses) reaches `need`.  If none does, the lowest non-empty bucket with
 // `before` = need (so that the caller's remaining need becomes 0: everything is kept).
-__device__ Pick find_bucket(const unsigned* cnt, const u64* mass, bool by_mass, u64 need, u64* scratch, int* s_hit,
+__device__ __noinline__ Pick find_bucket(const unsigned* cnt, const u64* mass, bool by_mass, u64 need, u64* scratch, int* s_hit,
                             u64* s_before) {
   constexpr int kPer = kBins / kThreads;  // 4 buckets per thread, in descending order
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -151,7 +155,7 @@ __device__ Pick find_bucket(const unsigned* cnt, const u64* mass, bool by_mass, 
 // `need`-th largest candidate.  by_mass = true: the key at which the running mass, in descending
 // key order, first reaches `need`.  Returns a threshold: the candidates to keep are those with
 // key >= threshold.
-__device__ u64 radix_select(const Row& row, int V, bool by_mass, u64 need, unsigned* cnt, u64* mass, u64* scratch,
+__device__ __noinline__ u64 radix_select(const Row& row, int V, bool by_mass, u64 need, unsigned* cnt, u64* mass, u64* scratch,
                             int* s_hit, u64* s_before) {
   const int shifts[6] = {53, 42, 32, 21, 10, 0};
   const int widths[6] = {11, 11, 10, 11, 11, 10};
@@ -199,7 +203,7 @@ constexpr int kListCap = 1024;  // entries of that list
 // kListCap masses behind them).  Each one's rank and the mass above it by comparison with all others, the
 // kept set (rank < top_k, and the mass above it short of the top_p target: the same set as the two radix
 // selections give), and the draw in index order.
-__device__ void finish_list(u64* list, int n, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
+__device__ __noinline__ void finish_list(u64* list, int n, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
                             u64* scratch, int* s_hit) {
   u64* kept_mass = list + kListCap;
   constexpr int kPer = kListCap / kThreads;
@@ -259,7 +263,7 @@ __device__ void finish_list(u64* list, int n, int top_k, bool use_p, u64 need_p,
 // index order.  Integer masses make every sum independent of the list's order.  Returns false
 // (having written nothing) when the list would not fit, which takes a bucket of hundreds of
 // candidates with the same leading digits on every level.
-__device__ bool sample_small(const Row& row, int V, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
+__device__ __noinline__ bool sample_small(const Row& row, int V, int top_k, bool use_p, u64 need_p, u64 u24, int fallback, int* out,
                              unsigned* cnt, u64* list, u64* scratch, int* s_hit, u64* s_before, int* s_n) {
   const int shifts[6] = {53, 42, 32, 21, 10, 0};
   const int widths[6] = {11, 11, 10, 11, 11, 10};
@@ -303,29 +307,57 @@ __device__ bool sample_small(const Row& row, int V, int top_k, bool use_p, u64 n
 // The other way to the short list (see the head of the file): the threshold is the top_k-th largest of
 // the threads' own maxima.  lmax: kThreads floats of scratch.  Returns false (nothing written) if more
 // than kListCap entries reach the threshold.
-__device__ bool sample_by_thread_maxima(const float* s_p, int V, float my_max, int top_k, bool use_p, u64 need_p, u64 u24,
+__device__ __noinline__ bool sample_by_thread_maxima(const float* s_p, int V, float my_max, int top_k, bool use_p, u64 need_p, u64 u24,
                                         int fallback, int* out, float* lmax, u64* list, u64* scratch, int* s_hit, int* s_n) {
-  __shared__ float s_thr;
-  lmax[threadIdx.x] = my_max;  // -1 for a thread without entries
-  if (threadIdx.x == 0) {
-    *s_n = 0;
-    s_thr = -1.f;              // fewer threads with entries than top_k: everything is a candidate
-  }
-  __syncthreads();
-  int rank = 0;
-  for (int j = 0; j < kThreads; ++j) {
-    const float o = lmax[j];
-    rank += (o > my_max || (o == my_max && j < (int)threadIdx.x)) ? 1 : 0;
-  }
-  if (rank == top_k - 1 && my_max >= 0.f) s_thr = my_max;
-  __syncthreads();
-  const float thr = s_thr;
-  for (int i = threadIdx.x; i < V; i += kThreads) {
-    const float p = s_p[i];
-    if (p >= thr) {
-      const int at = atomicAdd(s_n, 1);
-      if (at < kListCap) list[at] = key_of(p, i);
+  // The top_k-th largest of the threads' maxima by radix selection over their bits, 8 bits a pass (p >= 0, so the
+  // bits order as the values do; 0 stands for a thread without entries, below every p).
+  __shared__ unsigned s_digit, s_left;
+  unsigned* hist = reinterpret_cast<unsigned*>(lmax);  // 256 counters
+  const unsigned key = my_max >= 0.f ? __float_as_uint(my_max) + 1u : 0u;
+  unsigned prefix = 0, need = (unsigned)top_k;
+  if (threadIdx.x == 0) *s_n = 0;
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    if (threadIdx.x < 256) hist[threadIdx.x] = 0;
+    __syncthreads();
+    if (shift == 24 || (key >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+    __syncthreads();
+    if (threadIdx.x < 32) {  // lane l owns the digits 255 - 8 l down to 248 - 8 l
+      unsigned c[8], mine = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mine += (c[j] = hist[255 - (threadIdx.x * 8 + j)]);
+      unsigned incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned up = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((int)threadIdx.x >= o) incl += up;
+      }
+      unsigned before = incl - mine;  // keys in higher digits than this lane's
+      if (before < need && need <= incl) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (before < need && need <= before + c[j]) {
+            s_digit = 255u - (threadIdx.x * 8 + j);
+            s_left = need - before;
+          }
+          before += c[j];
+        }
+      }
     }
+    __syncthreads();
+    prefix |= s_digit << shift;
+    need = s_left;
+  }
+  const float thr = prefix ? __uint_as_float(prefix - 1u) : -1.f;  // (no entry at all in the top_k-th thread: everything)
+  for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {  // eight reads in flight a thread (a write to the list
+    float p[8];                                             // in between would hold the next read back)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) p[j] = i0 + j * kThreads < V ? s_p[i0 + j * kThreads] : -2.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (p[j] >= thr) {
+        const int at = atomicAdd(s_n, 1);
+        if (at < kListCap) list[at] = key_of(p[j], i0 + j * kThreads);
+      }
   }
   __syncthreads();
   const int n = *s_n;
@@ -353,10 +385,22 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   const float* rowp = logits + (size_t)blockIdx.x * V;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
-  // The row comes into shared memory first when it fits: a 4-byte asynchronous copy for every entry, all
-  // of a thread's in flight together (no registers wait for them), so the row costs one trip to L2.
+  // The row comes into shared memory first when it fits, by asynchronous copies that are all in flight at once (no
+  // registers wait for them): one trip to L2.  16 bytes a copy where the row allows: a row begins anywhere modulo 16
+  // bytes (a vocabulary of 50,257), so its copy begins at the same offset in its buffer, and the few entries before
+  // the first and after the last 16-byte boundary go singly.
   if (CACHED) {
-    for (int i = threadIdx.x; i < V; i += kThreads)
+    const int shift = (int)((reinterpret_cast<size_t>(rowp) >> 2) & 3);  // entries from a 16-byte boundary to the row
+    s_p += shift;
+    const int head = min(V, (4 - shift) & 3), body = (V - head) >> 2;
+    for (int i = threadIdx.x; i < head; i += kThreads)
+      asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(s_p + i)), "l"(rowp + i)
+                   : "memory");
+    for (int q = threadIdx.x; q < body; q += kThreads)
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"((unsigned)__cvta_generic_to_shared(s_p + head + 4 * q)),
+                   "l"(rowp + head + 4 * q)
+                   : "memory");
+    for (int i = head + 4 * body + threadIdx.x; i < V; i += kThreads)
       asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"((unsigned)__cvta_generic_to_shared(s_p + i)), "l"(rowp + i)
                    : "memory");
     asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
@@ -366,12 +410,16 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   float best = -INFINITY;
   int best_i = 0x7fffffff;
   if (CACHED) {
-    for (int i = threadIdx.x; i < V; i += kThreads) {
-      const float l = s_p[i];
-      if (l > best) {  // indices ascend, so the first maximum stays
-        best = l;
-        best_i = i;
-      }
+    for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {  // eight reads in flight a thread
+      float l[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) l[j] = i0 + j * kThreads < V ? s_p[i0 + j * kThreads] : -INFINITY;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (l[j] > best) {  // indices ascend, so the first maximum stays
+          best = l[j];
+          best_i = i0 + j * kThreads;
+        }
     }
   } else {
     for (int i0 = threadIdx.x; i0 < V; i0 += 8 * kThreads) {  // eight loads in flight a thread
@@ -425,6 +473,7 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, fl
   u64 z = 0;
   float my_max = -1.f;  // the largest p among this thread's entries (CACHED)
   if (CACHED) {
+#pragma unroll 4
     for (int i = threadIdx.x; i < V; i += kThreads) {
       const float l = s_p[i];
       const float p = (l == l) ? expf((l - row.mx) * row.inv_t) : 0.f;  // as Row::p
@@ -511,7 +560,7 @@ EMBER_API int ember_sample(const float* logits, int* out, int rows, int V, float
   EMBER_CHECK(rows > 0 && V > 0, "sample: rows = %d, vocabulary = %d", rows, V);
   EMBER_CHECK(temperature >= 0.f, "sample: temperature %g is negative", (double)temperature);
   const size_t bins = kBins * (sizeof(u64) + sizeof(unsigned));
-  const size_t cached = bins + (size_t)V * sizeof(float);
+  const size_t cached = bins + ((size_t)V + 4) * sizeof(float);  // (the row lies up to three entries into its buffer)
   static bool configured = false;
   const size_t limit = 226 * 1024;  // of the 227 KB a block may have; the kernel's static arrays take the rest
   if (cached <= limit) {
