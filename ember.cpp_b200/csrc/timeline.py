@@ -1,12 +1,13 @@
 """Timeline of one decode step, launch by launch.
 
-    EMBER_TIMELINE=1 python -m ember_cpp_b200.csrc.timeline [--layers 4] [--batch 8] [--context 576] [--blocks KERNEL]
+    EMBER_TIMELINE=1 python -m ember_cpp_b200.csrc.timeline [--layers 4] [--batch 8] [--context 576] [--blocks KERNEL] [--steps 1]
 
 builds (once) the instrumented library, runs a model of GPT-2 XL's layer sizes with random weights
 for a few one-token steps as a replayed graph, and prints for every launch of the last step when
 its first and last block started, passed the wait for the kernel in front, and ended (microseconds
 from the step's first mark), with the marks that the kernel's source places in between (A, B, C,
-D).  `--blocks attention_decode` adds every block of that kernel's third launch.  The instrumented
+D).  `--blocks attention_decode` adds every block of that kernel's third launch; `--steps 3` reports the
+last three steps one after another, which shows what lies between the end of one step and the start of the next.  The instrumented
 kernels are a little slower (a mark costs a block's first thread a global timer read and a store).
 """
 from __future__ import annotations
@@ -71,6 +72,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=576)
     ap.add_argument("--blocks", default=None, help="a kernel's name: list every block of its third launch")
+    ap.add_argument("--steps", type=int, default=1, help="consecutive steps to report (more than one shows the edge between steps)")
     args = ap.parse_args()
     if os.environ.get("EMBER_TIMELINE") != "1":
         print("set EMBER_TIMELINE=1: the marks are compiled in only then", file=sys.stderr)
@@ -99,7 +101,7 @@ def main() -> int:
     ids = sampler.sample(logits, params, streams, [0] * args.batch, out=engine.sample_target(args.batch))
     rows = list(range(args.batch))
     for i in range(12):
-        if i == 11:                      # the last step alone
+        if i == 12 - max(1, args.steps):  # the last step alone (or the last few)
             torch.cuda.synchronize()
             engine.ops.timeline()
         logits = engine.step([(s, [0], [0]) for s in slots], borrow=True, device_tokens=(ids, rows))
