@@ -246,6 +246,8 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="tokens of each prompt before decoding starts")
     ap.add_argument("--only", default=None, choices=["prefill"],
                     help="run only the 2,048-token prefill (a few repeats; prints its line and no benchmark record): for profiling")
+    ap.add_argument("--kernels", action="store_true",
+                    help="with --only prefill: one more step under torch's profiler, and the device time of each of its kernels")
     ap.add_argument("--linear", type=int, nargs=3, metavar=("M", "N", "K"), default=None,
                     help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
     ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
@@ -418,6 +420,26 @@ def main() -> int:
                 "host_queue_ms": [round(t, 3) for t in host_times]}
         if engine.ops.op_timing:     # EMBER_OP_TIMING=1: the time per kernel entry point over the repeats (launches do not overlap then)
             line["op_ms_per_prefill"] = {k: round(ms / len(times + [0, 0]), 4) for k, (n, ms) in sorted(engine.ops.op_times().items())}
+        if args.kernels:   # one more step, under torch's profiler (CUPTI): what each kernel takes inside the step
+            from torch.profiler import ProfilerActivity, profile
+            slots = [engine.open() for _ in range(n_seq)]
+            prompts = [rng.integers(0, V, plen).tolist() for _ in range(n_seq)]
+            torch.cuda.synchronize()
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                engine.step([(s, p, [plen - 1]) for s, p in zip(slots, prompts)])
+                torch.cuda.synchronize()
+            for s in slots:
+                engine.close(s)
+            evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                         key=lambda e: e.time_range.start)
+            agg: dict = {}
+            for e in evs:
+                n, us = agg.get(e.name, (0, 0.0))
+                agg[e.name] = (n + 1, us + e.time_range.end - e.time_range.start)
+            span = evs[-1].time_range.end - evs[0].time_range.start if evs else 0.0
+            line["kernels_us"] = {"span": round(span, 1), "sum": round(sum(us for _, us in agg.values()), 1),
+                                  "by_kernel": [[name[:64], n, round(us, 1)] for name, (n, us) in
+                                                sorted(agg.items(), key=lambda kv: -kv[1][1])[:14]]}
         print(json.dumps(line))
         return 0
 
