@@ -362,7 +362,7 @@ def test_per_launch_timing_and_ranges(tiny_folders, plains):
     plain = plains["tiny_b"]
     seqs = [random_ids(480 + i, plain.vocab, n) for i, n in enumerate((70, 9))]
     timed = Engine.from_folder(tiny_folders["tiny_b"], dtype="bfloat16", max_tokens=512,
-                               options=E.RuntimeOptions(op_timing=True, nvtx=True))
+                               options=E.RuntimeOptions.from_env().replace(op_timing=True, nvtx=True))
     assert not timed.cuda_graphs
     rows, _ = run_batch(timed, seqs, (60, 5))
     times = timed.ops.op_times()
