@@ -278,13 +278,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    // A warp reads 32 rows x 32 columns of the accumulator with a row in each thread.  A whole block in
-    // a matrix with 16-byte rows is finished as it is read: a thread's 32 columns are 128 bytes of the
-    // float32 residual and output (a line a thread, 16 bytes an access; with the residual fetched a column
-    // a lane through a turn in shared memory the output projection took 166 instead of 127 microseconds
-    // at 16,384 rows).  Blocks cut off by the matrix's edge, and rows that are not 16-byte aligned, are
-    // turned through shared memory and finished with a column in each lane.  The residual of a block is
-    // requested before its accumulator is read.
+    // A warp reads 32 rows x 32 columns of the accumulator with a row in each thread, turns the
+    // block through shared memory and finishes it with a column in each lane: the bias is one
+    // value a lane, and every access to the residual and the output covers 32 consecutive
+    // columns of one row.  The residual of a block is requested before its accumulator is read.
+    // (Tried for the residual: a thread finishing the 32 columns of its own row, 128 bytes of residual and
+    // of output a thread, with no turn.  The output projection gained, 167 -> 135 microseconds at 16,384
+    // rows, but the down projection lost, 264 -> 294, and the form without a residual ran 8 % slower
+    // for having the other beside it in the loop; taken out.)
     const int quarter = warp & 3;            // the 32 tensor-memory lanes this warp may read
     const int half = (warp - 2) >> 2;        // which of the two warps of this quarter: it takes every other 32 columns
     const bool vec_ok = p.out_f32 ? (p.N % 4 == 0) : (p.N % 8 == 0);
@@ -306,27 +307,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int r = 0; r < 32; ++r)
           res[r] = (p.residual && col_ok && r < rows) ? __ldcs(p.residual + (size_t)(m0 + r) * p.N + n) : 0.f;
       };
-      auto whole = [&](int c) { return vec_ok && c + 32 <= p.bn && n0 + c + 32 <= p.N; };  // finished by row (below)
       int c0 = half * 32;
-      if (c0 < p.bn && !whole(c0)) fetch_residual(c0);
+      if (c0 < p.bn) fetch_residual(c0);
       ok = mbar_wait(acc_full0 + 8 * as, (t >> 1) & 1);
       if (!ok) break;
       fence_after();
       const unsigned taddr = tmem + ((unsigned)(quarter * 32) << 16) + as * kAccStride;
       for (; c0 < p.bn; c0 += 64) {
-        // Whole blocks of 32 columns in a matrix whose rows are 16-byte aligned: each thread finishes the 32
-        // columns of its own row (128 bytes of the residual and of a float32 output: a whole line a thread).
-        const bool by_row = whole(c0);
-        float4 rr[8];
-        if (by_row && p.residual && lane < rows) {  // asked for before the accumulator is read
-          const float4* src = reinterpret_cast<const float4*>(p.residual + (size_t)(m0 + lane) * p.N + n0 + c0);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) rr[j] = __ldcs(src + j);
-        }
         unsigned acc[32];
         tmem_ld32(taddr + c0, acc);  // every lane of the warp takes part, whatever its row
         tmem_wait();
-        if (by_row) {
+        if (!p.residual && vec_ok && c0 + 32 <= p.bn && n0 + c0 + 32 <= p.N) {
+          // no residual to fetch: each thread finishes the 32 columns of its own row
           if (lane < rows) {
             const int n = n0 + c0;
             float v[32];
@@ -346,10 +338,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
               for (int j = 0; j < 32; ++j) v[j] = gelu_erf(v[j]);
             }
-            if (p.residual) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) v[4 * j] += rr[j].x, v[4 * j + 1] += rr[j].y, v[4 * j + 2] += rr[j].z, v[4 * j + 3] += rr[j].w;
-            }
             const size_t at = (size_t)(m0 + lane) * p.N + n;
             if (p.out_f32) {
               float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.out) + at);
@@ -366,7 +354,6 @@ __global__ void __launch_bounds__(kThreads, 1)
               }
             }
           }
-          if (c0 + 64 < p.bn && !whole(c0 + 64)) fetch_residual(c0 + 64);  // (the block after this one is turned)
           continue;
         }
 #pragma unroll
@@ -391,7 +378,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
           }
         }
-        if (c0 + 64 < p.bn && !whole(c0 + 64)) fetch_residual(c0 + 64);
+        if (c0 + 64 < p.bn) fetch_residual(c0 + 64);
         __syncwarp();
       }
       fence_before();
@@ -438,14 +425,17 @@ int tc_setup() {
 }
 
 // The tile width: the one whose waves of tiles cost least, a tile costing its columns plus a
-// fixed share (the first fill of the ring and the last epilogue, which nothing hides).  Among the
-// multiples of 64: the widths between them measured slower every time (GPT-2 XL's q|k|v product at
-// 2,048 rows: 28.5 microseconds at 192 columns, 36.3 at 208, 32.2 at 160).
+// fixed share (the first fill of the ring and the last epilogue, which nothing hides).  With few
+// waves (up to 4,096 rows) only multiples of 64 are considered: the widths between them run a tile
+// slower (GPT-2 XL's q|k|v product at 2,048 rows: 28.5 microseconds at 192 columns, 36.3 at 208,
+// 32.2 at 160), which many waves make up for by a fuller last wave (the down projection at 16,384
+// rows: 264 microseconds at 208 columns, 284 at 192) and few do not.
 int pick_bn(int M, int N, int groups, int ctas) {
   const int tiles_m = (M + BM * ctas - 1) / (BM * ctas);
+  const int step = tiles_m <= 16 ? 64 : 16;
   int best = 0;
   double best_cost = 0;
-  for (int bn = kMaxBN; bn >= 64; bn -= 64) {
+  for (int bn = kMaxBN; bn >= 64; bn -= step) {
     const int tiles = tiles_m * ((N + bn - 1) / bn);
     const double cost = (double)((tiles + groups - 1) / groups) * (bn + 32);
     if (!best || cost < best_cost - 1e-9) best = bn, best_cost = cost;
