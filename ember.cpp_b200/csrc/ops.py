@@ -36,8 +36,8 @@ _SIGNATURES = {
     "ember_linear_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_linear_stream": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
                             _c_void, _c_size, _c_void],
-    "ember_linear_decode": [_c_void, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int,
-                            _c_int, _c_int, _c_void, _c_void, _c_float, _c_void, _c_void, _c_void, _c_size, _c_void],
+    "ember_linear_decode": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void,
+                            _c_size, _c_void],
     "ember_clear_tails": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_kv_store": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_void],
@@ -66,18 +66,6 @@ class KernelError(RuntimeError):
 SMALL_M = 16          # rows up to which the mma.sync weight-streaming product (linear_decode.cu) is used
 STREAM_M = 64         # rows up to which the tcgen05 weight-streaming product (linear_stream.cu) is used above that
 TC_MIN_M = 64         # rows above which the tcgen05 product is used (its tiles have 128 rows)
-
-
-class LazyNorm:
-    """A layer norm that has not run yet: the next linear layer applies it in its own prologue.
-    Only `CudaOps.linear` takes one; `materialize()` gives the tensor."""
-
-    def __init__(self, ops, x, w, b, eps, out_dtype):
-        self.ops, self.x, self.w, self.b, self.eps, self.dtype = ops, x, w, b, eps, out_dtype
-        self.shape = x.shape
-
-    def materialize(self):
-        return self.ops.layernorm(self.x, self.w, self.b, self.eps, self.dtype)
 
 
 def _current_stream() -> int:
@@ -143,11 +131,6 @@ class CudaOps:
         self.sms = torch.cuda.get_device_properties(0).multi_processor_count
         self.decode_slots = 6 * self.sms   # blocks of the decode attention that are resident at once
         # What the switches are and why their defaults are what they are (all measured on GPT-2 XL's shapes):
-        # fuse_norm: a layer norm inside the following product's kernel.  Off: a separate norm kernel, overlapped
-        #   with the product's weight fetch by programmatic dependent launch, is faster (a step of 12 layers at 8
-        #   rows 0.586 against 0.683 ms with the norm's gain and bias staged beside the weights): every block of
-        #   the product reads and norms all the rows again, 300 to 400 times the norm kernel's traffic from L2.
-        self.fuse_norm = options.fuse_norm
         # cache_ahead: a decode attention asks the next layer's rows of the cache into L2.  Off: with the kernel
         #   that loads keys into registers the step's time did not change (0.5822 against 0.5820 ms of 12 layers);
         #   with the tensor-core kernel it grew (0.538 against 0.516 ms): a layer's rows and weights together do
@@ -156,21 +139,11 @@ class CudaOps:
         # decode_mma: decode attention on the tensor cores where that kernel has an instantiation (head size 64
         #   or 128, up to 8 query heads to a key/value head); off takes the other kernel.
         self.decode_mma = options.decode_mma
-        # tail_norm: the norm that follows a sum into the residual stream runs in the tail of that sum's product
-        #   (`expect_norm` announces it, `layernorm` then finds its result ready).  Off: at batch 8 a step of
-        #   GPT-2 XL takes 2.08 against 1.44 ms with it.  The separate norm kernel is not only hidden: while it
-        #   runs, every block of the next product is resident (nothing else holds shared memory) and has its
-        #   weights on the way; without it the next product's last blocks start when the sum's blocks leave and
-        #   wait for their weights then.
-        self.tail_norm = options.tail_norm
-        self._expected = None          # (gain, bias, eps, dtype) announced for the next sum
         self._warm = None              # tensor announced by `warm` for the next product
         self._coming = []              # weight matrices announced by `announce_weights`, in the order their products run
         # warm: the second product of a feed-forward has its weights landed about a microsecond earlier with it
         #   (its blocks cannot be resident beside the first product's); a step of 12 layers 0.519 against 0.521 ms.
         self.warm_ahead = options.warm
-        self._normed = None            # (stream ptr, gain ptr, bias ptr, eps, dtype, result) of the last tail norm
-        self._tail_counter = None
         # gemm: products of more than STREAM_M rows go to cuBLASLt ("lt"), as ember.cpp's own go to cuBLAS, or
         #   ("tc"), above TC_MIN_M rows, to this library's tcgen05 kernel.  On GPT-2 XL's four products the
         #   library is ahead at 2,048 rows; at 16,384 rows the tcgen05 kernel reaches 95 % of it on the QKV product.
@@ -273,18 +246,11 @@ class CudaOps:
             raise KernelError("embed: tokens from the device need both their rows and the ids")
         if ids is not None and (ids.dtype != torch.int32 or not ids.is_cuda or not ids.is_contiguous()):
             raise KernelError("embed: sampled ids are a contiguous int32 CUDA tensor")
-        self._expected = self._normed = None
         x = torch.empty((T, d), dtype=torch.float32, device=table.device)
         self._call("ember_embed", tokens.data_ptr(), positions.data_ptr(), self._dense(table, "token table").data_ptr(),
                    self._ptr(pos_table), x.data_ptr(), T, d, _code(table.dtype), self._ptr(token_src), self._ptr(ids),
                    0 if ids is None else ids.numel(), table.shape[0])
         return x
-
-    def expect_norm(self, w, b, eps, out_dtype) -> None:
-        """Announces that the result of the next sum into the residual stream (the next `linear`
-        with a residual) will be normed with these parameters.  A hint: the product may then norm
-        the stream in its own launch, and the `layernorm` call that follows returns that result."""
-        self._expected = (w, b, float(eps), out_dtype)
 
     def warm(self, tensor) -> None:
         """Announces constants that a kernel soon after the next product reads (the weights of the product
@@ -308,18 +274,9 @@ class CudaOps:
                 return nxt if nxt.numel() * nxt.element_size() <= self.AHEAD_BYTES else None
         return None
 
-    def layernorm(self, x, w, b, eps, out_dtype, lazy=False):
-        """Layer norm of float32 rows.  With `lazy` the caller promises to hand the result to
-        `linear` and nothing else; for a few rows in bfloat16 the norm then runs inside that
-        product's kernel and a LazyNorm is returned in place of a tensor."""
+    def layernorm(self, x, w, b, eps, out_dtype):
+        """Layer norm of float32 rows."""
         rows, d = x.shape
-        done, self._normed = self._normed, None
-        if done is not None and done[:5] == (x.data_ptr(), w.data_ptr(), b.data_ptr(), float(eps), out_dtype) \
-                and tuple(done[5].shape) == (rows, d):
-            return done[5]
-        if (lazy and self.fuse_norm and out_dtype == torch.bfloat16 and rows <= SMALL_M and d % 8 == 0 and d <= 16384
-                and x.dtype == torch.float32 and x.is_contiguous()):
-            return LazyNorm(self, x, w, b, eps, out_dtype)
         if x.dtype != torch.float32 or w.dtype != torch.float32 or b.dtype != torch.float32:
             raise KernelError("layernorm: input, gain and bias are float32")
         if w.shape[0] != d or b.shape[0] != d:
@@ -387,22 +344,12 @@ class CudaOps:
         sum is made in float32 into the residual's buffer, which is returned."""
         if act not in _ACT:
             raise KernelError(f"linear: activation {act!r}")
-        expected = None
         warm, self._warm = self._warm, None
-        if residual is not None:       # the sum into the stream that an announced norm follows
-            expected, self._expected = self._expected, None
-            self._normed = None        # the stream changes: an earlier norm of it is stale
-        norm = None
-        if isinstance(a, LazyNorm):
-            if w.dtype == torch.bfloat16:
-                norm, a = a, a.x
-            else:
-                a = a.materialize()
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K:
             raise KernelError(f"linear: input width {K} does not match the weight's {tuple(w.shape)}")
-        if norm is None and a.dtype != w.dtype:
+        if a.dtype != w.dtype:
             raise KernelError(f"linear: input is {a.dtype}, weight is {w.dtype}")
         if bias is not None and (bias.dtype != torch.float32 or bias.shape[0] != N):
             raise KernelError("linear: the bias is float32 of the output's width")
@@ -425,26 +372,10 @@ class CudaOps:
             # GPT-2 XL 1.556 -> 1.512 ms; at 16 rows nothing either way; below 8 rows it costs 1 to 2 %).
             if warm is None and M >= 8:
                 warm = self._after(w)
-            tail = None
-            if (self.tail_norm and residual is not None and expected is not None and expected[3] == torch.bfloat16
-                    and expected[0].dtype == torch.float32 and expected[1].dtype == torch.float32
-                    and expected[0].shape[0] == N and expected[1].shape[0] == N):
-                if self._tail_counter is None:
-                    self._tail_counter = torch.zeros(1, dtype=torch.int32, device=a.device)
-                tail = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-            self._call("ember_linear_decode", a.data_ptr(), None if norm is None else norm.w.data_ptr(),
-                       None if norm is None else norm.b.data_ptr(), 0.0 if norm is None else float(norm.eps),
-                       w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(), M, N, K, _ACT[act],
-                       _code(target), None if tail is None else expected[0].data_ptr(),
-                       None if tail is None else expected[1].data_ptr(), 0.0 if tail is None else expected[2],
-                       self._ptr(tail), None if tail is None else self._tail_counter.data_ptr(),
-                       None if warm is None else warm.data_ptr(),
+            self._call("ember_linear_decode", a.data_ptr(), w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(),
+                       M, N, K, _ACT[act], _code(target), None if warm is None else warm.data_ptr(),
                        0 if warm is None else warm.numel() * warm.element_size() // 16 * 16)
-            if tail is not None:
-                self._normed = (out.data_ptr(), expected[0].data_ptr(), expected[1].data_ptr(), expected[2], expected[3], tail)
             return out
-        if norm is not None:
-            a = norm.materialize()
         if self.linear_stream_on and M <= STREAM_M and K % 8 == 0:
             return self.linear_stream(a, w, bias, act, residual, out, warm=warm if warm is not None else self._after(w))
         # an output width that is no multiple of 8 (a vocabulary of 50,257) leaves the library only unaligned,

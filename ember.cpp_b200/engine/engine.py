@@ -75,7 +75,6 @@ class StepContext:
     plan: StepPlan
     apps: list
     position: object
-    next_norm: object = None   # set by the model: the norm that reads the stream after the current block, if any
     next_weights: tuple = ()   # set by the model: the first matrix that the block after the current one streams
 
 

@@ -25,8 +25,6 @@ options given in code), so a measurement can flip a switch without touching the 
   decode_cluster   EMBER_DECODE_CLUSTER   its chunks merge in a thread-block cluster (0: through scratch and a ticket)
   decode_bulk      EMBER_DECODE_BULK      the CUDA-core decode attention brings pages in by bulk copies (0: by loads)
   pdl              EMBER_PDL              programmatic dependent launch between the kernels of a step
-  fuse_norm        EMBER_FUSE_NORM        a layer norm runs in the prologue of the product after it (few rows)
-  tail_norm        EMBER_TAIL_NORM        a layer norm runs in the tail of the product before it (few rows)
   cache_ahead      EMBER_CACHE_AHEAD      a decode attention asks the next layer's rows of the cache into L2
   warm             EMBER_WARM             a small product asks the next product's weights into L2
   op_timing        EMBER_OP_TIMING        every launch is bracketed by CUDA events; `CudaOps.op_times()` gives the time per
@@ -73,8 +71,6 @@ class RuntimeOptions:
     decode_cluster: bool = True
     decode_bulk: bool = True
     pdl: bool = True
-    fuse_norm: bool = False
-    tail_norm: bool = False
     cache_ahead: bool = False
     warm: bool = True
     op_timing: bool = False

@@ -15,7 +15,6 @@ from .base import CacheNeed, Mixer, WeightSpec, register_part
 
 
 class CausalAttention(Mixer):
-    takes_lazy_norm = True
 
     def __init__(self, prefix: str, width: int, n_heads: int, kv_heads: int, head_dim: int, scale: float,
                  window: int = 0, qkv: str = "c_attn", out: str = "c_proj", stored: str = "in_out",

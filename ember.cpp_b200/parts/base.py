@@ -5,7 +5,7 @@ tensors are named by a prefix that the architecture gives it.  No part knows whi
 
 Roles and what each must provide:
 
-  norm      forward(ctx, x, out_dtype, lazy=False) -> tensor         (x: fp32 residual stream)
+  norm      forward(ctx, x, out_dtype) -> tensor                     (x: fp32 residual stream)
   mixer     forward(ctx, h, residual, app) -> new residual stream    (h: normed input)
             cache_need() -> CacheNeed | None, state_need() -> StateNeed | {name: StateNeed} | None
   ffn       forward(ctx, h, residual) -> new residual stream
@@ -80,20 +80,12 @@ class Part:
 class Norm(Part):
     role = "norm"
 
-    def forward(self, ctx, x, out_dtype, lazy=False):
-        """`lazy` is a hint that the result goes to `ops.linear` and nowhere else (so the kernels
-        may fuse the two); a norm may ignore it."""
+    def forward(self, ctx, x, out_dtype):
         raise NotImplementedError
-
-    def announce(self, ctx, out_dtype) -> None:
-        """Tells the kernels that the next sum into the residual stream is normed by this part
-        next (so that they may run the norm in that sum's launch).  A hint; the default says nothing."""
 
 
 class Mixer(Part):
     role = "mixer"
-    # True if forward() passes its normed input `h` to ops.linear and uses it for nothing else
-    takes_lazy_norm = False
 
     def cache_need(self) -> CacheNeed | None:
         return None
@@ -107,7 +99,6 @@ class Mixer(Part):
 
 class FeedForward(Part):
     role = "ffn"
-    takes_lazy_norm = False
 
     def forward(self, ctx, h, residual):
         raise NotImplementedError

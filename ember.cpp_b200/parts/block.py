@@ -3,9 +3,7 @@
 `pre_norm` is GPT-2's: `x -> norm1 -> mixer -> +x -> norm2 -> feed-forward -> +x`, the residual
 sums in float32 (graph_ir.cpp:732-756, the sequential branch; operand order x then the
 branch's output, :754-756).  The mixer and the feed-forward add into the stream themselves so that
-their last projection can do the sum in its epilogue.  Before each sum the block announces the norm
-that reads the stream next (its own second norm, or the first norm of whatever the model runs after
-this block), so that the kernels may run that norm in the sum's launch.
+their last projection can do the sum in its epilogue.
 """
 from __future__ import annotations
 
@@ -23,13 +21,9 @@ class PreNormBlock(Block):
         announce = getattr(ctx.ops, "announce_weights", None)
         if announce is not None:    # a hint: this block's matrices in the order they are streamed, then what follows
             announce(self.mixer.stream_weights() + self.ffn.stream_weights() + list(getattr(ctx, "next_weights", ())))
-        h = self.norm1.forward(ctx, x, ctx.dtype, lazy=self.mixer.takes_lazy_norm)
-        self.norm2.announce(ctx, ctx.dtype)         # what follows the mixer's sum into the stream
+        h = self.norm1.forward(ctx, x, ctx.dtype)
         x = self.mixer.forward(ctx, h, x, app)
-        h = self.norm2.forward(ctx, x, ctx.dtype, lazy=self.ffn.takes_lazy_norm)
-        after = getattr(ctx, "next_norm", None)     # what follows this block (set by the model), if a norm
-        if after is not None:
-            after.announce(ctx, ctx.dtype)
+        h = self.norm2.forward(ctx, x, ctx.dtype)
         return self.ffn.forward(ctx, h, x)
 
 

@@ -13,7 +13,6 @@ ACTIVATIONS = ("gelu_tanh", "gelu_erf")
 
 
 class DenseFeedForward(FeedForward):
-    takes_lazy_norm = True
 
     def __init__(self, prefix: str, width: int, inner: int, activation: str, up: str = "c_fc", down: str = "c_proj",
                  stored: str = "in_out", bias: bool = True, init_std: float = 0.02, down_init_std: float = 0.02,

@@ -91,18 +91,14 @@ class DecoderModel:
         if self.spec.embedding_scale != 1.0:
             x = ops.scale_cap(x, scale=self.spec.embedding_scale)
         for i, app in enumerate(ctx.apps):
-            if i + 1 < len(ctx.apps):
-                ctx.next_norm = self.blocks[ctx.apps[i + 1].layer].norm1
-                ctx.next_weights = self.blocks[ctx.apps[i + 1].layer].mixer.stream_weights()[:1]
-            else:  # the final norm reads the stream itself only if no rows are picked out first
-                ctx.next_norm = self.final_norm if plan.n_want and plan.wants_every_row else None
-                ctx.next_weights = ()
+            # (a hint for the kernels: the first matrix that the block after this one streams)
+            following = ctx.apps[i + 1].layer if i + 1 < len(ctx.apps) else None
+            ctx.next_weights = self.blocks[following].mixer.stream_weights()[:1] if following is not None else ()
             x = self.blocks[app.layer].forward(ctx, x, app)
-        ctx.next_norm = None
         if plan.n_want == 0:
             return None
         rows = x if plan.wants_every_row else ops.gather_rows(x, plan.want_rows, plan.n_want)
-        h = self.final_norm.forward(ctx, rows, ctx.dtype, lazy=True)
+        h = self.final_norm.forward(ctx, rows, ctx.dtype)
         logits = ops.linear(h, self.head, self.head_bias, out_dtype=torch.float32)
         if self.spec.logit_cap is not None:
             logits = ops.scale_cap(logits, cap=self.spec.logit_cap)

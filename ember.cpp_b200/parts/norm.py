@@ -27,15 +27,8 @@ class LayerNorm(Norm):
         self.w = runtime.vector(get(self.weight_name))
         self.b = runtime.vector(get(self.bias_name))
 
-    def forward(self, ctx, x, out_dtype, lazy=False):
-        """`lazy`: the caller hands the result to `ops.linear` only, which may then run the norm in
-        its own kernel (the value is the same)."""
-        return ctx.ops.layernorm(x, self.w, self.b, self.eps, out_dtype, lazy=lazy)
-
-    def announce(self, ctx, out_dtype) -> None:
-        expect = getattr(ctx.ops, "expect_norm", None)
-        if expect is not None:
-            expect(self.w, self.b, self.eps, out_dtype)
+    def forward(self, ctx, x, out_dtype):
+        return ctx.ops.layernorm(x, self.w, self.b, self.eps, out_dtype)
 
 
 register_part("norm", "layernorm", LayerNorm)

@@ -23,7 +23,7 @@ class CpuOps:
             x = x + pos_table[positions.long()].float()
         return x
 
-    def layernorm(self, x, w, b, eps, out_dtype, lazy=False):
+    def layernorm(self, x, w, b, eps, out_dtype):
         x = x.float()
         mean = x.mean(-1, keepdim=True)
         var = ((x - mean) ** 2).mean(-1, keepdim=True)

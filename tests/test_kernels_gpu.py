@@ -197,49 +197,6 @@ def test_linear_stream_every_split_and_ring(ops, M, N, K):
     ops.check()
 
 
-@pytest.mark.parametrize("M, N, K", [(1, 1600, 1600), (8, 1600, 6400), (9, 96, 64), (16, 2056, 72), (5, 100, 1600), (16, 1600, 1600)])
-def test_linear_norms_the_stream_in_its_tail(ops, M, N, K):
-    """A product that sums into the residual stream and was told which norm follows leaves that
-    norm's result ready: the block that finishes last computes it.  It equals the separate kernel's
-    result (to a rounding of bfloat16, the two add the row's sums in different orders), the stream
-    itself is what the product alone would give, and the counter is zero again for the next call."""
-    from ember_cpp_b200.csrc.ops import CudaOps
-    ops = CudaOps()
-    ops.tail_norm = True          # off by default: measured, it gains nothing over the separate kernel
-    a, w, bias = gen((M, K), 60, torch.bfloat16), gen((N, K), 61, torch.bfloat16, 0.1), gen((N,), 62)
-    res = gen((M, N), 63) * 3 + 1
-    gw, gb = gen((N,), 64) * 0.1 + 1, gen((N,), 65) * 0.1
-    for rep in range(3):
-        x = res.clone()
-        ops.expect_norm(gw, gb, 1e-5, torch.bfloat16)
-        out = ops.linear(a, w, bias, residual=x)
-        assert out.data_ptr() == x.data_ptr() and ops._normed is not None
-        launches = ops.launches
-        h = ops.layernorm(out, gw, gb, 1e-5, torch.bfloat16)
-        assert ops.launches == launches            # nothing was launched for the norm
-        assert int(ops._tail_counter.item()) == 0
-        want_x = linear_ref(a, w, bias, None, res)
-        assert (out.double() - want_x).abs().max().item() / want_x.abs().max().item() < 2e-4
-        apart = ops.layernorm(out, gw, gb, 1e-5, torch.bfloat16)
-        assert ops.launches == launches + 1        # the result is handed out once
-        ref = torch.nn.functional.layer_norm(out.double(), (N,), gw.double(), gb.double(), 1e-5)
-        assert (h.double() - ref).abs().max().item() < 2 ** -7 * ref.abs().max().item()
-        assert (h.float() - apart.float()).abs().max().item() <= 2 ** -7 * ref.abs().max().item()
-    # other parameters than the announced ones, or a changed stream: the norm runs as usual
-    x = res.clone()
-    ops.expect_norm(gw, gb, 1e-5, torch.bfloat16)
-    out = ops.linear(a, w, bias, residual=x)
-    launches = ops.launches
-    ops.layernorm(out, gb, gw, 1e-5, torch.bfloat16)
-    assert ops.launches == launches + 1
-    ops.expect_norm(gw, gb, 1e-5, torch.bfloat16)
-    out = ops.linear(a, w, bias, residual=x)
-    out = ops.linear(a, w, bias, residual=out)     # a second sum without an announcement
-    launches = ops.launches
-    ops.layernorm(out, gw, gb, 1e-5, torch.bfloat16)
-    assert ops.launches == launches + 1
-
-
 @pytest.mark.parametrize("M, N, K, tile_n", [(128, 64, 64, 0), (200, 1600, 1600, 0), (129, 1001, 72, 0), (65, 48, 4104, 16),
                                              (300, 500, 200, 48), (1000, 777, 136, 256), (2048, 4800, 1600, 0),
                                              (257, 6400, 320, 208)])
@@ -271,30 +228,6 @@ def test_linear_routes_large_products_to_the_tcgen05_kernel_when_asked(ops, monk
     monkeypatch.setattr(ops, "gemm", "tc")
     ops.linear(a, w, None)
     assert seen == [1]
-
-
-@pytest.mark.parametrize("M, N, K", [(1, 4800, 1600), (7, 100, 96), (16, 1000, 64), (11, 320, 2056), (4, 64, 4104)])
-def test_linear_with_the_norm_in_its_prologue(ops, M, N, K):
-    """The layer norm run inside the product's kernel gives what the separate kernel gives."""
-    from ember_cpp_b200.csrc.ops import CudaOps, LazyNorm
-    ops = CudaOps()
-    ops.fuse_norm = True          # off by default: a separate norm kernel measured faster
-    x = gen((M, K), 34) * 2 + 0.5
-    gw, gb = gen((K,), 35) * 0.1 + 1, gen((K,), 36) * 0.1
-    w, bias = gen((N, K), 37, torch.bfloat16, 0.1), gen((N,), 38)
-    lazy = ops.layernorm(x, gw, gb, 1e-5, torch.bfloat16, lazy=True)
-    assert isinstance(lazy, LazyNorm)
-    fused = ops.linear(lazy, w, bias, act="gelu_tanh", out_dtype=torch.bfloat16)
-    h = ops.layernorm(x, gw, gb, 1e-5, torch.bfloat16)
-    apart = ops.linear(h, w, bias, act="gelu_tanh", out_dtype=torch.bfloat16)
-    want = linear_ref(h, w, bias, "gelu_tanh", None)
-    scale = want.abs().max().item()
-    assert (fused.double() - want).abs().max().item() / scale < 2 ** -7
-    assert (fused.double() - apart.double()).abs().max().item() / scale < 2 ** -7
-    assert torch.equal(lazy.materialize(), h)
-    # more rows than the streaming kernel takes: the norm runs on its own
-    assert torch.is_tensor(ops.layernorm(gen((17, K), 39), gw, gb, 1e-5, torch.bfloat16, lazy=True))
-    assert torch.is_tensor(ops.layernorm(x, gw, gb, 1e-5, torch.float32, lazy=True))
 
 
 @pytest.mark.parametrize("M, N, K", [(8, 6400, 1600), (3, 100, 72), (16, 48, 4104)])

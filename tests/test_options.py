@@ -13,7 +13,7 @@ def test_defaults_and_variable_names():
     assert RuntimeOptions.variable("decode_mma") == "EMBER_DECODE_MMA"
     assert {f.name for f in dataclasses.fields(RuntimeOptions)} >= {
         "dtype", "max_tokens", "max_slots", "cuda_graphs", "prompt_graphs", "deterministic", "gemm", "lt_tune", "linear_stream", "attention",
-        "decode_mma", "decode_cluster", "decode_bulk", "pdl", "fuse_norm", "tail_norm", "cache_ahead", "warm", "op_timing", "nvtx"}
+        "decode_mma", "decode_cluster", "decode_bulk", "pdl", "cache_ahead", "warm", "op_timing", "nvtx"}
 
 
 def test_variables_override_the_given_options():
