@@ -241,10 +241,12 @@ class Engine:
         self._account(host, shape)
         return logits
 
+    PROMPT_GRAPH_TOKENS = 8192   # a captured step keeps its activations' memory: larger steps are launched from the host
+
     def _prompt_graph(self, host):
         """The captured graph of a step of this shape, made when the shape comes for the second time; None for
         a shape that is new (it runs launch by launch) or when such graphs are off."""
-        if not (self.prompt_graphs > 0 and self.cuda_graphs):
+        if not (self.prompt_graphs > 0 and self.cuda_graphs) or host.T > self.PROMPT_GRAPH_TOKENS:
             return None
         key = (host.T, host.n, host.n_want, host.max_new, -(-host.max_end // 64), host.all_from_zero,
                host.wants_every_row, host.packed.shape[0])
