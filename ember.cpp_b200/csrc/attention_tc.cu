@@ -274,11 +274,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       }
       // a row that has seen no key yet keeps m = -inf; its exponent base is 0 so that nothing is NaN
       const float base_e = m_used == -INFINITY ? 0.f : m_used * p.scale_log2;
-      // the buffer of P is free once the products of two steps ago have read it
-      if (it >= 2) {
-        ok = mbar_wait(pv_done + 8 * b, ((it - 2) >> 1) & 1);
-        if (!ok) break;
-      }
+      // The buffer of P is free once the products of two steps ago have read it, and they have: the scores of
+      // this step were issued after them, the tensor core finishes a block's products in the order they were
+      // issued, and this step's scores were waited for above (their commit covers everything issued before).
       unsigned char* p_row = p_rows + b * kPBytes;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
