@@ -130,18 +130,25 @@ __global__ void __launch_bounds__(kThreads, 2)
                  recv_bar = res_bar + 8;
   const unsigned tmem_cols = p.mp <= 32 ? 32u : 64u;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) {
-      mbar_init(full0 + 8 * s, 1);
-      mbar_init(empty0 + 8 * s, 1);
+  // The barriers are set up by the first warp's lanes side by side (one after the other they cost the block's
+  // first thread a third of a microsecond before it can ask for anything).
+  if (warp == 0) {
+    if (lane < p.stages) {
+      mbar_init(full0 + 8 * lane, 1);
+      mbar_init(empty0 + 8 * lane, 1);
     }
-    mbar_init(done, 1);
-    mbar_init(res_bar, 1);
-    mbar_init(recv_bar, 1);
-    if (split > 1)  // what the partners will send: every other block's partial sums of this block's quads
-      mbar_expect_tx(recv_bar, (unsigned)((split - 1) * (quad_lo(quads, split, rank + 1) - quad_lo(quads, split, rank)) * BM * 16));
+    if (lane == 31) {
+      mbar_init(done, 1);
+      mbar_init(res_bar, 1);
+      mbar_init(recv_bar, 1);
+      if (split > 1)  // what the partners will send: every other block's partial sums of this block's quads
+        mbar_expect_tx(recv_bar, (unsigned)((split - 1) * (quad_lo(quads, split, rank + 1) - quad_lo(quads, split, rank)) * BM * 16));
+      s_failed = 0;
+    }
     mbar_init_fence();
-    s_failed = 0;
+    __syncwarp();
+  }
+  if (threadIdx.x == 0) {
     // The weights of the ring's first turn are asked for at once: before the other warps are met,
     // before tensor memory is there, and before the kernel in front is waited for (programmatic
     // dependent launch).  Weights are constants of the model.
