@@ -71,7 +71,9 @@ struct StreamArgs {
 
 enum : int { ST_PRODUCER = 21, ST_MMA = 22, ST_EPILOGUE = 23, ST_DRAIN = 24 };
 
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
+// (Relaxed: what the partners must see, this block's initialised barriers, was released at cluster scope by the
+// initialising lanes' own fence, and every thread that fenced also arrives here.)
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.relaxed.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ unsigned map_to_rank(unsigned addr, unsigned rank) {
   unsigned r;
