@@ -271,20 +271,27 @@ __global__ void __launch_bounds__(kThreads, 2)
     if (ok) {
       const unsigned taddr = tmem + ((unsigned)(quarter * 32) << 16);
       const unsigned mine = recv + (unsigned)((rank * q_most * BM + row) * 16);
-      for (int c = 0; c < p.mp; c += 16) {
-        unsigned a[16];
-        tmem_ld16(taddr + c, a);
-        tmem_wait();
+      // all of the row's columns are asked for before the first is waited for: one trip to tensor memory
+      unsigned a[kMaxRows / 16][16];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int q = (c >> 2) + j;
-          const unsigned owner = s_owner[q], at = mine + (unsigned)(s_local[q] * (BM * 16));
-          if ((int)owner == rank)
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(at), "r"(a[4 * j]), "r"(a[4 * j + 1]), "r"(a[4 * j + 2]),
-                         "r"(a[4 * j + 3])
-                         : "memory");
-          else
-            st_async_f4(map_to_rank(at, owner), a[4 * j], a[4 * j + 1], a[4 * j + 2], a[4 * j + 3], map_to_rank(recv_bar, owner));
+      for (int i = 0; i < kMaxRows / 16; ++i)
+        if (16 * i < p.mp) tmem_ld16(taddr + 16 * i, a[i]);
+      tmem_wait();
+#pragma unroll
+      for (int i = 0; i < kMaxRows / 16; ++i) {
+        if (16 * i < p.mp) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int q = 4 * i + j;
+            const unsigned owner = s_owner[q], at = mine + (unsigned)(s_local[q] * (BM * 16));
+            if ((int)owner == rank)
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(at), "r"(a[i][4 * j]), "r"(a[i][4 * j + 1]),
+                           "r"(a[i][4 * j + 2]), "r"(a[i][4 * j + 3])
+                           : "memory");
+            else
+              st_async_f4(map_to_rank(at, owner), a[i][4 * j], a[i][4 * j + 1], a[i][4 * j + 2], a[i][4 * j + 3],
+                          map_to_rank(recv_bar, owner));
+          }
         }
       }
     }
