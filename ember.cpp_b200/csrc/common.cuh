@@ -101,7 +101,7 @@ struct Entry {
   unsigned what;         // kernel << 8 | mark
   unsigned block;        // linear block index
   unsigned grid;         // blocks of the launch
-  unsigned pad;
+  unsigned sm;           // the SM the block runs on
 };
 static __device__ Entry g_log[kCap];
 static __device__ unsigned g_n;
@@ -117,7 +117,7 @@ __device__ __forceinline__ void put(unsigned at, unsigned kernel, unsigned m) {
     e.what = kernel << 8 | m;
     e.block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
     e.grid = gridDim.x * gridDim.y * gridDim.z;
-    e.pad = 0;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(e.sm));
     g_log[at + m] = e;
   }
 }
@@ -184,6 +184,16 @@ inline int sm_count() {
   return cached[dev];
 }
 
+// A launch whose blocks all fit the chip at once is fastest with its blocks on as many SMs as can be (an
+// SM takes in only some 50 KB a microsecond, and the block scheduler fills the SMs that are free first to
+// the brim): a request for more shared memory than the block needs caps what an SM takes at
+// ceil(blocks / SMs) blocks.
+inline size_t spread_smem(size_t need, long long blocks) {
+  const long long per_sm = (blocks + sm_count() - 1) / sm_count();
+  const size_t room = (size_t)(227 * 1024) / (size_t)per_sm;
+  const size_t want = room > 8192 ? room - 6144 : 0;  // less a block's own kilobyte of the SM's shared memory and its static variables
+  return want > need ? want : need;
+}
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};

@@ -293,7 +293,7 @@ class CudaOps:
 
     def timeline(self):
         """What the kernels of a library built with EMBER_TIMELINE=1 noted since the last call: a list of
-        (nanoseconds, kernel name, mark, block, blocks of the launch) sorted by time; mark 0 = the block
+        (nanoseconds, kernel name, mark, block, blocks of the launch, SM) sorted by time; mark 0 = the block
         started, 1 = its wait for the kernel in front returned, 2 = it ended (3: it ended after merging
         the partial results of a decode attention), 4 to 7 = places in between that the kernel's source
         names.  Synchronizes with the device."""
@@ -309,9 +309,9 @@ class CudaOps:
             if n < 0:
                 raise KernelError(f"timeline: reading the log of {name}.cu failed")
             for i in range(n):
-                t, what, block, grid, _ = struct.unpack_from("<QIIII", buf, i * 24)
+                t, what, block, grid, sm = struct.unpack_from("<QIIII", buf, i * 24)
                 if t:
-                    out.append((t, self.TIMELINE_KERNELS.get(what >> 8, str(what >> 8)), what & 255, block, grid))
+                    out.append((t, self.TIMELINE_KERNELS.get(what >> 8, str(what >> 8)), what & 255, block, grid, sm))
         out.sort()
         return out
 

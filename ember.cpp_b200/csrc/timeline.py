@@ -5,7 +5,7 @@
 builds (once) the instrumented library, runs a model of GPT-2 XL's layer sizes with random weights
 for a few one-token steps as a replayed graph, and prints for every launch of the last step when
 its first and last block started, passed the wait for the kernel in front, and ended (microseconds
-from the step's first mark), with the marks that the kernel's source places in between (A, B, C,
+from the step's first mark), on how many SMs its blocks ran and the most that one SM took, with the marks that the kernel's source places in between (A, B, C,
 D).  `--blocks attention_decode` adds every block of that kernel's third launch; `--steps 3` reports the
 last three steps one after another, which shows what lies between the end of one step and the start of the next.  The instrumented
 kernels are a little slower (a mark costs a block's first thread a global timer read and a store).
@@ -21,19 +21,20 @@ ORDER = (0, 1, 7, 4, 5, 6, 2, 3)
 
 
 def launches_of(marks):
-    """Groups (t, kernel, mark, block, grid) into launches: a block's start mark joins the open launch
+    """Groups (t, kernel, mark, block, grid, sm) into launches: a block's start mark joins the open launch
     of its (kernel, grid) until that launch has all its blocks (or, for a kernel whose idle blocks leave
     no mark, until the block index repeats); its later marks go where its start went."""
     launches, open_, of_block = [], {}, {}
-    for t, k, m, b, g in marks:
+    for t, k, m, b, g, sm in marks:
         key = (k, g)
         if m == 0:
             cur = open_.get(key)
             if cur is None or cur["n"] >= g or b in cur["blocks"]:
-                cur = dict(kernel=k, grid=g, n=0, t={}, blocks={})
+                cur = dict(kernel=k, grid=g, n=0, t={}, blocks={}, sms={})
                 launches.append(cur)
                 open_[key] = cur
             cur["n"] += 1
+            cur["sms"][sm] = cur["sms"].get(sm, 0) + 1
             of_block[(k, g, b)] = cur
         cur = of_block.get((k, g, b))
         if cur is None:
@@ -49,7 +50,7 @@ def report(launches, blocks_of: str | None = None) -> str:
     t0 = launches[0]["t"][0][0]
     lines = []
     for cur in launches:
-        parts = [f'{cur["kernel"]:17s} grid {cur["grid"]:5d} n {cur["n"]:5d}']
+        parts = [f'{cur["kernel"]:17s} grid {cur["grid"]:5d} n {cur["n"]:5d} on {len(cur["sms"]):3d} SMs (<= {max(cur["sms"].values()):2d})']
         for m in ORDER:
             if m in cur["t"]:
                 lo, hi = cur["t"][m]

@@ -267,10 +267,11 @@ ops.timeline()
 h = ops.layernorm(x, w, b, 1e-5, torch.bfloat16)
 y = ops.linear(h, torch.randn(96, 320, device="cuda").bfloat16(), None)
 marks = ops.timeline()
-names = {(k, m) for _, k, m, _, _ in marks}
+names = {(k, m) for _, k, m, _, _, _ in marks}
 assert {("layernorm", 0), ("layernorm", 1), ("layernorm", 2), ("linear_decode", 0), ("linear_decode", 1),
         ("linear_decode", 2)} <= names, names
-assert sum(1 for _, k, m, _, _ in marks if k == "linear_decode" and m == 0) == 6   # 96 / 16 tiles
+assert sum(1 for _, k, m, _, _, _ in marks if k == "linear_decode" and m == 0) == 6   # 96 / 16 tiles
+assert all(0 <= sm < torch.cuda.get_device_properties(0).multi_processor_count for *_, sm in marks)
 assert all(a[0] <= b[0] for a, b in zip(marks, marks[1:]))
 assert ops.timeline() == []
 print("ok")
