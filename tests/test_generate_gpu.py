@@ -218,16 +218,38 @@ def check_top1(got, ref) -> int:
     return int(sure.sum())
 
 
-def shape_engines(n_embd, n_head, n_inner, n_layer, max_tokens, seed):
+def shape_engines(n_embd, n_head, n_inner, n_layer, max_tokens, seed, n_positions=1024):
     """The two compute types over one set of random weights of the given layer sizes (vocabulary 50,257)."""
     from ember_cpp_b200.config import get_architecture
     from ember_cpp_b200.parts import DecoderModel
     from ember_cpp_b200.weights import random_tensors
-    cfg = E.GPT2Config.from_dict(dict(vocab_size=50257, n_positions=1024, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
+    cfg = E.GPT2Config.from_dict(dict(vocab_size=50257, n_positions=n_positions, n_embd=n_embd, n_layer=n_layer, n_head=n_head,
                                       n_inner=n_inner, activation_function="gelu_new", layer_norm_epsilon=1e-5))
     spec = get_architecture(cfg.architecture).build_spec(cfg)
     tensors = random_tensors(DecoderModel(spec).weight_specs(), seed, torch.bfloat16, "cuda")
     return {d: Engine.from_spec(spec, tensors, dtype=d, max_tokens=max_tokens) for d in DTYPES}
+
+
+def test_a_context_of_four_thousand_positions():
+    """A configuration with 4,096 positions (four heads of 64, two layers): prompts of 4,020 and 700 tokens in
+    one step (63 pages for the longer one), then 24 one-token steps across a page's edge in the largest
+    buckets of lengths, bfloat16 against the 32-bit path on the same weights."""
+    engines = shape_engines(256, 4, 1024, 2, 2 * 4096, seed=41, n_positions=4096)
+    seqs = [random_ids(4100 + i, 50257, n + 24) for i, n in enumerate((4020, 700))]
+    rows = {}
+    for d, eng in engines.items():
+        slots = [eng.open() for _ in seqs]
+        out = [eng.step([(s, q[:-24], [len(q) - 25]) for s, q in zip(slots, seqs)]).float().cpu().numpy()]
+        for k in range(24, 0, -1):
+            out.append(eng.step([(s, [q[-k]], [0]) for s, q in zip(slots, seqs)]).float().cpu().numpy())
+        rows[d] = np.concatenate(out)
+        eng.ops.check()
+        assert eng.length(slots[0]) == 4044
+        for s in slots:
+            eng.close(s)
+    assert rows["float32"].shape == (2 + 48, 50257)
+    assert rel_error(rows["bfloat16"], rows["float32"]) < TOL["bfloat16"]
+    assert check_top1(rows["bfloat16"], rows["float32"]) > 0
 
 
 def test_large_shape_ragged_prompts_then_256_steps():

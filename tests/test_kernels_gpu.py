@@ -597,6 +597,41 @@ def test_decode_attention_finds_one_far_key(hd, mma):
                 assert (got - want).abs().max().item() < 5e-2
 
 
+@pytest.mark.parametrize("far", [5, 2111, 4031])
+def test_attention_finds_one_key_among_thousands(ops, far):
+    """Contexts of more than 4,000 positions (65 pages; a configuration may ask for them): a prompt through
+    the tcgen05 kernel and one-token steps through the tensor-core decode kernel (few sequences: chunks merged
+    in a cluster; many: longer walks), with one key that stands out in the first page, in the middle or in the
+    last full page.  Every later query must return that key's value and nothing of the other rows, whose
+    values differ from page to page."""
+    heads, hd = 2, 64
+
+    def shape(data):
+        qw = heads * hd
+        for d in data:
+            n = d.shape[0]
+            d[:, :2 * qw] *= 0.05
+            if far < n:
+                d[far, qw:2 * qw] = 4.0                          # the key that stands out, in every head
+                d[far + 1:, :qw] = 4.0                           # the later queries aligned with it
+            d[:, 2 * qw:] = ((torch.arange(n) // 7) % 16)[:, None].float() / 8
+            if far < n:
+                d[far, 2 * qw:] = 7.0
+        return data
+
+    got, want = run_attention(ops, [(0, 4100)], heads, heads, hd, "bfloat16", seed=7, qkv_fn=shape, poison=NAN)
+    ops.check()
+    assert (got[far + 1:] - 7.0).abs().max().item() < 5e-2
+    assert (got - want).abs().max().item() < 5e-2
+    few = [(4100, 1), (far + 1, 1), (4159, 1)]
+    many = [(far + 1 + 5 * i, 1) for i in range(40)]
+    for seqs in (few, many):
+        got, want = run_attention(ops, seqs, heads, heads, hd, "bfloat16", seed=8, qkv_fn=shape, poison=NAN)
+        ops.check()
+        assert (got - 7.0).abs().max().item() < 5e-2, len(seqs)
+        assert (got - want).abs().max().item() < 5e-2
+
+
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("mma", [True, False])
 @pytest.mark.parametrize("p", [63, 64, 65, 191, 192, 511, 700])
