@@ -25,13 +25,10 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int kWarps = 2;
 constexpr int kMaxCluster = 8;      // chunks of a (token, head) that can merge through distributed shared memory
-constexpr int kThreads = kWarps * 32;
 constexpr int kMaxChunkPages = 64;  // page numbers of a chunk kept in shared memory
 constexpr int kMergeAtOnce = 8;     // chunks whose partial results the merging block fetches in one batch
 constexpr int kMaxGroup = 8;        // query heads per key/value head that a block takes as rows
-static_assert(kMaxChunkPages <= kThreads, "a thread fetches at most one page number of its chunk");
 
 __device__ int g_gave_up = 0;  // set when a warp's wait for its page ran out
 
@@ -71,8 +68,9 @@ __device__ __forceinline__ unsigned swz(int row, int chunk) { return (unsigned)(
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory"); }
 
-template <int HD, bool CLUSTER>
-__global__ void __launch_bounds__(kThreads, 6)
+// W: the block's warps (2 or 4), a page each at a time.
+template <int HD, bool CLUSTER, int W>
+__global__ void __launch_bounds__(W * 32, W == 2 ? 6 : 3)
 attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                             const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ out,
                             float* __restrict__ part_ml, float* __restrict__ part_acc, int* __restrict__ counters,
@@ -81,6 +79,8 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             int window, int pages_per_chunk, int n_chunks, __nv_bfloat16* __restrict__ k_store,
                             __nv_bfloat16* __restrict__ v_store, const __nv_bfloat16* __restrict__ ahead_k,
                             const __nv_bfloat16* __restrict__ ahead_v) {
+  constexpr int kWarps = W, kThreads = W * 32;
+  static_assert(kMaxChunkPages <= kThreads, "a thread fetches at most one page number of its chunk");
   constexpr int KS = HD / 16;                   // 16-wide steps over the head's dims
   constexpr int kBoxes = HD / 64;               // TMA boxes (64 dims wide) of a page's keys
   constexpr unsigned kBox = kPage * 128;        // bytes of a box
@@ -328,7 +328,7 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
   EMBER_MARK(kAttentionDecode, kPhaseA);  // keys folded
 
-  // the two warps' results, over the stages (both warps are done with them)
+  // the warps' results, over the stages (every warp is done with them)
   float* s_m = reinterpret_cast<float*>(smem_raw);   // [kWarps][kMaxGroup]
   float* s_l = s_m + kWarps * kMaxGroup;             // [kWarps][kMaxGroup]
   float* s_acc = s_l + kWarps * kMaxGroup;           // [kWarps][kMaxGroup][HD]
@@ -349,11 +349,16 @@ attention_decode_mma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   for (int i = threadIdx.x; i < group * HD; i += kThreads) {
     const int row = i / HD, d = i % HD;
     const int h = kvh * group + row;
-    const float m0 = s_m[row], m1 = s_m[kMaxGroup + row];
-    const float M = fmaxf(m0, m1);
-    const float w0 = weight(m0, M), w1 = weight(m1, M);
-    const float L = s_l[row] * w0 + s_l[kMaxGroup + row] * w1;
-    const float A = s_acc[row * HD + d] * w0 + s_acc[(kMaxGroup + row) * HD + d] * w1;
+    float M = s_m[row];
+#pragma unroll
+    for (int w = 1; w < kWarps; ++w) M = fmaxf(M, s_m[w * kMaxGroup + row]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {  // in warp order
+      const float ww = weight(s_m[w * kMaxGroup + row], M);
+      L += s_l[w * kMaxGroup + row] * ww;
+      A += s_acc[(w * kMaxGroup + row) * HD + d] * ww;
+    }
     const size_t item = ((size_t)t * n_heads + h) * n_chunks + c;
     if (n_valid == 1) {
       out[((size_t)t * n_heads + h) * HD + d] = __float2bfloat16_rn(A / L);
@@ -486,17 +491,17 @@ int cache_map(const void* ptr, long long rows, int hd, CUtensorMap* out) {
   return 0;
 }
 
-template <int HD>
+template <int HD, int W>
 int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, void* kc, void* vc, void* out,
            float* part_ml, float* part_acc, int* counters, const int* positions, const int* seq_slot, const int* pages,
            int max_blocks, int n_chunks, int T, int n_heads, int kv_heads, float scale, int window, int pages_per_chunk,
            int store_kv, const void* ahead_k, const void* ahead_v, cudaStream_t stream) {
-  constexpr size_t smem = (size_t)kWarps * 2 * (HD / 64) * kPage * 128 + 1024;
+  constexpr size_t smem = (size_t)W * 2 * (HD / 64) * kPage * 128 + 1024;
   static bool configured = false;  // per instantiation
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, false, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, true, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return ember_fail("attention_decode_mma: %s", cudaGetErrorString(e));
     configured = true;
   }
@@ -505,7 +510,7 @@ int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, 
   const bool cluster = cluster_allowed && n_heads == kv_heads && n_chunks >= 2 && n_chunks <= kMaxCluster;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_chunks, kv_heads, T);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(W * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attrs[2];
@@ -525,10 +530,10 @@ int launch(const CUtensorMap& map_k, const CUtensorMap& map_v, const void* qkv, 
   const __nv_bfloat16* ak = (const __nv_bfloat16*)ahead_k;
   const __nv_bfloat16* av = (const __nv_bfloat16*)ahead_v;
   cudaError_t e =
-      cluster ? cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, true>, map_k, map_v, q, o, part_ml, part_acc, counters,
+      cluster ? cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, true, W>, map_k, map_v, q, o, part_ml, part_acc, counters,
                                    positions, seq_slot, pages, max_blocks, n_heads, kv_heads, scale_log2, window,
                                    pages_per_chunk, n_chunks, ks, vs, ak, av)
-              : cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, false>, map_k, map_v, q, o, part_ml, part_acc, counters,
+              : cudaLaunchKernelEx(&cfg, attention_decode_mma_kernel<HD, false, W>, map_k, map_v, q, o, part_ml, part_acc, counters,
                                    positions, seq_slot, pages, max_blocks, n_heads, kv_heads, scale_log2, window,
                                    pages_per_chunk, n_chunks, ks, vs, ak, av);
   if (e != cudaSuccess) return ember_fail("attention_decode_mma: %s", cudaGetErrorString(e));
@@ -574,11 +579,16 @@ EMBER_API int ember_attention_decode_mma(const void* qkv, void* kc, void* vc, vo
   CUtensorMap map_k, map_v;
   const long long rows = (long long)n_pages * kv_heads * kPage;
   if (cache_map(kc, rows, hd, &map_k) || cache_map(vc, rows, hd, &map_v)) return 1;
+  // Chunks of three or four pages take four warps, a page each, so that all of a chunk's pages are on their
+  // way from the block's first instruction (head size 64; three such blocks fit an SM).
+  if (hd == 64 && pages_per_chunk >= 3 && pages_per_chunk <= 4 && (long long)n_chunks * kv_heads * T <= 3LL * sm_count())
+    return launch<64, 4>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
+                         n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
   if (hd == 64)
-    return launch<64>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
-                      n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
-  return launch<128>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
-                     n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
+    return launch<64, 2>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
+                         n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
+  return launch<128, 2>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
+                        n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
 }
 
 EMBER_TIMELINE_READER(attention_decode_mma)

@@ -492,6 +492,12 @@ class CudaOps:
             mma = self.decode_mma and head_dim in (64, 128) and n_heads // kv_heads <= 8
             pairs = plan.T * (kv_heads if mma else n_heads)   # the tensor-core kernel takes a group of heads a block
             n_chunks = max(1, min(self.decode_slots // pairs, -(-blocks // 2)))
+            # Head size 64 on the tensor cores: while chunks of up to four pages are few enough for three such
+            # blocks an SM to hold them all, the chunks are that long and a block has four warps, a page each:
+            # fewer blocks to merge (none up to four pages), and every page on its way from the block's start.
+            by_four = -(-blocks // 4)
+            if mma and head_dim == 64 and blocks > 2 and by_four <= 8 and by_four * pairs <= 3 * self.sms:
+                n_chunks = by_four
             per_chunk = -(-blocks // n_chunks)
             n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
             partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
