@@ -581,7 +581,7 @@ EMBER_API int ember_attention_decode_mma(const void* qkv, void* kc, void* vc, vo
   if (cache_map(kc, rows, hd, &map_k) || cache_map(vc, rows, hd, &map_v)) return 1;
   // Chunks of three or four pages take four warps, a page each, so that all of a chunk's pages are on their
   // way from the block's first instruction (head size 64; three such blocks fit an SM).
-  if (hd == 64 && pages_per_chunk >= 3 && pages_per_chunk <= 4 && (long long)n_chunks * kv_heads * T <= 3LL * sm_count())
+  if (hd == 64 && pages_per_chunk >= 3 && (long long)n_chunks * kv_heads * T <= 3LL * sm_count())
     return launch<64, 4>(map_k, map_v, qkv, kc, vc, out, part_ml, part_acc, counters, positions, seq_slot, pages, max_blocks,
                          n_chunks, T, n_heads, kv_heads, scale, window, pages_per_chunk, store_kv, ahead_k, ahead_v, stream);
   if (hd == 64)

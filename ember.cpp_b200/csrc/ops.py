@@ -492,12 +492,17 @@ class CudaOps:
             mma = self.decode_mma and head_dim in (64, 128) and n_heads // kv_heads <= 8
             pairs = plan.T * (kv_heads if mma else n_heads)   # the tensor-core kernel takes a group of heads a block
             n_chunks = max(1, min(self.decode_slots // pairs, -(-blocks // 2)))
-            # Head size 64 on the tensor cores: while chunks of up to four pages are few enough for three such
-            # blocks an SM to hold them all, the chunks are that long and a block has four warps, a page each:
-            # fewer blocks to merge (none up to four pages), and every page on its way from the block's start.
-            by_four = -(-blocks // 4)
-            if mma and head_dim == 64 and blocks > 2 and by_four <= 8 and by_four * pairs <= 3 * self.sms:
-                n_chunks = by_four
+            # Head size 64 on the tensor cores: while chunks of up to four pages (else of up to eight) are few
+            # enough for three blocks of four warps an SM to hold them all, the chunks are that long and a block
+            # has four warps, a page each at a time: fewer blocks to merge (none up to four pages), and four
+            # pages of a chunk on their way from the block's start.  (GPT-2 XL at batch 8: the first steps
+            # 1.312 -> 1.260 ms, the sweep to 1,024 tokens 1.433 -> 1.414.)
+            if mma and head_dim == 64 and blocks > 2:
+                for longest in (4, 8):
+                    n = -(-blocks // longest)
+                    if n <= 8 and n * pairs <= 3 * self.sms:
+                        n_chunks = n
+                        break
             per_chunk = -(-blocks // n_chunks)
             n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
             partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
