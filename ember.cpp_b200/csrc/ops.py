@@ -368,10 +368,9 @@ class CudaOps:
         # rows on (GPT-2 XL's head at 16 rows: 34.7 against 48.0 microseconds; at 8 rows 32.9 against 27.4).
         big = w.numel() * 2 > (64 << 20) and M > 8 and self.linear_stream_on
         if M <= SMALL_M and K % 8 == 0 and K <= 16384 and not big:
-            # From 8 rows on, the next announced matrix is asked into L2 by every product (at batch 8 a step of
-            # GPT-2 XL 1.556 -> 1.512 ms; at 16 rows nothing either way; below 8 rows it costs 1 to 2 %).
-            if warm is None and M >= 8:
-                warm = self._after(w)
+            # (Only a matrix that a part announced with `warm` is asked into L2 here.  Every product asking for the
+            # next announced matrix paid at 8 rows once, 1.556 -> 1.512 ms a step of GPT-2 XL, and costs since the
+            # launches spread over the chip: 1.307 against 1.280 ms.)
             self._call("ember_linear_decode", a.data_ptr(), w.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(),
                        M, N, K, _ACT[act], _code(target), None if warm is None else warm.data_ptr(),
                        0 if warm is None else warm.numel() * warm.element_size() // 16 * 16)
