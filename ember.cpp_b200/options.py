@@ -26,7 +26,8 @@ options given in code), so a measurement can flip a switch without touching the 
   decode_bulk      EMBER_DECODE_BULK      the CUDA-core decode attention brings pages in by bulk copies (0: by loads)
   pdl              EMBER_PDL              programmatic dependent launch between the kernels of a step
   cache_ahead      EMBER_CACHE_AHEAD      a decode attention asks the next layer's rows of the cache into L2
-  warm             EMBER_WARM             a small product asks the next product's weights into L2
+  warm             EMBER_WARM             a product asks into L2 the weights that a part announced for the product after it
+                                          (a feed-forward its second matrix; the tcgen05 streaming product the next matrix)
   op_timing        EMBER_OP_TIMING        every launch is bracketed by CUDA events; `CudaOps.op_times()` gives the time per
                                           kernel entry point (ember.cpp: EMBER_OP_TIMING=1, model.h:465-467).  Steps then run
                                           launch by launch (no graph) and without overlap between kernels: read the shares
