@@ -9,11 +9,14 @@
 // that share the key/value head, up to 8; for plain multi-head attention one row of 16 is used,
 // which wastes a tensor pipe that is idle anyway), about 150 instructions a page and warp.
 //
-// A block is two warps (or four: the launch code says when), a page each at a time.  A page's keys and values for one head are one TMA
-// box each (64 rows of 128 bytes, 128-byte swizzle, so that ldmatrix reads them without bank
-// conflicts), requested before the kernel in front is waited for; a warp that has more than one
-// page in its chunk refills its own stage.  Every wait has a limit, after which the launch's
-// results are marked invalid (ember_attention_decode_status).
+// A block is two warps, a page each at a time, or four where chunks are three pages and longer and
+// three such blocks an SM hold the whole launch (head size 64): every page of a short chunk is then
+// on its way from the block's first instruction, and a context of up to four pages is one block with
+// nothing to merge.  A page's keys and values for one head are one TMA box each (64 rows of 128
+// bytes, 128-byte swizzle, so that ldmatrix reads them without bank conflicts), requested before the
+// kernel in front is waited for; a warp that has more than one page in its chunk refills its own
+// stage.  Every wait has a limit, after which the launch's results are marked invalid
+// (ember_attention_decode_status).
 #include <cooperative_groups.h>
 
 #include <unordered_map>
