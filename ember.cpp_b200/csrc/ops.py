@@ -115,6 +115,30 @@ def load_library() -> ctypes.CDLL:
     return lib
 
 
+def decode_chunks(blocks: int, pairs: int, sms: int, slots: int, four_warps: bool) -> int:
+    """Into how many chunks the decode attention cuts a context of `blocks` pages, each chunk a block of the
+    launch, for `pairs` (token, head) pairs on a chip of `sms` SMs that holds `slots` two-warp blocks at once.
+
+    The context is cut so that the launch fills the chip once: as many chunks as resident blocks per pair
+    allow, at least two pages each (a block's fixed costs are then shared by 128 keys).  Pairs that fill the
+    chip by themselves are not cut: their blocks write the output directly, with no partial results to
+    merge.  (A block that waits for an SM starts its copies late: a step of 12 layers at batch 8 and a
+    context of 900 to 1,024 0.557 against 0.593 ms.)
+
+    four_warps (head size 64 on the tensor cores): while chunks of up to four pages (else of up to eight)
+    are few enough for three blocks of four warps an SM to hold them all, the chunks are that long and a block
+    has four warps, a page each at a time: fewer blocks to merge (none up to four pages), and four pages of a
+    chunk on their way from the block's start.  (GPT-2 XL at batch 8: the first steps 1.312 -> 1.260 ms, the
+    sweep to 1,024 tokens 1.433 -> 1.414.)"""
+    n_chunks = max(1, min(slots // max(pairs, 1), -(-blocks // 2)))
+    if four_warps and blocks > 2:
+        for longest in (4, 8):
+            n = -(-blocks // longest)
+            if n <= 8 and n * pairs <= 3 * sms:
+                return n
+    return n_chunks
+
+
 class CudaOps:
     name = "cuda-sm100a"
 
@@ -482,26 +506,9 @@ class CudaOps:
             if plan.T != plan.n:      # the decode kernels take token t for sequence t of the step
                 raise KernelError("attention: a step of one token each has as many tokens as sequences")
             blocks = min(plan.max_blocks, max(1, -(-plan.max_end // 64)))
-            # The context is cut into chunks for separate blocks so that the launch fills the chip once: as
-            # many chunks as resident blocks per (token, head) pair allow, at least two pages each (a block's
-            # fixed costs are then shared by 128 keys).  Pairs that fill the chip by themselves are not cut:
-            # their blocks write the output directly, with no partial results to merge.  (A block that waits
-            # for an SM starts its copies late: a step of 12 layers at batch 8 and a context of 900 to 1,024
-            # 0.557 against 0.593 ms.)
             mma = self.decode_mma and head_dim in (64, 128) and n_heads // kv_heads <= 8
             pairs = plan.T * (kv_heads if mma else n_heads)   # the tensor-core kernel takes a group of heads a block
-            n_chunks = max(1, min(self.decode_slots // pairs, -(-blocks // 2)))
-            # Head size 64 on the tensor cores: while chunks of up to four pages (else of up to eight) are few
-            # enough for three blocks of four warps an SM to hold them all, the chunks are that long and a block
-            # has four warps, a page each at a time: fewer blocks to merge (none up to four pages), and four
-            # pages of a chunk on their way from the block's start.  (GPT-2 XL at batch 8: the first steps
-            # 1.312 -> 1.260 ms, the sweep to 1,024 tokens 1.433 -> 1.414.)
-            if mma and head_dim == 64 and blocks > 2:
-                for longest in (4, 8):
-                    n = -(-blocks // longest)
-                    if n <= 8 and n * pairs <= 3 * self.sms:
-                        n_chunks = n
-                        break
+            n_chunks = decode_chunks(blocks, pairs, self.sms, self.decode_slots, mma and head_dim == 64)
             per_chunk = -(-blocks // n_chunks)
             n_partials = self.lib.ember_attention_decode_partials(plan.T, n_heads, head_dim, blocks, per_chunk)
             partials, counters = self._decode_scratch(n_partials, plan.T * n_heads)
